@@ -1,0 +1,153 @@
+/*
+ * ppml_b200.h -- C ABI of libppml_b200.so: the dense-contraction path of the PPML graph executor,
+ * written for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, launches asynchronously on the given
+ * stream (stream = NULL: the legacy default stream, which is what the reference's CUDABackend
+ * uses) and returns a status code: 0 = launched; 1 = bad arguments / unsupported; 2 = K not a
+ * multiple of 32 (Q8); 3 = scratch allocation failed; 4 = quantize launch failed; 5 = unknown
+ * weight type; 6 = kernel launch failed; 7 = the requested kernel family cannot take this shape.
+ * Buffers stay owned by the caller; nothing is retained after the call returns.
+ *
+ * Each declaration names the reference interface it stands in for (path inside the reference
+ * project : line).  The C++ symbols with the reference's own names and signatures (namespace
+ * ppml), which its src/backend/CUDAKernels.cpp binds at link time, are thin forwarders to these
+ * (csrc/ppml_forwarders.cpp).
+ *
+ * Matrix conventions follow the reference: A is [M][K] row-major, B is [N][K] row-major (already
+ * "transposed"), C is [M][N] row-major, C[m][n] = bias[n] + sum_k A[m][k] * B[n][k].
+ */
+#ifndef PPML_B200_H
+#define PPML_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* kernel family selectors ("path" arguments) */
+#define PPML_B200_PATH_AUTO 0   /* tensor cores when the shape allows, else CUDA cores */
+#define PPML_B200_PATH_SIMT 1   /* CUDA cores only (exact fp32 accumulation order)      */
+#define PPML_B200_PATH_UMMA 2   /* tcgen05 only; status 7 when the shape is not eligible */
+
+/* how fp32 operands become tf32 on the tensor-core path */
+#define PPML_B200_TF32_ROUND 0      /* round to nearest in shared memory (cvt.rna), as the reference's tf32 kernel */
+#define PPML_B200_TF32_TMA 1        /* let the TMA unit deliver tf32 */
+#define PPML_B200_TF32_TRUNCATE 2   /* feed fp32 words unchanged; the tensor core drops the low mantissa bits */
+
+const char* ppml_b200_version(void);
+
+/* Replaces cutlass_hw_supported (src/backend/CUDAKernels.cpp:147): 1 when the current device is
+ * compute capability 10.x; major/minor may be NULL. */
+int ppml_b200_hw_supported(int* out_major, int* out_minor);
+
+/* Synchronizes the device and returns 0, or the code a kernel left in the device error word when one
+ * of its bounded waits ran out (8); `where` (may be NULL) receives the site id.  Clears the word. */
+int ppml_b200_device_status(int* where);
+
+/* ---- OP_MUL_MAT, fp32 operands ------------------------------------------------------------
+ * Replaces mul_mat_cuda (src/backend/CUDAKernels.cpp:158; src/cuda/CUDAKernels.cu:1174) and
+ * mul_mat_mma_tf32_smem (src/backend/CUDAKernels.cpp:187; src/cuda/CUDAKernels.cu:1675).
+ * path AUTO/UMMA compute in tf32 with fp32 accumulation, SIMT in fp32. */
+int ppml_b200_mul_mat_f32(const float* A, const float* B, float* C, int M, int K, int N, const float* bias,
+                          int path, int tf32_mode, void* stream);
+
+/* ---- OP_MUL_MAT, 16-bit operands, fp32 output ------------------------------------------------
+ * fp16: replaces mul_mat_mma_f16_smem / mul_mat_mma_f16 / mul_mat_cuda_f16
+ * (src/backend/CUDAKernels.cpp:199, :195, :182).  bf16 has no counterpart in the reference (its type
+ * enum has no bf16 storage); same contract with bfloat16 operands.  bias may be NULL. */
+int ppml_b200_mul_mat_f16(const void* A16, const void* B16, float* C, int M, int K, int N, const float* bias,
+                          int path, void* stream);
+int ppml_b200_mul_mat_bf16(const void* A16, const void* B16, float* C, int M, int K, int N, const float* bias,
+                           int path, void* stream);
+
+/* fp32 -> fp16 / bf16 (round to nearest even); no counterpart in the reference (it has no cast op). */
+int ppml_b200_cast_f32_to_f16(const float* x, void* y, int64_t n, void* stream);
+int ppml_b200_cast_f32_to_bf16(const float* x, void* y, int64_t n, void* stream);
+
+/* ---- Q8 block-quantized OP_MUL_MAT ----------------------------------------------------------
+ * Replaces mul_mat_q8_cuda (src/backend/CUDAKernels.cpp:169; src/cuda/MulMatQ8Kernel.cu:476-547).
+ * W: quantized weights, M rows (out features) of K; wtype 0 = Q8_0 (34-byte blocks), 1 = Q8_1
+ * (36-byte blocks), 2 = Q8_0R ([M*K/32*32] int8 plane then [M*K/32] half scales).  X: fp32
+ * activations [N][K], quantized on the fly per 32-block.  c_trans 0: C[m*N+n]; 1: C[n*M+m].
+ * path_out (may be NULL): 1 = tensor cores, 0 = dp4a.
+ * Extensions over the reference: bias[M] (may be NULL) is added after the last block;
+ * sumi_out (may be NULL) receives the exact int32 block sums as [N][M][K/32]. */
+int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, int K, int wtype, int c_trans,
+                         const float* bias, int32_t* sumi_out, int path, int* path_out, void* stream);
+
+/* Replace quantize_rows_q8_1_cuda / dequantize_q8_0_cuda / dequantize_q8_1_cuda
+ * (src/backend/CUDAKernels.cpp:164-166; src/cuda/QuantKernels.cu:86-109).  ne = element count. */
+int ppml_b200_quantize_rows_q8_1(const float* x, void* y, int64_t ne, void* stream);
+int ppml_b200_dequantize_q8_0(const void* x, float* y, int64_t ne, void* stream);
+int ppml_b200_dequantize_q8_1(const void* x, float* y, int64_t ne, void* stream);
+
+/* Weight preparation.  Host versions replace quantize_q8_0_host + repack_q8_0_host
+ * (include/ppml/QuantBlocks.h:62-79, :128-135) as used by PPMLModel::quantize_big_weight_matrices
+ * (src/model/PPML.cpp:4504-4524); the device version does both steps in one kernel. */
+int ppml_b200_quantize_q8_0_host(const float* src, void* blocks34, int64_t n);
+int ppml_b200_repack_q8_0_host(const void* blocks34, int64_t nblocks, void* q8_0r);
+int ppml_b200_quantize_q8_0r(const float* w_dev, void* q8_0r_dev, int64_t ne, void* stream);
+int64_t ppml_b200_q8_0r_bytes(int64_t numel);
+
+/* ---- OP_FLASH_ATTN_EXT forward ---------------------------------------------------------------
+ * Replaces flash_attn_forward_cuda (src/backend/CUDAKernels.cpp:174; include/ppml/FlashAttn.h:60;
+ * src/cuda/FlashAttnKernel.cu:206-251).  Q/K/V/O [B][h][L][d] (d innermost), bias [B][h][L][L] or
+ * NULL, LSE [B][h][L] or NULL.  O = softmax(scale*Q K^T + bias) V with denominator (l + eps).
+ * scale <= 0 means 1/sqrt(d). */
+typedef struct ppml_b200_flash_cfg {
+    int B, h, L, d;
+    int causal;
+    float scale;
+    float softmax_eps;
+    int Br, Bc;               /* accepted for compatibility; the kernels pick their own tiles */
+} ppml_b200_flash_cfg;
+
+int ppml_b200_flash_attn_forward(const ppml_b200_flash_cfg* cfg, const float* Q, const float* K, const float* V,
+                                 const float* bias, float* O, float* LSE, int path, void* stream);
+
+/* Extended form (no counterpart in the reference, whose config has a single L): Lk keys per query row
+ * (K/V [B][h][Lk][d], bias rows of Lk), and bias_batch_stride in elements between batches
+ * (h*L*Lk for a full bias tensor, 0 to share one [h][L][Lk] bias across the batch). */
+int ppml_b200_flash_attn_forward_ex(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
+                                    const float* Q, const float* K, const float* V, const float* bias,
+                                    float* O, float* LSE, int path, void* stream);
+
+/* ---- OP_OUT_PROD -------------------------------------------------------------------------------
+ * Replaces out_prod_cuda (src/backend/CUDAKernels.cpp:201; src/cuda/OutProdKernel.cu:211-260):
+ * dst[i0,i1,i2,i3] = sum_k s0[i0,k,i2/(ne2/ne02),i3/(ne3/ne03)] * s1[i1,k,i2,i3]; dims in the graph's
+ * order (index 0 innermost).  dst is fully overwritten. */
+int ppml_b200_out_prod(const float* src0, const float* src1, float* dst,
+                       int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03,
+                       int64_t ne10, int64_t ne11, int64_t ne12, int64_t ne13,
+                       int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3, int path, void* stream);
+
+/* ---- OP_TRI_MUL ---------------------------------------------------------------------------------
+ * Replaces tri_mul_cuda (src/backend/CUDAKernels.cpp:316; src/cuda/PairKernels.cu:47-77, :514-523).
+ * Flat layout with D outermost and B innermost: outgoing left[d][i][k][b], right[d][j][k][b];
+ * incoming left[d][k][i][b], right[d][k][j][b]; dst[d][i][j][b] = clamp(inv_L * sum_k ..., +-1e4),
+ * NaN -> 0. */
+int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t D, int64_t I, int64_t J,
+                      int64_t K, int64_t B, float inv_L, int outgoing, int path, void* stream);
+
+/* ---- OP_OUTER_PROD_MEAN ---------------------------------------------------------------------------
+ * Replaces outer_prod_mean_cuda (src/backend/CUDAKernels.cpp:325; src/cuda/PairKernels.cu:177-199,
+ * :553-561): left/right flat [D][L][N][B]; dst[(d1*D+d2)][i][j][b] = inv_N * sum_n left[d1][i][n][b] *
+ * right[d2][j][n][b]. */
+int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst, int64_t D, int64_t L,
+                              int64_t N, int64_t B, float inv_N, int path, void* stream);
+
+/* ---- per-shape statistics ----------------------------------------------------------------------------
+ * Replace mulmat_stats_cuda_begin / mulmat_stats_cuda_end (src/backend/CUDAKernels.cpp:190-191;
+ * src/cuda/CUDAKernels.cu:1693-1732): event pair around one launch, totals per (path, M, K, N).
+ * Active only when the environment has PPML_MULMAT_STATS=1.  ppml_b200_mulmat_stats_dump writes
+ * the table (one line per shape) into buf and returns the number of bytes written. */
+void ppml_b200_mulmat_stats_begin(int M, int K, int N);
+void ppml_b200_mulmat_stats_end(const char* path);
+int ppml_b200_mulmat_stats_dump(char* buf, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PPML_B200_H */

@@ -1,0 +1,60 @@
+// kernels.h -- internal launcher interface between the C-ABI layer (capi.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace ppml_b200 {
+
+// Strided batched contraction on CUDA cores (simt_kernels.cu).
+//   D[plane][m][n] = epi( sum_k A[..][m*a_sm + k*a_sk] * B[..][n*b_sn + k*b_sk] )
+// plane = i3*ne2 + i2; A's plane is (i2 / a_div2, i3 / a_div3) (broadcast as the reference's CPU
+// out_prod does, src/backend/CPUKernels.cpp:836-858).
+struct SimtContract {
+    long long M, N, K;
+    long long a_sm, a_sk, b_sn, b_sk;
+    long long c_sm, c_sn;
+    long long planes, ne2;
+    long long a_s2, a_s3, a_div2, a_div3;
+    long long b_s2, b_s3, c_s2, c_s3;
+    const float* bias;
+    int bias_seed;              // 1: accumulator starts at bias[n] (fp32 mul_mat); 0: added at the end
+    float alpha;
+    int clamp;                  // NaN -> 0, clamp to +-1e4
+    long long opm_D, opm_L, opm_B;   // opm_L > 0: blocked outer-product-mean store
+};
+int launch_simt_contract(const void* A, const void* B, float* C, const SimtContract& p, int elem /*0 f32,1 f16,2 bf16*/,
+                         cudaStream_t st);
+
+int launch_cast(const float* x, void* y, long long n, int to_bf16, cudaStream_t st);
+int launch_quantize_q8_1(const float* x, void* y, long long ne, cudaStream_t st);
+int launch_quantize_q8_0r(const float* w, void* out, long long ne, cudaStream_t st);
+int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaStream_t st);
+int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
+                   const float* bias, int* sumi_out, cudaStream_t st);
+int launch_attn_rowwarp(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+                        int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
+                        long long bias_batch_stride, cudaStream_t st);
+
+// tcgen05 paths (umma_gemm.cu / umma_q8.cu / umma_attn.cu).  Each returns ST_UNSUPPORTED_PATH when the
+// shape or the alignment rules it out, so that the caller can take the CUDA-core kernel.
+struct UmmaGemmArgs {
+    const void* A; const void* B; float* C;
+    int M, N, K, batch;
+    long long lda, ldb;                // row strides (elements)
+    long long a_batch, b_batch;        // batch strides (elements)
+    long long ldc, c_batch;
+    const float* bias; float alpha; int clamp;
+    int opm_D, opm_L;                  // opm_L > 0: blocked outer-product-mean store
+    int elem;                          // 0 fp32 (tf32 math), 1 fp16, 2 bf16
+    int tf32_mode;                     // fp32 only: 0 round in smem (rna), 1 TMA tf32 type, 2 truncate
+};
+int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st);
+
+int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
+                   int* sumi_out, cudaStream_t st);
+
+int num_sms();
+
+}  // namespace ppml_b200

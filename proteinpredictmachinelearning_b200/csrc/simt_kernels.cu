@@ -1,0 +1,392 @@
+// simt_kernels.cu -- CUDA-core kernels: exact-fp32 contraction for every shape the tensor-core
+// paths do not take (unaligned K, inner batch > 1, tiny extents), the block quantizers, casts, the
+// dp4a Q8 product and the general attention kernel.  They keep the reference's summation order
+// (k ascending per output element) so fp32 results agree with its CPU kernels to rounding.
+#include "kernels.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+namespace ppml_b200 {
+
+__device__ int g_device_error[4] = {0, 0, 0, 0};
+
+int* device_error_ptr() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_error) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+
+// =============================================================================================
+// Generic strided batched contraction:  D[p][m][n] = epi( sum_k A[pa][m][k] * B[pb][n][k] )
+// 64 x 64 output tile, 16-deep K slices, 256 threads, 4 x 4 outputs per thread.
+// =============================================================================================
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T, bool A_KFAST, bool B_KFAST>
+__global__ void __launch_bounds__(256)
+simt_contract_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restrict__ C, SimtContract p) {
+    __shared__ float As[16][64 + 4];
+    __shared__ float Bs[16][64 + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const long long m0 = static_cast<long long>(blockIdx.y) * 64, n0 = static_cast<long long>(blockIdx.x) * 64;
+
+    for (long long plane = blockIdx.z; plane < p.planes; plane += gridDim.z) {
+        const long long i3 = plane / p.ne2, i2 = plane - i3 * p.ne2;
+        const T* Ap = A + (i2 / p.a_div2) * p.a_s2 + (i3 / p.a_div3) * p.a_s3;
+        const T* Bp = B + i2 * p.b_s2 + i3 * p.b_s3;
+        float* Cp = C + i2 * p.c_s2 + i3 * p.c_s3;
+
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const long long n = n0 + tx * 4 + j;
+                acc[i][j] = (p.bias_seed && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.0f;
+            }
+
+        for (long long k0 = 0; k0 < p.K; k0 += 16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = tid + i * 256;
+                int mm, kk;
+                if (A_KFAST) { kk = idx & 15; mm = idx >> 4; } else { mm = idx & 63; kk = idx >> 6; }
+                const long long m = m0 + mm, k = k0 + kk;
+                As[kk][mm] = (m < p.M && k < p.K) ? to_f32<T>(Ap[m * p.a_sm + k * p.a_sk]) : 0.0f;
+                int nn, kb;
+                if (B_KFAST) { kb = idx & 15; nn = idx >> 4; } else { nn = idx & 63; kb = idx >> 6; }
+                const long long n = n0 + nn, k2 = k0 + kb;
+                Bs[kb][nn] = (n < p.N && k2 < p.K) ? to_f32<T>(Bp[n * p.b_sn + k2 * p.b_sk]) : 0.0f;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < 16; ++kk) {
+                float a[4], b[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            }
+            __syncthreads();
+        }
+
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long m = m0 + ty * 4 + i;
+            if (m >= p.M) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const long long n = n0 + tx * 4 + j;
+                if (n >= p.N) continue;
+                float v = acc[i][j] * p.alpha;
+                if (!p.bias_seed && p.bias != nullptr) v += p.bias[n];
+                if (p.clamp) {
+                    if (!(v == v)) v = 0.0f; else v = fminf(fmaxf(v, -1e4f), 1e4f);
+                }
+                if (p.opm_L > 0) {
+                    const long long d1 = m / p.opm_L, ii = m - d1 * p.opm_L;
+                    const long long d2 = n / p.opm_L, jj = n - d2 * p.opm_L;
+                    Cp[(((d1 * p.opm_D + d2) * p.opm_L + ii) * p.opm_L + jj) * p.opm_B] = v;
+                } else {
+                    Cp[m * p.c_sm + n * p.c_sn] = v;
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+static int launch_contract_t(const T* A, const T* B, float* C, const SimtContract& p, cudaStream_t st) {
+    if (p.M <= 0 || p.N <= 0 || p.planes <= 0) return ST_BAD_ARGS;
+    dim3 grid(static_cast<unsigned>((p.N + 63) / 64), static_cast<unsigned>((p.M + 63) / 64),
+              static_cast<unsigned>(p.planes < 32768 ? p.planes : 32768));
+    if (grid.y > 65535u) return ST_BAD_ARGS;
+    const bool ak = (p.a_sk == 1), bk = (p.b_sk == 1);
+    if (ak && bk) simt_contract_kernel<T, true, true><<<grid, 256, 0, st>>>(A, B, C, p);
+    else if (ak) simt_contract_kernel<T, true, false><<<grid, 256, 0, st>>>(A, B, C, p);
+    else if (bk) simt_contract_kernel<T, false, true><<<grid, 256, 0, st>>>(A, B, C, p);
+    else simt_contract_kernel<T, false, false><<<grid, 256, 0, st>>>(A, B, C, p);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+int launch_simt_contract(const void* A, const void* B, float* C, const SimtContract& p, int elem, cudaStream_t st) {
+    if (elem == 0) return launch_contract_t<float>(static_cast<const float*>(A), static_cast<const float*>(B), C, p, st);
+    if (elem == 1) return launch_contract_t<__half>(static_cast<const __half*>(A), static_cast<const __half*>(B), C, p, st);
+    return launch_contract_t<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), C, p, st);
+}
+
+// =============================================================================================
+// Casts
+// =============================================================================================
+__device__ __forceinline__ void cast_store(__half* y, float x) { *y = __float2half_rn(x); }
+__device__ __forceinline__ void cast_store(__nv_bfloat16* y, float x) { *y = __float2bfloat16_rn(x); }
+
+template <typename T>
+__global__ void cast_kernel(const float* __restrict__ x, T* __restrict__ y, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        cast_store(y + i, x[i]);
+}
+
+int launch_cast(const float* x, void* y, long long n, int to_bf16, cudaStream_t st) {
+    if (!x || !y || n <= 0) return ST_BAD_ARGS;
+    const int grid = static_cast<int>(((n + 255) / 256) < 148 * 16 ? ((n + 255) / 256) : 148 * 16);
+    if (to_bf16) cast_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(x, static_cast<__nv_bfloat16*>(y), n);
+    else cast_kernel<__half><<<grid, 256, 0, st>>>(x, static_cast<__half*>(y), n);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// =============================================================================================
+// Block quantizers (one warp per 32-element block, lane = element)
+// =============================================================================================
+// Activation quantizer, Q8_1: d = vmax / -128 where vmax is the signed value of the FIRST element
+// holding the maximum magnitude; q = clamp(round(x * (1/d)), -128, 127); ds = (d, d * sum q) as half.
+__global__ void quantize_q8_1_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, long long nblocks) {
+    const long long ib = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ib >= nblocks) return;
+    const int lane = threadIdx.x & 31;
+    const float v = x[ib * 32 + lane];
+    float amax = fabsf(v), vmax = v;
+    int idx = lane;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
+        const float ov = __shfl_xor_sync(0xffffffffu, vmax, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+        if (oa > amax || (oa == amax && oi < idx)) { amax = oa; vmax = ov; idx = oi; }
+    }
+    const float d = (amax == 0.0f) ? 0.0f : vmax / -128.0f;
+    const float inv = (d == 0.0f) ? 0.0f : 1.0f / d;
+    float q = roundf(v * inv);
+    q = q > 127.0f ? 127.0f : (q < -128.0f ? -128.0f : q);
+    const int qi = static_cast<int>(q);
+    uint8_t* blk = y + ib * 36;
+    reinterpret_cast<int8_t*>(blk)[4 + lane] = static_cast<int8_t>(qi);
+    int qsum = qi;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, off);
+    if (lane == 0) {
+        const __half hd = __float2half_rn(d);
+        const __half hs = __float2half_rn(d * static_cast<float>(qsum));
+        reinterpret_cast<__half*>(blk)[0] = hd;
+        reinterpret_cast<__half*>(blk)[1] = hs;
+    }
+}
+
+int launch_quantize_q8_1(const float* x, void* y, long long ne, cudaStream_t st) {
+    if (!x || !y || ne <= 0 || (ne % 32) != 0) return ST_BAD_ARGS;
+    const long long nblocks = ne / 32;
+    const long long grid = (nblocks + 7) / 8;
+    if (grid > 0x7fffffffLL) return ST_BAD_ARGS;
+    quantize_q8_1_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(x, static_cast<uint8_t*>(y), nblocks);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// Weight quantizer, Q8_0 straight into the planar Q8_0R layout: d = amax / 127 (stored as half),
+// q = clamp(round(x * (1/d)), -127, 127); qs plane [nblocks*32], then d plane [nblocks].
+__global__ void quantize_q8_0r_kernel(const float* __restrict__ x, int8_t* __restrict__ qs, __half* __restrict__ dpl,
+                                      long long nblocks) {
+    const long long ib = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ib >= nblocks) return;
+    const int lane = threadIdx.x & 31;
+    const float v = x[ib * 32 + lane];
+    float amax = fabsf(v);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float d = amax / 127.0f;
+    const float inv = (amax == 0.0f) ? 0.0f : 1.0f / d;
+    float q = roundf(v * inv);
+    q = q > 127.0f ? 127.0f : (q < -127.0f ? -127.0f : q);
+    qs[ib * 32 + lane] = static_cast<int8_t>(q);
+    if (lane == 0) dpl[ib] = __float2half_rn(d);
+}
+
+int launch_quantize_q8_0r(const float* w, void* out, long long ne, cudaStream_t st) {
+    if (!w || !out || ne <= 0 || (ne % 32) != 0) return ST_BAD_ARGS;
+    const long long nblocks = ne / 32;
+    const long long grid = (nblocks + 7) / 8;
+    if (grid > 0x7fffffffLL) return ST_BAD_ARGS;
+    int8_t* qs = static_cast<int8_t*>(out);
+    __half* dpl = reinterpret_cast<__half*>(qs + nblocks * 32);
+    quantize_q8_0r_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(w, qs, dpl, nblocks);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+__global__ void dequantize_q8_kernel(const uint8_t* __restrict__ x, float* __restrict__ y, long long ne, int bsize, int qoff) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= ne) return;
+    const long long ib = i >> 5;
+    const int iq = static_cast<int>(i & 31);
+    const uint8_t* blk = x + ib * bsize;
+    const float d = __half2float(*reinterpret_cast<const __half*>(blk));
+    y[i] = d * static_cast<float>(reinterpret_cast<const int8_t*>(blk)[qoff + iq]);
+}
+
+int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaStream_t st) {
+    if (!x || !y || ne <= 0) return ST_BAD_ARGS;
+    const long long grid = (ne + 255) / 256;
+    if (grid > 0x7fffffffLL) return ST_BAD_ARGS;
+    dequantize_q8_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(static_cast<const uint8_t*>(x), y, ne,
+                                                                      kind == 0 ? 34 : 36, kind == 0 ? 2 : 4);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// =============================================================================================
+// Q8 product on CUDA cores (dp4a): one thread per output (m = weight row, n = token).
+// acts: Q8_1 blocks [N][nblk] (36 bytes each).  Per block: sumi (int32, exact), then
+// acc += float(sumi) * (d_w * d_a), blocks in ascending order.
+// =============================================================================================
+__device__ __forceinline__ int load_i32_unaligned2(const uint8_t* p) {   // 2-byte aligned source
+    const uint16_t lo = *reinterpret_cast<const uint16_t*>(p);
+    const uint16_t hi = *reinterpret_cast<const uint16_t*>(p + 2);
+    return static_cast<int>(static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16));
+}
+
+__global__ void __launch_bounds__(128)
+q8_dp4a_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ acts, float* __restrict__ C,
+               int M, int N, int nblk, int wtype, int c_trans, const float* __restrict__ bias,
+               int* __restrict__ sumi_out) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    const size_t nb_all = static_cast<size_t>(M) * nblk;
+    for (int n = blockIdx.y; n < N; n += gridDim.y) {
+    const uint8_t* arow = acts + static_cast<size_t>(n) * nblk * 36;
+    float acc = 0.0f;
+    for (int ib = 0; ib < nblk; ++ib) {
+        const size_t blk = static_cast<size_t>(m) * nblk + ib;
+        int wq[8];
+        float dw;
+        if (wtype == 2) {
+            const int* q = reinterpret_cast<const int*>(W + blk * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wq[j] = q[j];
+            dw = __half2float(*reinterpret_cast<const __half*>(W + nb_all * 32 + blk * 2));
+        } else if (wtype == 0) {
+            const uint8_t* b = W + blk * 34;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wq[j] = load_i32_unaligned2(b + 2 + 4 * j);
+            dw = __half2float(*reinterpret_cast<const __half*>(b));
+        } else {
+            const uint8_t* b = W + blk * 36;
+            const int* q = reinterpret_cast<const int*>(b + 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wq[j] = q[j];
+            dw = __half2float(*reinterpret_cast<const __half*>(b));
+        }
+        const uint8_t* ab = arow + static_cast<size_t>(ib) * 36;
+        const int* va = reinterpret_cast<const int*>(ab + 4);
+        int sumi = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sumi = __dp4a(wq[j], va[j], sumi);
+        if (sumi_out) sumi_out[(static_cast<size_t>(n) * M + m) * nblk + ib] = sumi;
+        const float da = __half2float(*reinterpret_cast<const __half*>(ab));
+        acc += static_cast<float>(sumi) * (dw * da);
+    }
+    if (bias) acc += bias[m];
+    if (c_trans) C[static_cast<size_t>(n) * M + m] = acc;
+    else C[static_cast<size_t>(m) * N + n] = acc;
+    }
+}
+
+int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
+                   const float* bias, int* sumi_out, cudaStream_t st) {
+    dim3 grid((M + 127) / 128, N < 65535 ? N : 65535);
+    q8_dp4a_kernel<<<grid, 128, 0, st>>>(static_cast<const uint8_t*>(W), static_cast<const uint8_t*>(acts), C, M, N,
+                                         nblk, wtype, c_trans, bias, sumi_out);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// =============================================================================================
+// General attention forward (any L, Lk, head dim <= 128): one warp per query row, lanes over keys.
+// O = softmax(scale * Q K^T + bias) V with denominator (l + eps); LSE = m + log(l + eps);
+// a row with no unmasked key gives O = 0, LSE = -inf.
+// =============================================================================================
+__global__ void __launch_bounds__(128)
+attn_rowwarp_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                    const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
+                    int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride) {
+    extern __shared__ float qs[];                    // [4][d]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 4 + warp;
+    const int hh = blockIdx.y, b = blockIdx.z;
+    const size_t bh = static_cast<size_t>(b) * H + hh;
+    const float* Qb = Q + bh * static_cast<size_t>(L) * d;
+    const float* Kb = K + bh * static_cast<size_t>(Lk) * d;
+    const float* Vb = V + bh * static_cast<size_t>(Lk) * d;
+    float* myq = qs + warp * d;
+    if (i < L) for (int dd = lane; dd < d; dd += 32) myq[dd] = Qb[static_cast<size_t>(i) * d + dd];
+    __syncwarp();
+    if (i >= L) return;
+    const float* Bb = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
+                                 (static_cast<size_t>(hh) * L + i) * static_cast<size_t>(Lk) : nullptr;
+    const int jmax = causal ? ((i + 1 < Lk) ? i + 1 : Lk) : Lk;
+    float m = -CUDART_INF_F, l = 0.0f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j0 = 0; j0 < jmax; j0 += 32) {
+        const int j = j0 + lane;
+        float s = -CUDART_INF_F;
+        if (j < jmax) {
+            const float* k = Kb + static_cast<size_t>(j) * d;
+            float dot = 0.0f;
+            for (int dd = 0; dd < d; ++dd) dot = fmaf(myq[dd], k[dd], dot);
+            s = dot * scale;
+            if (Bb) s += Bb[j];
+        }
+        float mt = s;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off));
+        const float m_new = fmaxf(m, mt);
+        const float alpha = (m == -CUDART_INF_F) ? 0.0f : expf(m - m_new);
+        const float pj = (j < jmax && m_new != -CUDART_INF_F) ? expf(s - m_new) : 0.0f;
+        float lt = pj;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, off);
+        l = alpha * l + lt;
+        m = m_new;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) acc[t] *= alpha;
+        const int nj = (jmax - j0 < 32) ? (jmax - j0) : 32;
+        for (int jj = 0; jj < nj; ++jj) {
+            const float p = __shfl_sync(0xffffffffu, pj, jj);
+            const float* v = Vb + static_cast<size_t>(j0 + jj) * d;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int dd = lane + 32 * t;
+                if (dd < d) acc[t] = fmaf(p, v[dd], acc[t]);
+            }
+        }
+    }
+    float* o = O + bh * static_cast<size_t>(L) * d + static_cast<size_t>(i) * d;
+    if (l > 0.0f) {
+        const float inv = 1.0f / (l + eps);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) { const int dd = lane + 32 * t; if (dd < d) o[dd] = acc[t] * inv; }
+        if (LSE && lane == 0) LSE[bh * L + i] = m + logf(l + eps);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) { const int dd = lane + 32 * t; if (dd < d) o[dd] = 0.0f; }
+        if (LSE && lane == 0) LSE[bh * L + i] = -CUDART_INF_F;
+    }
+}
+
+int launch_attn_rowwarp(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+                        int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
+                        long long bias_batch_stride, cudaStream_t st) {
+    if (d > 128 || H > 65535 || B > 65535) return ST_BAD_ARGS;
+    dim3 grid((L + 3) / 4, H, B);
+    attn_rowwarp_kernel<<<grid, 128, 4 * d * sizeof(float), st>>>(Q, K, V, bias, O, LSE, H, L, Lk, d, causal, scale,
+                                                                 eps, bias_batch_stride);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+}  // namespace ppml_b200

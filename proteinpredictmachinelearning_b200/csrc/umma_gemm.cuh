@@ -1,0 +1,270 @@
+// umma_gemm.cuh -- the tcgen05 contraction engine shared by mul_mat (tf32 / f16 / bf16), the
+// outgoing triangle multiplication and the outer-product-mean.
+//
+//   D[b][m][n] = sum_k A[b][m][k] * B[b][n][k]          (both operands K-major, i.e. "NT")
+//
+// One persistent CTA per SM walks the (batch, m-tile, n-tile) list.  Per tile:
+//   warp 0      TMA producer: 128 x 128-byte A tile and BN x 128-byte B tile per K step, 128-byte swizzle
+//   warps 6-9   (tf32 with software rounding only) round the landed fp32 words to tf32 in place
+//   warp 1      one elected thread issues tcgen05.mma (M = 128, N = BN, 32 bytes of K each) into TMEM
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulators, scale / bias / clamp, stores
+// TMEM holds two accumulators of BN columns so the epilogue of a tile overlaps the next tile's
+// main loop.  Every wait is bounded (common.cuh).
+#pragma once
+#include "common.cuh"
+
+namespace ppml_b200 {
+
+enum class Epi { ROW_MAJOR, OPM_BLOCKED };
+
+struct GemmParams {
+    int M, N, K;            // per-batch extents: rows of A, rows of B, contraction length
+    int batch;
+    int m_tiles, n_tiles;
+    int k_steps;            // ceil(K / elements per 128 bytes)
+    float* C;
+    long long ldc;          // row stride of C (elements)
+    long long c_batch;      // batch stride of C (elements)
+    const float* bias;      // [N] or null, added after alpha
+    float alpha;            // scales the accumulator
+    int clamp;              // 1: NaN -> 0 and clamp to +-1e4 (triangle multiplication)
+    int vec_ok;             // 1: float4 stores are legal (alignment checked on the host)
+    int opm_D, opm_L;       // OPM_BLOCKED: row = d1*L+i, col = d2*L+j -> ((d1*D+d2)*L+i)*L+j
+    int ab_fmt;             // operand format of the f16 kind: 0 = fp16, 1 = bf16
+    int* err;               // device error word
+};
+
+constexpr int kGemmStageA = 128 * 128;          // bytes of one A tile
+constexpr int kGemmMaxStages = 8;
+
+template <int BN>
+__host__ __device__ constexpr int gemm_stage_bytes() { return kGemmStageA + BN * 128; }
+
+template <int BN>
+__host__ __device__ constexpr int gemm_num_stages() {
+    int s = (200 * 1024) / gemm_stage_bytes<BN>();
+    return s > kGemmMaxStages ? kGemmMaxStages : s;
+}
+
+// dynamic smem: [stages x (A tile | B tile)] (1024-byte aligned) followed by the barriers
+template <int BN>
+__host__ __device__ constexpr int gemm_smem_bytes() {
+    return gemm_num_stages<BN>() * gemm_stage_bytes<BN>() + 1024 /*alignment slack*/ + 512 /*barriers*/;
+}
+
+template <MmaKind KIND, int BN, Epi EPI, bool CONVERT>
+__global__ void __launch_bounds__(CONVERT ? 320 : 192, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+    constexpr int STAGES = gemm_num_stages<BN>();
+    constexpr int STAGE_BYTES = gemm_stage_bytes<BN>();
+    constexpr int ESIZE = (KIND == MmaKind::TF32) ? 4 : (KIND == MmaKind::F16 ? 2 : 1);
+    constexpr int BK = 128 / ESIZE;                       // elements of K per stage
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "UMMA N");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    // barrier slots (8 bytes each)
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kGemmMaxStages + s); };
+    auto conv_bar = [&](int s) { return bar_base + 8u * (2 * kGemmMaxStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (3 * kGemmMaxStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (3 * kGemmMaxStages + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 8 * (3 * kGemmMaxStages + 4));
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(smem_gen + STAGES * STAGE_BYTES + 8 * (3 * kGemmMaxStages + 4) + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+            mbar_init(conv_bar(s), 4);
+        }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        *cta_abort = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&tmA); prefetch_tmap(&tmB); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_per_batch = p.m_tiles * p.n_tiles;
+    const int total_tiles = tiles_per_batch * p.batch;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int b = t / tiles_per_batch;
+                const int r = t - b * tiles_per_batch;
+                const int mt = r / p.n_tiles, nt = r - mt * p.n_tiles;
+                for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, p.err, 0x101)) { ok = false; break; }
+                    const uint32_t sa = smem_base + s * STAGE_BYTES;
+                    mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
+                    tma_load_3d(sa, &tmA, full_bar(s), ks * BK, mt * 128, b);
+                    tma_load_3d(sa + kGemmStageA, &tmB, full_bar(s), ks * BK, nt * BN, b);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------
+        if (lane == 0) {
+            uint32_t idesc;
+            if constexpr (KIND == MmaKind::I8) idesc = make_idesc(2, 1, 1, 0, 0, 128, BN);
+            else if constexpr (KIND == MmaKind::TF32) idesc = make_idesc(1, 2, 2, 0, 0, 128, BN);
+            else idesc = make_idesc(1, p.ab_fmt, p.ab_fmt, 0, 0, 128, BN);
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+                const int acc = tile_i & 1;
+                const uint32_t acc_ph = (tile_i >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, cta_abort, p.err, 0x201)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(CONVERT ? conv_bar(s) : full_bar(s), ph, cta_abort, p.err, 0x202)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * STAGE_BYTES;
+                    const uint64_t da = make_smem_desc(sa, 16, 1024, kLayoutSW128);
+                    const uint64_t db = make_smem_desc(sa + kGemmStageA, 16, 1024, kLayoutSW128);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        // 32 bytes of K per instruction: advance the start address by 2 x 16 bytes
+                        umma<KIND>(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));          // stage reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(tfull_bar(acc));    // accumulator complete
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ------------------------------- epilogue -----------------------------------
+        const int q = warp & 3;                          // TMEM lane quarter this warp may touch
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+            const int b = t / tiles_per_batch;
+            const int r = t - b * tiles_per_batch;
+            const int mt = r / p.n_tiles, nt = r - mt * p.n_tiles;
+            const int acc = tile_i & 1;
+            const uint32_t acc_ph = (tile_i >> 1) & 1u;
+            if (!mbar_wait(tfull_bar(acc), acc_ph, cta_abort, p.err, 0x301)) { ok = false; break; }
+            tc_fence_after();
+            const int row = mt * 128 + q * 32 + lane;
+            const int col0 = nt * BN;
+            const bool row_ok = row < p.M;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int cbase = col0 + c * 32;
+                if (cbase >= p.N) break;                 // uniform across the warp
+                uint32_t v[32];
+                tmem_ld32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                tmem_ld_wait();
+                if (row_ok) {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(v[j]) * p.alpha;
+                        if (p.bias != nullptr && cbase + j < p.N) x += p.bias[cbase + j];
+                        if (p.clamp) {
+                            if (!(x == x)) x = 0.0f;
+                            else x = fminf(fmaxf(x, -1e4f), 1e4f);
+                        }
+                        f[j] = x;
+                    }
+                    if constexpr (EPI == Epi::ROW_MAJOR) {
+                        float* dst = p.C + static_cast<long long>(b) * p.c_batch + static_cast<long long>(row) * p.ldc + cbase;
+                        if (p.vec_ok && cbase + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (cbase + j < p.N) dst[j] = f[j];
+                        }
+                    } else {
+                        const int L = p.opm_L, D = p.opm_D;
+                        const int d1 = row / L, i = row - d1 * L;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const int col = cbase + j;
+                            if (col >= p.N) break;
+                            const int d2 = col / L, jj = col - d2 * L;
+                            float* dst = p.C + ((static_cast<long long>(d1) * D + d2) * L + i) * L + jj;
+                            if (p.vec_ok && jj + 4 <= L) {
+                                *reinterpret_cast<float4*>(dst) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int ce = col + e;
+                                    if (ce < p.N) {
+                                        const int d2e = ce / L, je = ce - d2e * L;
+                                        p.C[((static_cast<long long>(d1) * D + d2e) * L + i) * L + je] = f[j + e];
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    } else {
+        // ------------------------------- tf32 rounding (CONVERT only) ----------------
+        if constexpr (CONVERT) {
+            const int ctid = threadIdx.x - 6 * 32;       // 0..127
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, cta_abort, p.err, 0x401)) { ok = false; break; }
+                    float4* st = reinterpret_cast<float4*>(smem_gen + s * STAGE_BYTES);
+#pragma unroll 4
+                    for (int i = ctid; i < STAGE_BYTES / 16; i += 128) {
+                        float4 x = st[i];
+                        x.x = tf32_round(x.x); x.y = tf32_round(x.y); x.z = tf32_round(x.z); x.w = tf32_round(x.w);
+                        st[i] = x;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(conv_bar(s));
+                }
+            }
+        }
+    }
+
+    // common exit: all roles meet here (also after an aborted wait) before TMEM is released
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace ppml_b200

@@ -1,0 +1,396 @@
+// umma_q8.cu -- W8A8 block-quantized mul_mat on tcgen05 (kind::i8), Q8_0R weights.
+//
+//   C[token][out] = sum_blocks float(sum_{32} q_w * q_a) * (d_w * d_a)   (+ bias[out])
+//
+// The activations never make a round trip through HBM as int8: fp32 rows are pulled in by TMA
+// (128 tokens x one 32-element quant block per stage, 128-byte swizzle), quantized from shared
+// memory by four warps (one thread per token row: absmax, d = vmax / -128, q = round(x / d)) and
+// written as the K-major int8 A operand, which stays resident for all weight column blocks of the
+// work item.  The int8 weights stream in by TMA.  Every quant block is ONE tcgen05.mma (K = 32)
+// into its own 128-column TMEM slot (four slots rotate); eight epilogue warps drain a slot, convert
+// the exact int32 block sums to fp32, scale by d_w * d_a and accumulate in registers in block order.
+//
+// Warp roles (480 threads): 0 activation TMA, 1 weight TMA, 2 MMA issue + TMEM owner,
+// 3-10 epilogue (two per TMEM lane quarter, 64 columns each), 11-14 quantizers.
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "tma_host.h"
+
+namespace ppml_b200 {
+
+namespace {
+
+constexpr int kTile = 128 * 128;          // bytes: one int8 A tile (128 rows x 128 K) == one weight stage == one raw fp32 stage
+constexpr int kMaxKT = 8;                 // K <= 1024
+constexpr int kMaxStages = 6;
+constexpr int kThreads = 480;
+
+struct Q8Params {
+    int Mout, Ntok, K, nblk, KT;
+    int m_tiles;               // token tiles
+    int n_blocks;              // weight column blocks of 128
+    int groups, blocks_per_group;
+    int RS, BS;                // ring depths
+    const __half* Wd;          // weight scales [Mout][nblk]
+    float* C;
+    const float* bias;
+    int* sumi_out;
+    int c_trans;
+    int vec_ok;
+    int* err;
+};
+
+struct SmemLayout {
+    uint32_t a_off, raw_off, w_off, dw_off, da_off, bar_off, total;
+};
+
+__host__ __device__ inline SmemLayout q8_layout(int KT, int nblk, int RS, int BS) {
+    SmemLayout L;
+    L.a_off = 0;
+    L.raw_off = L.a_off + KT * kTile;
+    L.w_off = L.raw_off + RS * kTile;
+    L.dw_off = L.w_off + BS * kTile;                 // float [nblk][128]
+    L.da_off = L.dw_off + nblk * 128 * 4;            // half  [2][nblk][128]
+    L.bar_off = L.da_off + 2 * nblk * 128 * 2;
+    L.bar_off = (L.bar_off + 15u) & ~15u;
+    L.total = L.bar_off + 8 * (4 * kMaxStages + 2 * kMaxKT + 8 + 4) + 16;
+    return L;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Q8Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* sg = smem_raw + (smem_base - smem_u32(smem_raw));
+    const SmemLayout L = q8_layout(p.KT, p.nblk, p.RS, p.BS);
+    const uint32_t bar0 = smem_base + L.bar_off;
+    auto raw_full = [&](int s) { return bar0 + 8u * s; };
+    auto raw_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+    auto w_full = [&](int s) { return bar0 + 8u * (2 * kMaxStages + s); };
+    auto w_empty = [&](int s) { return bar0 + 8u * (3 * kMaxStages + s); };
+    auto a_full = [&](int k) { return bar0 + 8u * (4 * kMaxStages + k); };
+    auto a_empty = [&](int k) { return bar0 + 8u * (4 * kMaxStages + kMaxKT + k); };
+    auto t_full = [&](int s) { return bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + s); };
+    auto t_empty = [&](int s) { return bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + 4 + s); };
+    auto epi_done = [&](int b) { return bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + 8 + b); };
+    const uint32_t dw_full = bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + 10);
+    const uint32_t dw_free = bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + 11);
+    uint8_t* tail = sg + L.bar_off + 8 * (4 * kMaxStages + 2 * kMaxKT + 12);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tail + 8);
+
+    float* dw_s = reinterpret_cast<float*>(sg + L.dw_off);
+    __half* da_s = reinterpret_cast<__half*>(sg + L.da_off);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), 4);
+            mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1);
+        }
+        for (int k = 0; k < kMaxKT; ++k) {
+            int nb = p.nblk - 4 * k; nb = nb < 0 ? 0 : (nb > 4 ? 4 : nb);
+            mbar_init(a_full(k), nb > 0 ? 4 * nb : 1);
+            mbar_init(a_empty(k), 1);
+        }
+        for (int s = 0; s < 4; ++s) { mbar_init(t_full(s), 1); mbar_init(t_empty(s), 8); }
+        mbar_init(epi_done(0), 8); mbar_init(epi_done(1), 8);
+        mbar_init(dw_full, 8); mbar_init(dw_free, 8);
+        *cta_abort = 0;
+        fence_barrier_init();
+    }
+    if (warp == 2) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) prefetch_tmap(&tmX);
+    if (warp == 1 && lane == 0) prefetch_tmap(&tmW);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_items = p.m_tiles * p.groups;
+
+    if (warp == 0) {
+        // ---------------- activation TMA: one 128 x 32 fp32 box per quant block -----------------
+        if (lane == 0) {
+            uint32_t cnt = 0; bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                const int mt = item / p.groups;
+                for (int kb = 0; kb < p.nblk; ++kb, ++cnt) {
+                    const int s = cnt % p.RS; const uint32_t ph = (cnt / p.RS) & 1u;
+                    if (!mbar_wait(raw_empty(s), ph ^ 1u, cta_abort, p.err, 0x1101)) { ok = false; break; }
+                    mbar_arrive_expect_tx(raw_full(s), kTile);
+                    tma_load_3d(smem_base + L.raw_off + s * kTile, &tmX, raw_full(s), kb * 32, mt * 128, 0);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- weight TMA: 128 rows x 128 int8 per stage ------------------------------
+        if (lane == 0) {
+            uint32_t cnt = 0; bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                const int g = item % p.groups;
+                const int nb0 = g * p.blocks_per_group;
+                const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
+                for (int nb = nb0; nb < nb1 && ok; ++nb) {
+                    for (int ks = 0; ks < p.KT; ++ks, ++cnt) {
+                        const int s = cnt % p.BS; const uint32_t ph = (cnt / p.BS) & 1u;
+                        if (!mbar_wait(w_empty(s), ph ^ 1u, cta_abort, p.err, 0x1201)) { ok = false; break; }
+                        mbar_arrive_expect_tx(w_full(s), kTile);
+                        tma_load_3d(smem_base + L.w_off + s * kTile, &tmW, w_full(s), ks * 128, nb * 128, 0);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ---------------- MMA issue: one instruction per quant block -----------------------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(2, 1, 1, 0, 0, 128, 128);
+            uint32_t wcnt = 0, bcnt = 0, n_it = 0; bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
+                const int g = item % p.groups;
+                const int nb0 = g * p.blocks_per_group;
+                const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
+                for (int nb = nb0; nb < nb1 && ok; ++nb) {
+                    for (int ks = 0; ks < p.KT && ok; ++ks, ++wcnt) {
+                        if (nb == nb0) {
+                            if (!mbar_wait(a_full(ks), n_it & 1u, cta_abort, p.err, 0x1301)) { ok = false; break; }
+                        }
+                        const int s = wcnt % p.BS; const uint32_t ph = (wcnt / p.BS) & 1u;
+                        if (!mbar_wait(w_full(s), ph, cta_abort, p.err, 0x1302)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t da = make_smem_desc(smem_base + L.a_off + ks * kTile, 16, 1024, kLayoutSW128);
+                        const uint64_t db = make_smem_desc(smem_base + L.w_off + s * kTile, 16, 1024, kLayoutSW128);
+                        const int nblk_step = min(4, p.nblk - 4 * ks);
+                        for (int j = 0; j < nblk_step; ++j, ++bcnt) {
+                            const int slot = bcnt & 3; const uint32_t tph = (bcnt >> 2) & 1u;
+                            if (!mbar_wait(t_empty(slot), tph ^ 1u, cta_abort, p.err, 0x1303)) { ok = false; break; }
+                            tc_fence_after();
+                            umma<MmaKind::I8>(tmem_base + slot * 128, da + 2u * j, db + 2u * j, idesc, 0u);
+                            umma_commit(t_full(slot));
+                        }
+                        if (!ok) break;
+                        umma_commit(w_empty(s));
+                        if (nb == nb1 - 1) umma_commit(a_empty(ks));
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 11) {
+        // ---------------- epilogue: per-block rescale, fp32 accumulation in registers -------------
+        const int q = warp & 3;                       // TMEM lane quarter
+        const int half = (warp - 3) >> 2;             // which 64 of the 128 columns
+        const int etid = threadIdx.x - 3 * 32;        // 0..255
+        const int row = q * 32 + lane;                // token row inside the tile
+        uint32_t bcnt = 0, n_it = 0, nbcnt = 0; bool ok = true;
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
+            const int mt = item / p.groups, g = item % p.groups;
+            const int nb0 = g * p.blocks_per_group;
+            const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
+            const int tok = mt * 128 + row;
+            const __half* da_row = da_s + (n_it & 1) * p.nblk * 128 + row;
+            for (int nb = nb0; nb < nb1 && ok; ++nb, ++nbcnt) {
+                // stage this column block's weight scales as fp32 [nblk][128]: wait until every
+                // epilogue warp has finished with the previous table, fill, publish
+                if (!mbar_wait(dw_free, (nbcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
+                for (int i = etid; i < p.nblk * 128; i += 256) {
+                    const int kb = i >> 7, col = i & 127;
+                    const int mo = nb * 128 + col;
+                    dw_s[i] = (mo < p.Mout) ? __half2float(p.Wd[static_cast<size_t>(mo) * p.nblk + kb]) : 0.0f;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dw_full);
+                if (!mbar_wait(dw_full, nbcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
+                float acc[64];
+#pragma unroll
+                for (int j = 0; j < 64; ++j) acc[j] = 0.0f;
+                for (int kb = 0; kb < p.nblk; ++kb, ++bcnt) {
+                    const int slot = bcnt & 3; const uint32_t tph = (bcnt >> 2) & 1u;
+                    if (!mbar_wait(t_full(slot), tph, cta_abort, p.err, 0x1401)) { ok = false; break; }
+                    tc_fence_after();
+                    const float da = __half2float(da_row[kb * 128]);
+                    const float4* dwp = reinterpret_cast<const float4*>(dw_s + kb * 128 + half * 64);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_base + slot * 128 + half * 64 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 w4 = dwp[c * 8 + j4];
+                            acc[c * 32 + j4 * 4 + 0] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 0])), w4.x * da, acc[c * 32 + j4 * 4 + 0]);
+                            acc[c * 32 + j4 * 4 + 1] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 1])), w4.y * da, acc[c * 32 + j4 * 4 + 1]);
+                            acc[c * 32 + j4 * 4 + 2] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 2])), w4.z * da, acc[c * 32 + j4 * 4 + 2]);
+                            acc[c * 32 + j4 * 4 + 3] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 3])), w4.w * da, acc[c * 32 + j4 * 4 + 3]);
+                        }
+                        if (p.sumi_out != nullptr && tok < p.Ntok) {
+                            for (int j = 0; j < 32; ++j) {
+                                const int mo = nb * 128 + half * 64 + c * 32 + j;
+                                if (mo < p.Mout)
+                                    p.sumi_out[(static_cast<size_t>(tok) * p.Mout + mo) * p.nblk + kb] = static_cast<int>(v[j]);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(t_empty(slot));
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dw_free);
+                if (tok < p.Ntok) {
+                    const int mo0 = nb * 128 + half * 64;
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
+                    }
+                    if (p.c_trans) {
+                        float* dst = p.C + static_cast<size_t>(tok) * p.Mout + mo0;
+                        if (p.vec_ok && mo0 + 64 <= p.Mout) {
+#pragma unroll
+                            for (int j = 0; j < 64; j += 4)
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 64; ++j) if (mo0 + j < p.Mout) dst[j] = acc[j];
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j)
+                            if (mo0 + j < p.Mout) p.C[static_cast<size_t>(mo0 + j) * p.Ntok + tok] = acc[j];
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_done(n_it & 1));
+        }
+    } else {
+        // ---------------- quantizers: one thread per token row ------------------------------------
+        const int row = threadIdx.x - 11 * 32;        // 0..127
+        uint32_t cnt = 0, n_it = 0; bool ok = true;
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
+            if (n_it >= 2) {
+                if (!mbar_wait(epi_done(n_it & 1), ((n_it >> 1) - 1) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
+            }
+            __half* da_w = da_s + (n_it & 1) * p.nblk * 128 + row;
+            for (int kb = 0; kb < p.nblk; ++kb, ++cnt) {
+                const int ks = kb >> 2;
+                if ((kb & 3) == 0) {
+                    if (!mbar_wait(a_empty(ks), (n_it & 1u) ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
+                }
+                const int s = cnt % p.RS; const uint32_t ph = (cnt / p.RS) & 1u;
+                if (!mbar_wait(raw_full(s), ph, cta_abort, p.err, 0x1503)) { ok = false; break; }
+                const uint8_t* raw = sg + L.raw_off + s * kTile;
+                float x[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 t = *reinterpret_cast<const float4*>(raw + sw128_off(row, c));
+                    x[4 * c] = t.x; x[4 * c + 1] = t.y; x[4 * c + 2] = t.z; x[4 * c + 3] = t.w;
+                }
+                // signed value of the first element that attains the maximum magnitude
+                float vpos = x[0], vneg = x[0];
+#pragma unroll
+                for (int i = 1; i < 32; ++i) { vpos = fmaxf(vpos, x[i]); vneg = fminf(vneg, x[i]); }
+                const float amax = fmaxf(vpos, -vneg);
+                float vmax;
+                if (vpos == -vneg && amax != 0.0f) {        // +a and -a both present: the first one wins
+                    vmax = 0.0f;
+#pragma unroll
+                    for (int i = 31; i >= 0; --i) if (fabsf(x[i]) == amax) vmax = x[i];
+                } else {
+                    vmax = (vpos == amax) ? vpos : vneg;
+                }
+                const float d = (amax == 0.0f) ? 0.0f : vmax / -128.0f;
+                const float inv = (d == 0.0f) ? 0.0f : 1.0f / d;
+                uint32_t packed[8];
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float qf = roundf(x[4 * w + e] * inv);
+                        qf = fminf(fmaxf(qf, -128.0f), 127.0f);
+                        word |= (static_cast<uint32_t>(static_cast<int>(qf)) & 0xffu) << (8 * e);
+                    }
+                    packed[w] = word;
+                }
+                uint8_t* at = sg + L.a_off + ks * kTile;
+                const int c0 = (kb & 3) * 2;
+                *reinterpret_cast<uint4*>(at + sw128_off(row, c0)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(at + sw128_off(row, c0 + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                da_w[kb * 128] = __float2half_rn(d);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(raw_empty(s)); mbar_arrive(a_full(ks)); }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+}  // namespace
+
+// W: Q8_0R weights ([Mout*nblk*32] int8 plane followed by [Mout*nblk] half scales); X fp32 [Ntok][K];
+// M = weight rows (out features), N = tokens, as in the reference's launcher.
+int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
+                   int* sumi_out, cudaStream_t st) {
+    if (!W || !X || !C || M <= 0 || N <= 0 || K <= 0) return ST_BAD_ARGS;
+    if (K % 32) return ST_BAD_K;
+    if (K > 128 * kMaxKT) return ST_UNSUPPORTED_PATH;
+    if ((reinterpret_cast<uintptr_t>(W) & 15u) || (reinterpret_cast<uintptr_t>(X) & 15u)) return ST_UNSUPPORTED_PATH;
+    int* err = device_error_ptr();
+    if (!err) return ST_LAUNCH;
+
+    Q8Params p{};
+    p.Mout = M; p.Ntok = N; p.K = K; p.nblk = K / 32; p.KT = (K + 127) / 128;
+    p.m_tiles = (N + 127) / 128;
+    p.n_blocks = (M + 127) / 128;
+    const int sms = num_sms();
+    int groups = 1;
+    if (p.m_tiles < sms) {
+        groups = (sms + p.m_tiles - 1) / p.m_tiles;
+        if (groups > p.n_blocks) groups = p.n_blocks;
+    }
+    p.blocks_per_group = (p.n_blocks + groups - 1) / groups;
+    p.groups = (p.n_blocks + p.blocks_per_group - 1) / p.blocks_per_group;
+    // ring depths from what the resident A tile and the scale tables leave
+    const int budget = 226 * 1024;
+    const int fixed = static_cast<int>(q8_layout(p.KT, p.nblk, 0, 0).total) + 1024;
+    int stages = (budget - fixed) / kTile;
+    if (stages < 3) return ST_UNSUPPORTED_PATH;
+    if (stages > 2 * kMaxStages) stages = 2 * kMaxStages;
+    p.RS = stages / 2; p.BS = stages - p.RS;
+    if (p.RS > kMaxStages) p.RS = kMaxStages;
+    if (p.BS > kMaxStages) p.BS = kMaxStages;
+    const __half* Wd = reinterpret_cast<const __half*>(static_cast<const int8_t*>(W) + static_cast<size_t>(M) * p.nblk * 32);
+    p.Wd = Wd; p.C = C; p.bias = bias; p.sumi_out = sumi_out; p.c_trans = c_trans; p.err = err;
+    p.vec_ok = c_trans && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && (M % 4 == 0);
+
+    CUtensorMap tmX, tmW;
+    if (!make_tmap_3d(&tmX, TmaType::F32, X, K, N, 1, static_cast<uint64_t>(K) * 4, 0, 32, 128, true)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, true)) return ST_UNSUPPORTED_PATH;
+
+    const int smem = static_cast<int>(q8_layout(p.KT, p.nblk, p.RS, p.BS).total) + 1024;
+    static int configured_smem[64] = {0};
+    int dev = 0; cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured_smem[dev] < smem) {
+        if (cudaFuncSetAttribute(umma_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+            cudaGetLastError();
+            return ST_LAUNCH;
+        }
+        configured_smem[dev] = 227 * 1024;
+    }
+    const int total_items = p.m_tiles * p.groups;
+    const int grid = total_items < sms ? total_items : sms;
+    umma_q8_kernel<<<grid, kThreads, smem, st>>>(tmX, tmW, p);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+}  // namespace ppml_b200

@@ -1,0 +1,182 @@
+"""Host-side mirror of the reference's per-op launcher interface for the dense-contraction path
+(the free functions CUDABackend::dispatch_node calls, src/backend/CUDAKernels.cpp:97-345), over the
+C ABI of libppml_b200.so.  Same names, argument meaning and error behaviour; tensors are torch CUDA
+tensors used only as device memory.  A non-zero status raises RuntimeError."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import PATH_AUTO, PATH_SIMT, PATH_UMMA, TF32_ROUND, FlashCfg
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    s = torch.cuda.current_stream().cuda_stream
+    return C.c_void_p(s) if s else None
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with status {rc}")
+
+
+def _f32c(t):
+    assert t.is_cuda and t.dtype == torch.float32
+    return t.contiguous()
+
+
+def device_status():
+    """Synchronizes; returns (code, where): (0, 0) unless a kernel gave up a bounded wait."""
+    where = C.c_int(0)
+    rc = _lib.load().ppml_b200_device_status(C.byref(where))
+    return rc, where.value
+
+
+def mul_mat_cuda(A, B, bias=None, path=PATH_AUTO, tf32_mode=TF32_ROUND, out=None):
+    """C[M,N] = A[M,K] @ B[N,K]^T (+ bias[N]); replaces mul_mat_cuda / mul_mat_mma_tf32_smem."""
+    A, B = _f32c(A), _f32c(B)
+    M, K = A.shape
+    N = B.shape[0]
+    assert B.shape[1] == K
+    Cout = out if out is not None else torch.empty((M, N), device=A.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_mul_mat_f32(_p(A), _p(B), _p(Cout), M, K, N, _p(bias), path, tf32_mode, _stream())
+    _check(rc, "mul_mat_f32")
+    return Cout
+
+
+def mul_mat_16(A16, B16, bias=None, path=PATH_AUTO, out=None):
+    """16-bit operands (torch.float16 or torch.bfloat16), fp32 output; replaces the mul_mat_*f16* launchers."""
+    assert A16.dtype == B16.dtype and A16.dtype in (torch.float16, torch.bfloat16)
+    A16, B16 = A16.contiguous(), B16.contiguous()
+    M, K = A16.shape
+    N = B16.shape[0]
+    Cout = out if out is not None else torch.empty((M, N), device=A16.device, dtype=torch.float32)
+    fn = _lib.load().ppml_b200_mul_mat_f16 if A16.dtype == torch.float16 else _lib.load().ppml_b200_mul_mat_bf16
+    _check(fn(_p(A16), _p(B16), _p(Cout), M, K, N, _p(bias), path, _stream()), "mul_mat_16")
+    return Cout
+
+
+def cast(x, dtype):
+    x = _f32c(x)
+    y = torch.empty(x.shape, device=x.device, dtype=dtype)
+    fn = _lib.load().ppml_b200_cast_f32_to_f16 if dtype == torch.float16 else _lib.load().ppml_b200_cast_f32_to_bf16
+    _check(fn(_p(x), _p(y), x.numel(), _stream()), "cast")
+    return y
+
+
+def quantize_q8_0r(W):
+    """fp32 weights [M,K] (device) -> planar Q8_0R bytes (device uint8), K % 32 == 0."""
+    W = _f32c(W)
+    out = torch.empty(W.numel() // 32 * 34, device=W.device, dtype=torch.uint8)
+    _check(_lib.load().ppml_b200_quantize_q8_0r(_p(W), _p(out), W.numel(), _stream()), "quantize_q8_0r")
+    return out
+
+
+def quantize_q8_0_host(w):
+    """numpy fp32 -> 34-byte Q8_0 blocks (host)."""
+    w = np.ascontiguousarray(w, np.float32)
+    out = np.empty(w.size // 32 * 34, np.uint8)
+    _check(_lib.load().ppml_b200_quantize_q8_0_host(w.ctypes.data, out.ctypes.data, w.size), "quantize_q8_0_host")
+    return out
+
+
+def repack_q8_0_host(blocks):
+    nb = blocks.size // 34
+    out = np.empty(nb * 34, np.uint8)
+    _check(_lib.load().ppml_b200_repack_q8_0_host(blocks.ctypes.data, nb, out.ctypes.data), "repack_q8_0_host")
+    return out
+
+
+def quantize_rows_q8_1_cuda(x):
+    x = _f32c(x)
+    out = torch.empty(x.numel() // 32 * 36, device=x.device, dtype=torch.uint8)
+    _check(_lib.load().ppml_b200_quantize_rows_q8_1(_p(x), _p(out), x.numel(), _stream()), "quantize_rows_q8_1")
+    return out
+
+
+def dequantize_q8_cuda(blocks, kind):
+    bs = 34 if kind == 0 else 36
+    ne = blocks.numel() // bs * 32
+    y = torch.empty(ne, device=blocks.device, dtype=torch.float32)
+    fn = _lib.load().ppml_b200_dequantize_q8_0 if kind == 0 else _lib.load().ppml_b200_dequantize_q8_1
+    _check(fn(_p(blocks), _p(y), ne, _stream()), "dequantize")
+    return y
+
+
+def mul_mat_q8_cuda(W, X, M, wtype=2, c_trans=1, bias=None, path=PATH_AUTO, want_sumi=False, out=None):
+    """W: quantized weight bytes (device uint8), M rows of K; X fp32 [N,K].  Returns C ([N,M] if c_trans
+    else [M,N]), the path taken (1 tensor cores / 0 dp4a) and, if asked, the int32 block sums [N,M,K/32]."""
+    X = _f32c(X)
+    N, K = X.shape
+    Cout = out if out is not None else torch.empty((N, M) if c_trans else (M, N), device=X.device, dtype=torch.float32)
+    sumi = torch.empty((N, M, K // 32), device=X.device, dtype=torch.int32) if want_sumi else None
+    taken = C.c_int(0)
+    rc = _lib.load().ppml_b200_mul_mat_q8(_p(W), _p(X), _p(Cout), M, N, K, wtype, c_trans, _p(bias), _p(sumi), path,
+                                          C.byref(taken), _stream())
+    _check(rc, "mul_mat_q8")
+    return (Cout, taken.value, sumi) if want_sumi else (Cout, taken.value)
+
+
+def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-9, bias_bcast=False, path=PATH_AUTO):
+    """Q [B,h,L,d], K/V [B,h,Lk,d], bias [B,h,L,Lk] (or [h,L,Lk] shared over B with bias_bcast).
+    Returns (O, LSE).  Lk != L and bias_bcast go through the extended entry."""
+    Q, K, V = _f32c(Q), _f32c(K), _f32c(V)
+    B, h, L, d = Q.shape
+    Lk = K.shape[2]
+    O = torch.empty_like(Q)
+    LSE = torch.empty((B, h, L), device=Q.device, dtype=torch.float32)
+    cfg = FlashCfg(B, h, L, d, int(causal), float(scale), float(eps), 64, 64)
+    lib = _lib.load()
+    if Lk == L and not bias_bcast:
+        rc = lib.ppml_b200_flash_attn_forward(C.byref(cfg), _p(Q), _p(K), _p(V), _p(bias), _p(O), _p(LSE), path, _stream())
+    else:
+        stride = 0 if (bias is None or bias_bcast) else h * L * Lk
+        rc = lib.ppml_b200_flash_attn_forward_ex(C.byref(cfg), Lk, stride, _p(Q), _p(K), _p(V), _p(bias), _p(O), _p(LSE),
+                                                 path, _stream())
+    _check(rc, "flash_attn_forward")
+    return O, LSE
+
+
+def out_prod_cuda(s0, s1, path=PATH_AUTO):
+    """s0 [ne03,ne02,K,ne00], s1 [ne13,ne12,K,ne10] (torch order = reversed graph dims) -> [ne3,ne2,ne10,ne00]."""
+    s0, s1 = _f32c(s0), _f32c(s1)
+    ne03, ne02, ne01, ne00 = s0.shape
+    ne13, ne12, ne11, ne10 = s1.shape
+    ne2, ne3 = max(ne02, ne12), max(ne03, ne13)
+    dst = torch.empty((ne3, ne2, ne10, ne00), device=s0.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_out_prod(_p(s0), _p(s1), _p(dst), ne00, ne01, ne02, ne03, ne10, ne11, ne12, ne13,
+                                        ne00, ne10, ne2, ne3, path, _stream())
+    _check(rc, "out_prod")
+    return dst
+
+
+def tri_mul_cuda(left, right, L, outgoing, path=PATH_AUTO):
+    """Flat layout, D outermost, B innermost: outgoing left [D,I,K,B], right [D,J,K,B]; incoming left
+    [D,K,I,B], right [D,K,J,B] -> dst [D,I,J,B]."""
+    left, right = _f32c(left), _f32c(right)
+    if outgoing:
+        D, I, K, B = left.shape
+        J = right.shape[1]
+    else:
+        D, K, I, B = left.shape
+        J = right.shape[2]
+    dst = torch.empty((D, I, J, B), device=left.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_tri_mul(_p(left), _p(right), _p(dst), D, I, J, K, B, 1.0 / float(L), int(bool(outgoing)),
+                                       path, _stream())
+    _check(rc, "tri_mul")
+    return dst
+
+
+def outer_prod_mean_cuda(left, right, path=PATH_AUTO):
+    """left/right flat [D,L,N,B] -> [D*D, L, L, B], mean over N."""
+    left, right = _f32c(left), _f32c(right)
+    D, L, N, B = left.shape
+    dst = torch.empty((D * D, L, L, B), device=left.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_outer_prod_mean(_p(left), _p(right), _p(dst), D, L, N, B, 1.0 / float(N), path, _stream())
+    _check(rc, "outer_prod_mean")
+    return dst

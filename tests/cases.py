@@ -1,0 +1,71 @@
+"""Seeded synthetic inputs shared by the golden-fixture generator and the parity tests.  The shapes
+and value distributions are those BASELINE.json's configs give (dev-size forward shapes, the Q8
+sweep, axial attention, pair-track contractions), scaled down where a CPU checker must finish in
+seconds."""
+import numpy as np
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def mul_mat_case(M, K, N, seed=1, bias=True):
+    r = rng(seed)
+    a = r.standard_normal((M, K)).astype(np.float32)
+    b = (r.standard_normal((N, K)) * 0.02).astype(np.float32)      # N(0, 0.02) linear weights
+    bi = (r.standard_normal(N) * 0.1).astype(np.float32) if bias else None
+    return a, b, bi
+
+
+def q8_case(M_out, N_tok, K, seed=2):
+    r = rng(seed)
+    w = (r.standard_normal((M_out, K)) * 0.02).astype(np.float32)
+    x = r.standard_normal((N_tok, K)).astype(np.float32)
+    return w, x
+
+
+def attn_case(B, h, L, d, Lk=None, seed=3, bias=True, bias_bcast=False):
+    r = rng(seed)
+    Lk = L if Lk is None else Lk
+    s = 1.0 / np.sqrt(32.0)
+    Q = (r.standard_normal((B, h, L, d)) * s).astype(np.float32)
+    K = (r.standard_normal((B, h, Lk, d)) * s).astype(np.float32)
+    V = (r.standard_normal((B, h, Lk, d)) * s).astype(np.float32)
+    bi = None
+    if bias:
+        shape = (h, L, Lk) if bias_bcast else (B, h, L, Lk)
+        bi = r.standard_normal(shape).astype(np.float32)
+    return Q, K, V, bi
+
+
+def tri_case(D, I, J, K, B=1, outgoing=True, seed=4):
+    r = rng(seed)
+    if outgoing:
+        left = r.standard_normal((D, I, K, B)).astype(np.float32)
+        right = r.standard_normal((D, J, K, B)).astype(np.float32)
+    else:
+        left = r.standard_normal((D, K, I, B)).astype(np.float32)
+        right = r.standard_normal((D, K, J, B)).astype(np.float32)
+    return left, right
+
+
+def opm_case(D, L, N, B=1, seed=4):
+    r = rng(seed)
+    return (r.standard_normal((D, L, N, B)).astype(np.float32),
+            r.standard_normal((D, L, N, B)).astype(np.float32))
+
+
+def out_prod_case(ne00, ne10, K, ne2, ne3, ne02=None, ne03=None, seed=5):
+    r = rng(seed)
+    ne02 = ne2 if ne02 is None else ne02
+    ne03 = ne3 if ne03 is None else ne03
+    s0 = r.standard_normal((ne03, ne02, K, ne00)).astype(np.float32)
+    s1 = r.standard_normal((ne3, ne2, K, ne10)).astype(np.float32)
+    return s0, s1
+
+
+def rel_err(got, ref):
+    """max |got - ref| / max |ref| -- the normalised error every floating-point tolerance here uses."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
