@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): the Q8 block-quantized mul_mat sweep -- weights W[N,K] ~
+N(0, 0.02) quantized to int8 blocks of 32 with an fp16 scale (planar Q8_0R), activations X[M,K] ~ N(0,1)
+quantized on the fly; K in {128, 256, 1024}, N in {128, 256, 512, 1024}, M in {408, 2601, 65536}; seed 2.
+One step = one pass over all 36 shapes.  `value` is the whole-job rate with inputs resident in HBM;
+`e2e` is the same pass through the C ABI with host buffers (pinned), copies inside the timed region.
+At N > 1 GPUs every rank runs the sweep on its own shard of token rows (weak scaling, no data-path
+collective: token rows are independent).
+
+`--impl reference` times the reference arithmetic on the host cores: the reference ships no CPU kernel
+for Q8 mul_mat (include/ppml/QuantBlocks.h:56), so this arm runs the CPU restatement of its CUDA kernel
+(oracle/ppml_oracle.c) on a bounded sample of the same sweep, threaded over token rows.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+KS = (128, 256, 1024)
+NS = (128, 256, 512, 1024)
+MS = (408, 2601, 65536)
+SEED = 2
+
+
+def shapes(ms=MS):
+    return [(m, k, n) for m in ms for k in KS for n in NS]
+
+
+def q8_flops(m, k, n):
+    return 2.0 * m * k * n
+
+
+def q8_bytes(m, k, n):
+    """Algorithmic HBM bytes of one Q8 mul_mat: planar int8 weights with half scales, fp32
+    activations in, fp32 result out."""
+    return (34.0 / 32.0) * n * k + 4.0 * m * k + 4.0 * m * n
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the restated reference arithmetic on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_q8_pass(oracle, sample, threads):
+    """One pass of the CPU port over `sample` = [(W_packed, X, M_out)], token rows split over threads."""
+    import numpy as np
+
+    def work(W, X, m_out, out, lo, hi):
+        out[lo:hi] = oracle.mul_mat_q8(W, X[lo:hi], m_out, wtype=2, c_trans=1)
+
+    t0 = time.perf_counter()
+    for W, X, m_out in sample:
+        out = np.empty((X.shape[0], m_out), np.float32)
+        n = X.shape[0]
+        step = (n + threads - 1) // threads
+        ts = [threading.Thread(target=work, args=(W, X, m_out, out, lo, min(lo + step, n))) for lo in range(0, n, step)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+    return time.perf_counter() - t0
+
+
+def make_cpu_sample(oracle, ms):
+    import numpy as np
+    r = np.random.default_rng(SEED)
+    sample, flops = [], 0.0
+    for (m, k, n) in shapes(ms):
+        w = (r.standard_normal((n, k)) * 0.02).astype(np.float32)
+        x = r.standard_normal((m, k)).astype(np.float32)
+        sample.append((oracle.repack_q8_0(oracle.quantize_q8_0(w)), x, n))
+        flops += q8_flops(m, k, n)
+    return sample, flops
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from checkers import Oracle
+    oracle = Oracle()
+    threads = os.cpu_count() or 1
+    sample_ms = (408,)          # bounded sample: the 12 (K, N) pairs at M = 408 tokens
+    sample, flops = make_cpu_sample(oracle, sample_ms)
+    for _ in range(args.warmup):
+        cpu_q8_pass(oracle, sample, threads)
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_q8_pass(oracle, sample, threads)
+    val = flops * args.steps / t / 1e12
+    line = {
+        "impl": "reference", "metric": "mul_mat TFLOPS", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "q8 (int8 x int8 -> int32, fp32 rescale)", "data": "synthetic",
+        "config": {"workload": "configs[1] Q8 block-quantized mul_mat sweep", "K": list(KS), "N": list(NS), "M": list(MS)},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": "the 12 (K,N) pairs of the sweep at M=408 tokens per step (the reference has no CPU "
+                                   "Q8 kernel; restated CUDA arithmetic, threaded over token rows)"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from proteinpredictmachinelearning_b200 import PATH_AUTO, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # resident inputs: one X per (M, K), one W per (K, N), one C per (M, N); each rank seeds its own shard
+    g = torch.Generator(device=dev).manual_seed(SEED + 1000 * rank)
+    X = {(m, k): torch.randn((m, k), device=dev, generator=g) for m in MS for k in KS}
+    Wf = {(k, n): torch.randn((n, k), device=dev, generator=g) * 0.02 for k in KS for n in NS}
+    W = {kn: ops.quantize_q8_0r(w) for kn, w in Wf.items()}
+    Cout = {(m, n): torch.empty((m, n), device=dev) for m in MS for n in NS}
+    sh = shapes()
+    step_flops = sum(q8_flops(*s) for s in sh)
+    step_bytes = sum(q8_bytes(*s) for s in sh)
+
+    def one_pass(events=None):
+        for (m, k, n) in sh:
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            _, taken = ops.mul_mat_q8_cuda(W[(k, n)], X[(m, k)], n, wtype=2, c_trans=1, path=PATH_AUTO, out=Cout[(m, n)])
+            if events is not None:
+                e1.record()
+                events.append(((m, k, n), taken, e0, e1))
+
+    for _ in range(max(args.warmup, 3)):
+        one_pass()
+    code, where = ops.device_status()
+    if code != 0:
+        raise RuntimeError(f"device abort {code} at {where:#x}")
+
+    # ---- timed region 1: device-resident ("value") --------------------------------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    events = []
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        one_pass(events)
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    kernel_ms = sum(e0.elapsed_time(e1) for (_, _, e0, e1) in events)
+    per_shape = {}
+    for (s, taken, e0, e1) in events:
+        d = per_shape.setdefault(s, [0.0, 0, taken])
+        d[0] += e0.elapsed_time(e1)
+        d[1] += 1
+    umma_launches = sum(1 for (_, taken, _, _) in events if taken == 1)
+
+    # ---- timed region 2: end to end with host buffers ("e2e") ----------------------------------------
+    Xh = {key: torch.empty(t.shape, dtype=torch.float32).pin_memory().copy_(t.cpu()) for key, t in X.items()}
+    Ch = {key: torch.empty(t.shape, dtype=torch.float32).pin_memory() for key, t in Cout.items()}
+    h2d = sum(t.numel() * 4 for t in Xh.values())
+    d2h = sum(t.numel() * 4 for t in Ch.values())
+
+    def e2e_pass():
+        for key, t in Xh.items():
+            X[key].copy_(t, non_blocking=True)
+        one_pass()
+        for key, t in Ch.items():
+            t.copy_(Cout[key], non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_pass()
+    barrier()
+    u0 = torch.cuda.Event(enable_timing=True)
+    u1 = torch.cuda.Event(enable_timing=True)
+    u0.record()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    u1.record()
+    barrier()
+    e2e_ms = u0.elapsed_time(u1)
+    if world > 1:
+        tt = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item())
+    code, where = ops.device_status()
+    if code != 0:
+        raise RuntimeError(f"device abort {code} at {where:#x}")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = load_peaks()
+    achieved = step_bytes * args.steps / (kernel_ms * 1e-3) / 1e9
+    value = step_flops * args.steps * world / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "mul_mat TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "q8 (int8 x int8 -> int32, fp32 rescale)", "data": "synthetic",
+        "config": {"workload": "configs[1] Q8 block-quantized mul_mat sweep, 36 shapes per step", "K": list(KS),
+                   "N": list(NS), "M": list(MS), "seed": SEED, "sharding": f"token rows, {world} shard(s)",
+                   "l2": "working set per step (~0.9 GB) exceeds L2, no explicit flush"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "umma_q8_kernel, all launches of the timed region (sum of algorithmic bytes / sum of durations)"},
+        "e2e": {"value": step_flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": len(events), "tensor_core_launches": umma_launches, "clocks": clocks,
+        "per_shape": [{"M": s[0], "K": s[1], "N": s[2], "us": 1e3 * v[0] / v[1],
+                       "tflops": q8_flops(*s) / (v[0] / v[1] * 1e-3) / 1e12,
+                       "gbs": q8_bytes(*s) / (v[0] / v[1] * 1e-3) / 1e9, "tensor_cores": v[2]} for s, v in sorted(per_shape.items())],
+    }
+
+    # CPU baseline on rank 0, N = 1 only: the restated reference arithmetic on a bounded sample
+    if world == 1 and not args.no_cpu_baseline:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        from checkers import Oracle
+        oracle = Oracle()
+        threads = os.cpu_count() or 1
+        sample, flops = make_cpu_sample(oracle, (408,))
+        t = cpu_q8_pass(oracle, sample, threads)
+        reps = 1
+        while t < 10.0 and reps < 50:
+            t += cpu_q8_pass(oracle, sample, threads)
+            reps += 1
+        line["cpu_baseline"] = {"value": flops * reps / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                "sample": f"the 12 (K,N) pairs at M=408 tokens, {reps} pass(es), threaded over token rows; "
+                                          "the reference has no CPU Q8 kernel, this is the restated CUDA arithmetic"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,309 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker on identical seeded inputs.
+
+Tolerances (normalised error = max|got-ref| / max|ref|):
+  CUDA-core fp32 kernels        1e-5   (same summation order, FMA contraction only)
+  tf32 tensor-core kernels      1e-3   (BASELINE: fp32/tf32 within 1e-3)
+  fp16 / bf16 operand kernels   1e-5 against the checker fed the same 16-bit operands
+                                1e-2 against the fp32 product (BASELINE: bf16 within 1e-2)
+  Q8: quantized bytes, scales and int32 block sums bit-exact; fp32 result 1e-5
+"""
+import os
+
+import numpy as np
+import pytest
+
+import cases
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from proteinpredictmachinelearning_b200 import PATH_AUTO, PATH_SIMT, PATH_UMMA, TF32_ROUND, TF32_TMA, TF32_TRUNCATE  # noqa: E402
+from proteinpredictmachinelearning_b200 import ops  # noqa: E402
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cpu.npz"))
+TOL_FP32, TOL_TF32, TOL_16 = 1e-5, 1e-3, 1e-2
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.fixture(autouse=True)
+def _no_device_abort():
+    yield
+    code, where = ops.device_status()
+    assert code == 0, f"a kernel gave up a bounded wait: code {code} at site {where:#x}"
+
+
+# ------------------------------------------------------------------------------------------------
+# OP_MUL_MAT fp32
+# ------------------------------------------------------------------------------------------------
+MM_SHAPES = [(17, 9, 23), (408, 256, 256), (51, 128, 8), (255, 33, 32), (130, 64, 128), (1, 1, 1), (2601, 128, 256),
+             (300, 1024, 256), (129, 36, 260)]
+
+
+@pytest.mark.parametrize("M,K,N", MM_SHAPES)
+@pytest.mark.parametrize("bias", [False, True])
+def test_mul_mat_simt(oracle, M, K, N, bias):
+    a, b, bi = cases.mul_mat_case(M, K, N, seed=1, bias=bias)
+    got = host(ops.mul_mat_cuda(dev(a), dev(b), None if bi is None else dev(bi), path=PATH_SIMT))
+    key = f"{'mmb' if bias else 'mm'}_{M}_{K}_{N}"
+    ref = GOLD[key] if key in GOLD else oracle.mul_mat_f32(a, b, bi)
+    assert cases.rel_err(got, ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("M,K,N", [s for s in MM_SHAPES if s[1] % 4 == 0])
+@pytest.mark.parametrize("bias", [False, True])
+def test_mul_mat_tf32_umma(oracle, M, K, N, bias):
+    a, b, bi = cases.mul_mat_case(M, K, N, seed=1, bias=bias)
+    got = host(ops.mul_mat_cuda(dev(a), dev(b), None if bi is None else dev(bi), path=PATH_UMMA, tf32_mode=TF32_ROUND))
+    key = f"{'mmb' if bias else 'mm'}_{M}_{K}_{N}"
+    ref = GOLD[key] if key in GOLD else oracle.mul_mat_f32(a, b, bi)
+    assert cases.rel_err(got, ref) <= TOL_TF32
+
+
+def test_mul_mat_umma_rejects_unaligned_k_and_auto_falls_back(oracle):
+    a, b, bi = cases.mul_mat_case(255, 33, 32, seed=1)
+    with pytest.raises(RuntimeError):
+        ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_UMMA)
+    got = host(ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_AUTO))
+    assert cases.rel_err(got, GOLD["mmb_255_33_32"]) <= TOL_FP32
+
+
+def test_mul_mat_tf32_known_answer_exact():
+    """Reference TF32GemmCorrectness inputs (tests/test_cuda.cpp:1710-1740) are exact in tf32."""
+    M = K = N = 32
+    A = ((np.arange(M * K) % 7).astype(np.float32) * 0.25 - 0.5).reshape(M, K)
+    B = ((np.arange(N * K) % 8).astype(np.float32) * 0.125 + 0.25).reshape(N, K)
+    got = host(ops.mul_mat_cuda(dev(A), dev(B), path=PATH_UMMA))
+    ref = A.astype(np.float64) @ B.astype(np.float64).T
+    assert np.abs(got - ref).max() <= 1e-4
+
+
+@pytest.mark.parametrize("mode", [TF32_ROUND, TF32_TMA, TF32_TRUNCATE])
+def test_mul_mat_tf32_modes_report_error(oracle, mode):
+    """All three ways of feeding fp32 to the tf32 tensor core stay within a loose 4e-3; the default
+    (rounding) must meet 1e-3.  The measured errors are printed for the record."""
+    a, b, bi = cases.mul_mat_case(2048, 256, 256, seed=8, bias=False)
+    a = np.abs(a)
+    b = np.abs(b)                      # same-sign products expose a truncation bias
+    got = host(ops.mul_mat_cuda(dev(a), dev(b), path=PATH_UMMA, tf32_mode=mode))
+    err = cases.rel_err(got, oracle.mul_mat_f32(a, b))
+    print(f"tf32 mode {mode}: normalised error {err:.3e}")
+    assert err <= (TOL_TF32 if mode == TF32_ROUND else 4e-3)
+
+
+def test_mul_mat_large_property_linearity():
+    """Full-size shape (M = 65536 tokens): check linearity in A instead of a CPU product."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A1 = torch.randn((65536, 256), device="cuda", generator=g)
+    A2 = torch.randn((65536, 256), device="cuda", generator=g)
+    B = torch.randn((256, 256), device="cuda", generator=g) * 0.02
+    c1 = ops.mul_mat_cuda(A1, B, path=PATH_SIMT)
+    c2 = ops.mul_mat_cuda(A2, B, path=PATH_SIMT)
+    c12 = ops.mul_mat_cuda(A1 + A2, B, path=PATH_SIMT)
+    assert float((c12 - (c1 + c2)).abs().max() / c12.abs().max()) <= 1e-5
+    t = ops.mul_mat_cuda(A1, B, path=PATH_UMMA)
+    assert float((t - c1).abs().max() / c1.abs().max()) <= TOL_TF32
+
+
+# ------------------------------------------------------------------------------------------------
+# 16-bit operands
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("path", [PATH_SIMT, PATH_UMMA])
+@pytest.mark.parametrize("M,K,N", [(40, 64, 48), (408, 256, 256), (2601, 128, 128), (130, 72, 136)])
+def test_mul_mat_16bit(oracle, dtype, path, M, K, N):
+    a, b, bi = cases.mul_mat_case(M, K, N, seed=11)
+    tdt = torch.float16 if dtype == "f16" else torch.bfloat16
+    a16, b16 = ops.cast(dev(a), tdt), ops.cast(dev(b), tdt)
+    ref_cast = dev(a).to(tdt)
+    assert torch.equal(a16, ref_cast)                                  # the cast kernel rounds to nearest even
+    got = host(ops.mul_mat_16(a16, b16, dev(bi), path=path))
+    ref16 = oracle.mul_mat_16(host(a16.view(torch.int16)).view(np.uint16), host(b16.view(torch.int16)).view(np.uint16), bi, kind=dtype)
+    assert cases.rel_err(got, ref16) <= TOL_FP32
+    assert cases.rel_err(got, oracle.mul_mat_f32(a, b, bi)) <= TOL_16
+    if dtype == "f16" and (M, K, N) == (40, 64, 48):
+        assert cases.rel_err(got, GOLD["mm16_40_64_48"]) <= TOL_FP32
+
+
+# ------------------------------------------------------------------------------------------------
+# Q8
+# ------------------------------------------------------------------------------------------------
+def _q8_special(x):
+    x[3, :32] = 0.0
+    x[4, 0], x[4, 1] = 2.5, -2.5
+    x[5, 0], x[5, 1] = -1.5, 1.5
+    return x
+
+
+def test_quantizers_bit_exact(oracle):
+    w, x = cases.q8_case(24, 20, 128, seed=2)
+    x = _q8_special(x)
+    assert np.array_equal(host(ops.quantize_rows_q8_1_cuda(dev(x))), GOLD["q81_x"])
+    assert np.array_equal(host(ops.quantize_q8_0r(dev(w))), GOLD["q80r_w"])
+    assert np.array_equal(host(ops.dequantize_q8_cuda(dev(GOLD["q80_w"]), 0)), GOLD["deq80_w"])
+    assert np.array_equal(host(ops.dequantize_q8_cuda(dev(GOLD["q81_x"]), 1)), GOLD["deq81_x"])
+    r = np.random.default_rng(7)
+    big = (r.standard_normal(32 * 4099) * 10.0 ** r.integers(-5, 3, 32 * 4099)).astype(np.float32)
+    assert np.array_equal(host(ops.quantize_rows_q8_1_cuda(dev(big))), oracle.quantize_q8_1(big))
+    assert np.array_equal(host(ops.quantize_q8_0r(dev(big))), oracle.repack_q8_0(oracle.quantize_q8_0(big)))
+
+
+Q8_SHAPES = [(24, 20, 128), (128, 408, 128), (256, 408, 256), (512, 300, 1024), (1024, 130, 256), (136, 257, 96),
+             (256, 2601, 128)]
+
+
+@pytest.mark.parametrize("Mout,Ntok,K", Q8_SHAPES)
+@pytest.mark.parametrize("path", [PATH_SIMT, PATH_UMMA])
+def test_mul_mat_q8(oracle, Mout, Ntok, K, path):
+    w, x = cases.q8_case(Mout, Ntok, K, seed=2)
+    if Ntok >= 6:
+        x = _q8_special(x)
+    W = oracle.repack_q8_0(oracle.quantize_q8_0(w))
+    bias = (np.random.default_rng(3).standard_normal(Mout) * 0.1).astype(np.float32)
+    ref, ref_sumi = oracle.mul_mat_q8(W, x, Mout, wtype=2, c_trans=1, bias=bias, want_sumi=True)
+    got, taken, sumi = ops.mul_mat_q8_cuda(dev(W), dev(x), Mout, wtype=2, c_trans=1, bias=dev(bias), path=path, want_sumi=True)
+    assert taken == (1 if path == PATH_UMMA else 0)
+    assert np.array_equal(host(sumi), ref_sumi)                      # int32 block dot products: bit-exact
+    assert cases.rel_err(host(got), ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("wtype", [0, 1, 2])
+@pytest.mark.parametrize("c_trans", [0, 1])
+def test_mul_mat_q8_weight_layouts(oracle, wtype, c_trans):
+    w, x = cases.q8_case(72, 50, 160, seed=2)
+    q80 = oracle.quantize_q8_0(w)
+    if wtype == 0:
+        W = q80
+    elif wtype == 2:
+        W = oracle.repack_q8_0(q80)
+    else:                                                              # Q8_1-typed weights: same d, extra sum field
+        blocks = q80.reshape(-1, 34)
+        W = np.zeros((blocks.shape[0], 36), np.uint8)
+        W[:, :2] = blocks[:, :2]
+        W[:, 4:] = blocks[:, 2:]
+        W = W.reshape(-1)
+    ref = oracle.mul_mat_q8(W, x, 72, wtype=wtype, c_trans=c_trans)
+    got, taken = ops.mul_mat_q8_cuda(dev(W), dev(x), 72, wtype=wtype, c_trans=c_trans)
+    assert cases.rel_err(host(got), ref) <= TOL_FP32
+    if wtype == 2:
+        got2, taken2 = ops.mul_mat_q8_cuda(dev(W), dev(x), 72, wtype=2, c_trans=c_trans, path=PATH_UMMA)
+        assert taken2 == 1 and cases.rel_err(host(got2), ref) <= TOL_FP32
+
+
+def test_mul_mat_q8_full_size_property():
+    """M = 65536 tokens (BASELINE sweep size): tensor-core and dp4a paths must agree exactly on the
+    block sums' consequence -- the fp32 outputs agree to rounding -- and a row permutation of X
+    permutes the rows of C."""
+    g = torch.Generator(device="cuda").manual_seed(2)
+    X = torch.randn((65536, 256), device="cuda", generator=g)
+    Wf = torch.randn((256, 256), device="cuda", generator=g) * 0.02
+    W = ops.quantize_q8_0r(Wf)
+    c_t, taken = ops.mul_mat_q8_cuda(W, X, 256, path=PATH_UMMA)
+    c_s, _ = ops.mul_mat_q8_cuda(W, X, 256, path=PATH_SIMT)
+    assert taken == 1
+    assert float((c_t - c_s).abs().max() / c_s.abs().max()) <= TOL_FP32
+    perm = torch.randperm(65536, device="cuda", generator=g)
+    c_p, _ = ops.mul_mat_q8_cuda(W, X[perm].contiguous(), 256, path=PATH_UMMA)
+    assert torch.equal(c_p, c_t[perm])
+
+
+# ------------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------------
+def test_attention_golden(oracle):
+    Q, K, V, bi = cases.attn_case(2, 3, 70, 32, seed=3)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=1 / np.sqrt(32.0))
+    assert cases.rel_err(host(O), GOLD["fa_O"]) <= TOL_FP32
+    assert np.abs(host(LSE) - GOLD["fa_LSE"]).max() <= 1e-5
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None, causal=True)
+    assert cases.rel_err(host(O), GOLD["fa_causal_O"]) <= TOL_FP32
+    assert np.abs(host(LSE) - GOLD["fa_causal_LSE"]).max() <= 1e-5
+
+
+@pytest.mark.parametrize("B,h,L,d,Lk,bias,bcast", [
+    (8, 8, 51, 32, None, True, False),      # dev-size MSA row attention
+    (51, 8, 8, 32, None, False, False),     # dev-size MSA column attention
+    (8, 8, 51, 8, None, True, False),       # extra-MSA block, head dim 8
+    (51, 8, 1, 8, 8, False, False),         # global column attention, one query over N keys
+    (4, 8, 256, 32, None, True, True),      # full-size rows, one bias shared by the batch
+    (2, 4, 100, 64, 77, True, False),
+])
+def test_attention_shapes(oracle, B, h, L, d, Lk, bias, bcast):
+    Q, K, V, bi = cases.attn_case(B, h, L, d, Lk=Lk, seed=3, bias=bias, bias_bcast=bcast)
+    scale = 1 / np.sqrt(32.0)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None if bi is None else dev(bi), scale=scale, bias_bcast=bcast)
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast)
+    assert cases.rel_err(host(O), rO) <= TOL_FP32
+    assert np.abs(host(LSE) - rL).max() <= 1e-5
+    legacy = oracle.attention_legacy(Q, K, V, bi, scale, bias_bcast=bcast)   # ground truth when Lq != Lk
+    assert cases.rel_err(host(O), legacy) <= TOL_FP32
+
+
+def test_attention_fully_masked_row():
+    Q, K, V, bi = cases.attn_case(1, 1, 4, 8, seed=7)
+    bi[0, 0, 2, :] = -np.inf
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi))
+    O, LSE = host(O), host(LSE)
+    assert np.all(O[0, 0, 2] == 0) and LSE[0, 0, 2] == -np.inf and np.isfinite(O).all()
+
+
+# ------------------------------------------------------------------------------------------------
+# pair-track contractions
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("path,tol", [(PATH_SIMT, TOL_FP32), (PATH_AUTO, TOL_TF32)])
+def test_tri_mul_golden(oracle, path, tol):
+    l, r = cases.tri_case(6, 20, 24, 28, outgoing=True)
+    assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), 28.0, True, path=path)), GOLD["tri_out"]) <= tol
+    l, r = cases.tri_case(6, 20, 24, 28, outgoing=False)
+    assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), 28.0, False, path=path)), GOLD["tri_in"]) <= tol
+    l, r = cases.tri_case(3, 5, 6, 7, B=2, outgoing=True, seed=44)
+    assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), 7.0, True, path=path)), GOLD["tri_out_b2"]) <= tol
+    l = np.full((1, 2, 2, 1), 3e3, np.float32)
+    assert np.array_equal(host(ops.tri_mul_cuda(dev(l), dev(l), 1.0, True, path=path)), GOLD["tri_clamp"])
+    l, r = cases.tri_case(1, 2, 2, 3)
+    l[0, 0, 1, 0] = np.nan
+    got = host(ops.tri_mul_cuda(dev(l), dev(r), 3.0, True, path=path))
+    assert np.all(got[0, 0] == 0) and np.isfinite(got).all()
+
+
+@pytest.mark.parametrize("outgoing", [True, False])
+@pytest.mark.parametrize("L", [51, 128])
+def test_tri_mul_model_shapes(oracle, outgoing, L):
+    l, r = cases.tri_case(16, L, L, L, outgoing=outgoing)
+    ref = oracle.tri_mul(l, r, float(L), outgoing)
+    assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), float(L), outgoing, path=PATH_SIMT)), ref) <= TOL_FP32
+    assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), float(L), outgoing, path=PATH_AUTO)), ref) <= TOL_TF32
+
+
+@pytest.mark.parametrize("path,tol", [(PATH_SIMT, TOL_FP32), (PATH_AUTO, TOL_TF32)])
+def test_outer_prod_mean(oracle, path, tol):
+    l, r = cases.opm_case(4, 12, 9)
+    assert cases.rel_err(host(ops.outer_prod_mean_cuda(dev(l), dev(r), path=path)), GOLD["opm"]) <= tol
+    l, r = cases.opm_case(8, 51, 8)                                  # dev size: D*L = 408, N = 8
+    assert cases.rel_err(host(ops.outer_prod_mean_cuda(dev(l), dev(r), path=path)), oracle.outer_prod_mean(l, r)) <= tol
+    l, r = cases.opm_case(4, 40, 64, B=2, seed=9)
+    assert cases.rel_err(host(ops.outer_prod_mean_cuda(dev(l), dev(r), path=path)), oracle.outer_prod_mean(l, r, B=2)) <= tol
+
+
+def test_out_prod(oracle):
+    s0, s1 = cases.out_prod_case(13, 11, 17, 3, 2)
+    assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1))), GOLD["out_prod"]) <= TOL_FP32
+    s0, s1 = cases.out_prod_case(13, 11, 17, 4, 2, ne02=2, ne03=1)
+    assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1))), GOLD["out_prod_bcast"]) <= TOL_FP32
+    # the reference's "real shape" case (tests/test_cuda.cpp:262-341): ne0 = ne1 = 51, K = 51, 16 x 64 planes (cut to 16 x 4)
+    s0, s1 = cases.out_prod_case(51, 51, 51, 16, 4)
+    assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1))), oracle.out_prod(s0, s1)) <= TOL_FP32
+    # known answer of tests/test_cuda.cpp:207-245
+    a = (np.arange(12) % 7).astype(np.float32) * 0.5
+    b = (np.arange(15) % 9).astype(np.float32) * 0.25 - 1.0
+    got = host(ops.out_prod_cuda(dev(a.reshape(1, 1, 3, 4)), dev(b.reshape(1, 1, 3, 5)))).reshape(5, 4)
+    for i0 in range(4):
+        for i1 in range(5):
+            assert abs(got[i1, i0] - sum(float(a[i0 + k * 4]) * float(b[i1 + k * 5]) for k in range(3))) <= 1e-4
