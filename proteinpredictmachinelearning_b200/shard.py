@@ -1,0 +1,52 @@
+"""Partition of the contraction ops over the GPUs of one box (one process per GPU).
+
+Every activation is split into `world` contiguous chunks of its flat buffer, which under the
+reference's flat-buffer semantics means: token rows for mul_mat / Q8 mul_mat and attention batches,
+channel slabs d for the triangle multiplication (flat [D][I][K]: D independent L x L matrices,
+src/backend/CPUKernels.cpp:934-957) and left-channel slabs d1 for the outer-product-mean (flat
+[D][L][N]: output block (d1, d2) needs slab d1 of `left` and all of `right`,
+src/backend/CPUKernels.cpp:1022-1028).  Only the outer-product-mean needs an exchange (all-gather of
+`right`); everything else is rank-local."""
+
+
+def split(total, world, rank, align=1):
+    """Contiguous [lo, hi) of `total` units for `rank`; boundaries are multiples of `align`
+    (the last shard takes the remainder)."""
+    if world <= 0 or not (0 <= rank < world) or total < 0 or align <= 0:
+        raise ValueError("bad shard arguments")
+    units = (total + align - 1) // align
+    per = (units + world - 1) // world
+    lo = min(rank * per * align, total)
+    hi = min((rank + 1) * per * align, total)
+    return lo, hi
+
+
+def token_rows(M, world, rank):
+    """mul_mat / Q8 mul_mat: rows of X (tokens) are independent."""
+    return split(M, world, rank)
+
+
+def attention_batches(B, world, rank):
+    """OP_FLASH_ATTN_EXT: the outer batch B' (MSA rows, pair rows) is independent."""
+    return split(B, world, rank)
+
+
+def tri_mul_slabs(D, world, rank):
+    """OP_TRI_MUL: channel slabs."""
+    return split(D, world, rank)
+
+
+def opm_slabs(D, world, rank):
+    """OP_OUTER_PROD_MEAN: the d1 range of the output this rank owns (needs all of `right`)."""
+    return split(D, world, rank)
+
+
+def all_gather_rows(x_local, world, group=None):
+    """All-gather along dim 0 of equally sized shards (NCCL on GPUs, gloo in the CPU tests)."""
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return x_local
+    parts = [torch.empty_like(x_local) for _ in range(world)]
+    dist.all_gather(parts, x_local.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
