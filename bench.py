@@ -192,11 +192,13 @@ def run_ours(args):
 
     # resident inputs: one X per (M, K), one W per (K, N), one C per (M, N); each rank seeds its own shard
     g = torch.Generator(device=dev).manual_seed(SEED + 1000 * rank)
-    X = {(m, k): torch.randn((m, k), device=dev, generator=g) for m in MS for k in KS}
-    Wf = {(k, n): torch.randn((n, k), device=dev, generator=g) * 0.02 for k in KS for n in NS}
-    W = {kn: ops.quantize_q8_0r(w) for kn, w in Wf.items()}
-    Cout = {(m, n): torch.empty((m, n), device=dev) for m in MS for n in NS}
     sh = shapes()
+    if args.only:
+        sh = [tuple(int(v) for v in args.only.split(","))]
+    X = {(m, k): torch.randn((m, k), device=dev, generator=g) for (m, k) in sorted({(s[0], s[1]) for s in sh})}
+    Wf = {(k, n): torch.randn((n, k), device=dev, generator=g) * 0.02 for (k, n) in sorted({(s[1], s[2]) for s in sh})}
+    W = {kn: ops.quantize_q8_0r(w) for kn, w in Wf.items()}
+    Cout = {(m, n): torch.empty((m, n), device=dev) for (m, n) in sorted({(s[0], s[2]) for s in sh})}
     step_flops = sum(q8_flops(*s) for s in sh)
     step_bytes = sum(q8_bytes(*s) for s in sh)
 
@@ -245,6 +247,14 @@ def run_ours(args):
     umma_launches = sum(1 for (_, taken, _, _) in events if taken == 1)
 
     # ---- timed region 2: end to end with host buffers ("e2e") ----------------------------------------
+    if args.no_e2e:
+        if rank == 0:
+            print(json.dumps({"only": args.only, "ms_per_step": ms / args.steps, "kernel_ms_per_step": kernel_ms / args.steps,
+                              "tflops": step_flops * args.steps / (kernel_ms * 1e-3) / 1e12,
+                              "gbs": step_bytes * args.steps / (kernel_ms * 1e-3) / 1e9}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     Xh = {key: torch.empty(t.shape, dtype=torch.float32).pin_memory().copy_(t.cpu()) for key, t in X.items()}
     Ch = {key: torch.empty(t.shape, dtype=torch.float32).pin_memory() for key, t in Cout.items()}
     h2d = sum(t.numel() * 4 for t in Xh.values())
@@ -329,6 +339,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="stop after the device-resident region (profiling runs)")
+    ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

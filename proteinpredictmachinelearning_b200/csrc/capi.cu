@@ -202,7 +202,7 @@ int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t
             a.A = left; a.B = right; a.C = dst;
             a.M = static_cast<int>(I); a.N = static_cast<int>(J); a.K = static_cast<int>(K); a.batch = static_cast<int>(D);
             a.lda = K; a.ldb = K; a.a_batch = I * K; a.b_batch = J * K; a.ldc = J; a.c_batch = I * J;
-            a.bias = nullptr; a.alpha = inv_L; a.clamp = 1; a.elem = 0; a.tf32_mode = 0;
+            a.bias = nullptr; a.alpha = inv_L; a.clamp = 1; a.elem = 0; a.tf32_mode = PPML_B200_TF32_TMA;
             rc = launch_umma_gemm(a, st);
         }
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
@@ -230,7 +230,7 @@ int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst,
             a.A = left; a.B = right; a.C = dst;
             a.M = static_cast<int>(D * L); a.N = static_cast<int>(D * L); a.K = static_cast<int>(N); a.batch = 1;
             a.lda = N; a.ldb = N; a.ldc = D * L; a.alpha = inv_N;
-            a.opm_D = static_cast<int>(D); a.opm_L = static_cast<int>(L); a.elem = 0; a.tf32_mode = 0;
+            a.opm_D = static_cast<int>(D); a.opm_L = static_cast<int>(L); a.elem = 0; a.tf32_mode = PPML_B200_TF32_TMA;
             rc = launch_umma_gemm(a, st);
         }
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;

@@ -31,14 +31,14 @@ struct FlashAttnConfig {                    // include/ppml/FlashAttn.h:26-36
 // src/backend/CUDAKernels.cpp:158 -- no status in the signature: a failure is reported on stderr,
 // like the reference's wrappers report theirs.
 void mul_mat_cuda(float* A, float* B, float* C, int M, int K, int N, const float* bias) {
-    const int rc = ppml_b200_mul_mat_f32(A, B, C, M, K, N, bias, PPML_B200_PATH_AUTO, PPML_B200_TF32_ROUND, nullptr);
+    const int rc = ppml_b200_mul_mat_f32(A, B, C, M, K, N, bias, PPML_B200_PATH_AUTO, PPML_B200_TF32_TMA, nullptr);
     if (rc != 0) std::fprintf(stderr, "[ppml_b200] mul_mat_cuda failed rc=%d (M=%d K=%d N=%d)\n", rc, M, K, N);
 }
 
 // src/backend/CUDAKernels.cpp:187 -- 0 = launched, 1 = unsupported (caller falls back to mul_mat_cuda)
 int mul_mat_mma_tf32_smem(const void* A, const void* B, float* C, int M, int K, int N) {
     const int rc = ppml_b200_mul_mat_f32(static_cast<const float*>(A), static_cast<const float*>(B), C, M, K, N, nullptr,
-                                         PPML_B200_PATH_UMMA, PPML_B200_TF32_ROUND, nullptr);
+                                         PPML_B200_PATH_UMMA, PPML_B200_TF32_TMA, nullptr);
     return rc == 0 ? 0 : 1;
 }
 

@@ -13,9 +13,15 @@ namespace ppml_b200 {
 __device__ int g_device_error[4] = {0, 0, 0, 0};
 
 int* device_error_ptr() {
-    int* p = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_error) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    return p;
+    static int* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cached[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_error) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        cached[dev] = p;
+    }
+    return cached[dev];
 }
 
 // =============================================================================================

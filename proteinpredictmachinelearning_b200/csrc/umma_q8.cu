@@ -10,8 +10,9 @@
 // into its own 128-column TMEM slot (four slots rotate); eight epilogue warps drain a slot, convert
 // the exact int32 block sums to fp32, scale by d_w * d_a and accumulate in registers in block order.
 //
-// Warp roles (480 threads): 0 activation TMA, 1 weight TMA, 2 MMA issue + TMEM owner,
-// 3-10 epilogue (two per TMEM lane quarter, 64 columns each), 11-14 quantizers.
+// Warp roles: warps 0-3 = activation TMA (0), weight TMA (1), MMA issue + TMEM owner (2), idle (3);
+// warps 4-11 = epilogue (two warps per TMEM lane quarter, 64 columns each); warps 12.. = quantizers
+// (groups of four warps, one thread per token row, groups take quant blocks round-robin).
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -24,7 +25,8 @@ namespace {
 constexpr int kTile = 128 * 128;          // bytes: one int8 A tile (128 rows x 128 K) == one weight stage == one raw fp32 stage
 constexpr int kMaxKT = 8;                 // K <= 1024
 constexpr int kMaxStages = 6;
-constexpr int kThreads = 480;
+constexpr int kQuantGroups = 1;          // groups of four quantizer warps, taking quant blocks round-robin
+constexpr int kThreads = 32 * (12 + 4 * kQuantGroups);
 
 struct Q8Params {
     int Mout, Ntok, K, nblk, KT;
@@ -180,11 +182,13 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
         }
         __syncwarp();
-    } else if (warp < 11) {
+    } else if (warp == 3) {
+        // idle warp of warpgroup 0
+    } else if (warp < 12) {
         // ---------------- epilogue: per-block rescale, fp32 accumulation in registers -------------
         const int q = warp & 3;                       // TMEM lane quarter
-        const int half = (warp - 3) >> 2;             // which 64 of the 128 columns
-        const int etid = threadIdx.x - 3 * 32;        // 0..255
+        const int half = (warp - 4) >> 2;             // which 64 of the 128 columns
+        const int etid = threadIdx.x - 4 * 32;        // 0..255
         const int row = q * 32 + lane;                // token row inside the tile
         uint32_t bcnt = 0, n_it = 0, nbcnt = 0; bool ok = true;
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
@@ -205,31 +209,39 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dw_full);
                 if (!mbar_wait(dw_full, nbcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
-                float acc[64];
+                // 64 fp32 accumulators as 32 packed pairs
+                uint64_t acc2[32];
 #pragma unroll
-                for (int j = 0; j < 64; ++j) acc[j] = 0.0f;
+                for (int j = 0; j < 32; ++j) acc2[j] = 0ull;
                 for (int kb = 0; kb < p.nblk; ++kb, ++bcnt) {
                     const int slot = bcnt & 3; const uint32_t tph = (bcnt >> 2) & 1u;
                     if (!mbar_wait(t_full(slot), tph, cta_abort, p.err, 0x1401)) { ok = false; break; }
                     tc_fence_after();
                     const float da = __half2float(da_row[kb * 128]);
-                    const float4* dwp = reinterpret_cast<const float4*>(dw_s + kb * 128 + half * 64);
+                    const uint64_t da2 = pack2(da, da);
+                    const uint64_t neg_magic2 = pack2(-12582912.0f, -12582912.0f);
+                    const ulonglong2* dwp = reinterpret_cast<const ulonglong2*>(dw_s + kb * 128 + half * 64);
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem_base + slot * 128 + half * 64 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[16];
+                        tmem_ld16(tmem_base + slot * 128 + half * 64 + c * 16 + (static_cast<uint32_t>(q * 32) << 16), v);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j4 = 0; j4 < 8; ++j4) {
-                            const float4 w4 = dwp[c * 8 + j4];
-                            acc[c * 32 + j4 * 4 + 0] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 0])), w4.x * da, acc[c * 32 + j4 * 4 + 0]);
-                            acc[c * 32 + j4 * 4 + 1] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 1])), w4.y * da, acc[c * 32 + j4 * 4 + 1]);
-                            acc[c * 32 + j4 * 4 + 2] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 2])), w4.z * da, acc[c * 32 + j4 * 4 + 2]);
-                            acc[c * 32 + j4 * 4 + 3] = fmaf(static_cast<float>(static_cast<int>(v[j4 * 4 + 3])), w4.w * da, acc[c * 32 + j4 * 4 + 3]);
+                        for (int j4 = 0; j4 < 4; ++j4) {
+                            // int32 -> fp32 without the conversion unit: |sum| < 2^22, so the integer added to the
+                            // bit pattern of 1.5 * 2^23 is exactly that float plus the sum
+                            const ulonglong2 w4 = dwp[c * 4 + j4];
+                            const uint64_t f01 = fadd2(pack2(__int_as_float(static_cast<int>(v[j4 * 4 + 0]) + 0x4B400000),
+                                                             __int_as_float(static_cast<int>(v[j4 * 4 + 1]) + 0x4B400000)), neg_magic2);
+                            const uint64_t f23 = fadd2(pack2(__int_as_float(static_cast<int>(v[j4 * 4 + 2]) + 0x4B400000),
+                                                             __int_as_float(static_cast<int>(v[j4 * 4 + 3]) + 0x4B400000)), neg_magic2);
+                            acc2[c * 8 + j4 * 2 + 0] = ffma2(f01, fmul2(w4.x, da2), acc2[c * 8 + j4 * 2 + 0]);
+                            acc2[c * 8 + j4 * 2 + 1] = ffma2(f23, fmul2(w4.y, da2), acc2[c * 8 + j4 * 2 + 1]);
                         }
                         if (p.sumi_out != nullptr && tok < p.Ntok) {
-                            for (int j = 0; j < 32; ++j) {
-                                const int mo = nb * 128 + half * 64 + c * 32 + j;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int mo = nb * 128 + half * 64 + c * 16 + j;
                                 if (mo < p.Mout)
                                     p.sumi_out[(static_cast<size_t>(tok) * p.Mout + mo) * p.nblk + kb] = static_cast<int>(v[j]);
                             }
@@ -239,6 +251,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) mbar_arrive(t_empty(slot));
                 }
+                float acc[64];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
                 if (!ok) break;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dw_free);
@@ -269,17 +284,21 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (lane == 0) mbar_arrive(epi_done(n_it & 1));
         }
     } else {
-        // ---------------- quantizers: one thread per token row ------------------------------------
-        const int row = threadIdx.x - 11 * 32;        // 0..127
-        uint32_t cnt = 0, n_it = 0; bool ok = true;
-        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
+        // ---------------- quantizers: one thread per token row, two groups on alternate blocks ----------
+        const int qg = (warp - 12) >> 2;              // quantizer group
+        const int row = ((warp - 12) & 3) * 32 + lane;
+        uint32_t base_cnt = 0, n_it = 0; bool ok = true;
+        const uint64_t half2c = pack2(0.5f, 0.5f), big2 = pack2(8388608.0f, 8388608.0f);
+        const uint64_t nbig2 = pack2(-8388608.0f, -8388608.0f), magic2 = pack2(12582912.0f, 12582912.0f);
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it, base_cnt += p.nblk) {
             if (n_it >= 2) {
                 if (!mbar_wait(epi_done(n_it & 1), ((n_it >> 1) - 1) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
             }
             __half* da_w = da_s + (n_it & 1) * p.nblk * 128 + row;
-            for (int kb = 0; kb < p.nblk; ++kb, ++cnt) {
+            for (int kb = qg; kb < p.nblk; kb += kQuantGroups) {
+                const uint32_t cnt = base_cnt + kb;
                 const int ks = kb >> 2;
-                if ((kb & 3) == 0) {
+                if ((kb & 3) < kQuantGroups) {       // this group's first block of the K step
                     if (!mbar_wait(a_empty(ks), (n_it & 1u) ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
                 }
                 const int s = cnt % p.RS; const uint32_t ph = (cnt / p.RS) & 1u;
@@ -306,17 +325,27 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 }
                 const float d = (amax == 0.0f) ? 0.0f : vmax / -128.0f;
                 const float inv = (d == 0.0f) ? 0.0f : 1.0f / d;
+                const uint64_t inv2 = pack2(inv, inv);
+                // q = min(round-half-away(x * inv), 127), computed without the conversion unit:
+                //   m = floor(|y| + 0.5): both additions round toward zero, which never crosses an integer,
+                //       and adding 2^23 leaves the integer part; m carries y's sign again, is capped at 127,
+                //   and m + 1.5 * 2^23 has the two's-complement byte of q in its low mantissa byte.
                 uint32_t packed[8];
 #pragma unroll
                 for (int w = 0; w < 8; ++w) {
-                    uint32_t word = 0;
+                    uint32_t u[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float qf = roundf(x[4 * w + e] * inv);
-                        qf = fminf(fmaxf(qf, -128.0f), 127.0f);
-                        word |= (static_cast<uint32_t>(static_cast<int>(qf)) & 0xffu) << (8 * e);
+                    for (int e = 0; e < 2; ++e) {
+                        const uint64_t y2 = fmul2(pack2(x[4 * w + 2 * e], x[4 * w + 2 * e + 1]), inv2);
+                        const uint64_t a2 = y2 & 0x7FFFFFFF7FFFFFFFull;
+                        const uint64_t m2 = fadd2(fadd2_rz(fadd2_rz(a2, half2c), big2), nbig2);
+                        float z0, z1;
+                        unpack2(m2 | (y2 & 0x8000000080000000ull), z0, z1);
+                        const uint64_t u2 = fadd2(pack2(fminf(z0, 127.0f), fminf(z1, 127.0f)), magic2);
+                        u[2 * e] = static_cast<uint32_t>(u2);
+                        u[2 * e + 1] = static_cast<uint32_t>(u2 >> 32);
                     }
-                    packed[w] = word;
+                    packed[w] = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
                 }
                 uint8_t* at = sg + L.a_off + ks * kTile;
                 const int c0 = (kb & 3) * 2;
