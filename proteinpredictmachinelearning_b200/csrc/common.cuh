@@ -71,10 +71,32 @@ constexpr long long kWaitCycles = 3000000000LL;   // about 1.5 s at the maximum 
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort, int* err, int site) {
     if (mbar_test(bar, parity)) return true;
+
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_test(bar, parity)) return true;
         if ((it & 63u) == 0u) {
+            if (*cta_abort) return false;
+            if (clock64() - t0 > kWaitCycles) break;
+        }
+    }
+    *cta_abort = 1;
+    err[0] = ST_DEVICE_ABORT;
+    err[1] = site;
+    __threadfence();
+    return false;
+}
+
+// Same policy for roles that usually wait long (producers running ahead of a slow consumer): backs
+// off with nanosleep between polls so that the spinning does not take issue slots from the warps
+// doing the arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* cta_abort, int* err, int site) {
+    if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        __nanosleep(it < 8 ? 32 : 128);
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 15u) == 0u) {
             if (*cta_abort) return false;
             if (clock64() - t0 > kWaitCycles) break;
         }
@@ -140,6 +162,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
+}
+// Writes the same 32-bit value to 32 lanes x 32 consecutive columns (thread t -> lane base+t).
+__device__ __forceinline__ void tmem_st32_fill(uint32_t taddr, uint32_t v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+        "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+        ::"r"(taddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }

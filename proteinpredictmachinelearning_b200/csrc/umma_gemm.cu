@@ -94,7 +94,7 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st) {
     p.err = err;
     const bool c_al = (reinterpret_cast<uintptr_t>(a.C) & 15u) == 0;
     if (a.opm_L > 0) p.vec_ok = c_al && (a.opm_L % 4 == 0);
-    else p.vec_ok = c_al && (a.ldc % 4 == 0) && (a.c_batch % 4 == 0);
+    else p.vec_ok = c_al && (a.ldc % 4 == 0) && (a.c_batch % 4 == 0) && (a.N % 4 == 0);
 
     const bool opm = a.opm_L > 0;
     if (a.elem == 0) {

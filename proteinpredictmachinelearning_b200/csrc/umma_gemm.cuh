@@ -46,10 +46,16 @@ __host__ __device__ constexpr int gemm_num_stages() {
     return s > kGemmMaxStages ? kGemmMaxStages : s;
 }
 
-// dynamic smem: [stages x (A tile | B tile)] (1024-byte aligned) followed by the barriers
+constexpr int kEpiStagePitch = 144;                       // bytes per staged row: 32 floats + 16 bytes of padding
+constexpr int kEpiStageBytes = 32 * kEpiStagePitch;       // one warp's 32 x 32 transposition buffer
+constexpr int kEpiBiasBytes = 256 * 4;                    // one warp's copy of the tile's bias slice
+
+// dynamic smem: [stages x (A tile | B tile)] (1024-byte aligned), the barriers, then per epilogue warp a
+// transposition buffer and a bias slice
 template <int BN>
 __host__ __device__ constexpr int gemm_smem_bytes() {
-    return gemm_num_stages<BN>() * gemm_stage_bytes<BN>() + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    return gemm_num_stages<BN>() * gemm_stage_bytes<BN>() + 1024 /*alignment slack*/ + 512 /*barriers*/ +
+           4 * (kEpiStageBytes + kEpiBiasBytes);
 }
 
 template <MmaKind KIND, int BN, Epi EPI, bool CONVERT>
@@ -159,7 +165,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
     } else if (warp < 6) {
         // ------------------------------- epilogue -----------------------------------
+        // Each warp owns 32 accumulator rows (its TMEM lane quarter).  Per 32-column chunk: TMEM -> registers
+        // (thread = row), scale / bias / clamp, then through a padded shared-memory buffer so that the global
+        // stores are row-contiguous: eight lanes write one 128-byte row segment, four rows per instruction.
         const int q = warp & 3;                          // TMEM lane quarter this warp may touch
+        const int ew = warp - 2;
+        uint8_t* stage = smem_gen + STAGES * STAGE_BYTES + 512 + ew * (kEpiStageBytes + kEpiBiasBytes);
+        float* bias_s = reinterpret_cast<float*>(stage + kEpiStageBytes);
         uint32_t tile_i = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
@@ -168,11 +180,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int mt = r / p.n_tiles, nt = r - mt * p.n_tiles;
             const int acc = tile_i & 1;
             const uint32_t acc_ph = (tile_i >> 1) & 1u;
+            const int col0 = nt * BN;
+            __syncwarp();                                // every lane is done with the previous tile's bias slice
+            if (p.bias != nullptr) {
+                for (int j = lane; j < BN; j += 32) bias_s[j] = (col0 + j < p.N) ? p.bias[col0 + j] : 0.0f;
+            } else {
+                for (int j = lane; j < BN; j += 32) bias_s[j] = 0.0f;
+            }
+            __syncwarp();
             if (!mbar_wait(tfull_bar(acc), acc_ph, cta_abort, p.err, 0x301)) { ok = false; break; }
             tc_fence_after();
-            const int row = mt * 128 + q * 32 + lane;
-            const int col0 = nt * BN;
-            const bool row_ok = row < p.M;
+            const int row0 = mt * 128 + q * 32;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int cbase = col0 + c * 32;
@@ -180,48 +198,63 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 uint32_t v[32];
                 tmem_ld32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                 tmem_ld_wait();
-                if (row_ok) {
-                    float f[32];
+                float f[32];
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bias_s + c * 32 + j4 * 4);
+                    f[j4 * 4 + 0] = fmaf(__uint_as_float(v[j4 * 4 + 0]), p.alpha, b4.x);
+                    f[j4 * 4 + 1] = fmaf(__uint_as_float(v[j4 * 4 + 1]), p.alpha, b4.y);
+                    f[j4 * 4 + 2] = fmaf(__uint_as_float(v[j4 * 4 + 2]), p.alpha, b4.z);
+                    f[j4 * 4 + 3] = fmaf(__uint_as_float(v[j4 * 4 + 3]), p.alpha, b4.w);
+                }
+                if (p.clamp) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(v[j]) * p.alpha;
-                        if (p.bias != nullptr && cbase + j < p.N) x += p.bias[cbase + j];
-                        if (p.clamp) {
-                            if (!(x == x)) x = 0.0f;
-                            else x = fminf(fmaxf(x, -1e4f), 1e4f);
-                        }
+                        float x = f[j];
+                        x = (x == x) ? fminf(fmaxf(x, -1e4f), 1e4f) : 0.0f;
                         f[j] = x;
                     }
-                    if constexpr (EPI == Epi::ROW_MAJOR) {
-                        float* dst = p.C + static_cast<long long>(b) * p.c_batch + static_cast<long long>(row) * p.ldc + cbase;
-                        if (p.vec_ok && cbase + 32 <= p.N) {
+                }
+                if (p.vec_ok) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                        } else {
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(stage + lane * kEpiStagePitch + j * 16) =
+                            make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                    __syncwarp();
+                    const int cc = lane & 7;             // 16-byte chunk inside the 128-byte row segment
+                    const int col = cbase + cc * 4;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (cbase + j < p.N) dst[j] = f[j];
-                        }
-                    } else {
-                        const int L = p.opm_L, D = p.opm_D;
-                        const int d1 = row / L, i = row - d1 * L;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            const int col = cbase + j;
-                            if (col >= p.N) break;
-                            const int d2 = col / L, jj = col - d2 * L;
-                            float* dst = p.C + ((static_cast<long long>(d1) * D + d2) * L + i) * L + jj;
-                            if (p.vec_ok && jj + 4 <= L) {
-                                *reinterpret_cast<float4*>(dst) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = (lane >> 3) + 4 * i;
+                        const int row = row0 + rr;
+                        const float4 val = *reinterpret_cast<const float4*>(stage + rr * kEpiStagePitch + cc * 16);
+                        if (row < p.M && col < p.N) {    // vec_ok: N, ldc (or L) are multiples of 4
+                            if constexpr (EPI == Epi::ROW_MAJOR) {
+                                *reinterpret_cast<float4*>(p.C + static_cast<long long>(b) * p.c_batch +
+                                                           static_cast<long long>(row) * p.ldc + col) = val;
                             } else {
+                                const int L = p.opm_L, D = p.opm_D;
+                                const int d1 = row / L, ii = row - d1 * L;
+                                const int d2 = col / L, jj = col - d2 * L;
+                                *reinterpret_cast<float4*>(p.C + ((static_cast<long long>(d1) * D + d2) * L + ii) * L + jj) = val;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                } else {
+                    const int row = row0 + lane;
+                    if (row < p.M) {
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const int ce = col + e;
-                                    if (ce < p.N) {
-                                        const int d2e = ce / L, je = ce - d2e * L;
-                                        p.C[((static_cast<long long>(d1) * D + d2e) * L + i) * L + je] = f[j + e];
-                                    }
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = cbase + j;
+                            if (col < p.N) {
+                                if constexpr (EPI == Epi::ROW_MAJOR) {
+                                    p.C[static_cast<long long>(b) * p.c_batch + static_cast<long long>(row) * p.ldc + col] = f[j];
+                                } else {
+                                    const int L = p.opm_L, D = p.opm_D;
+                                    const int d1 = row / L, ii = row - d1 * L;
+                                    const int d2 = col / L, jj = col - d2 * L;
+                                    p.C[((static_cast<long long>(d1) * D + d2) * L + ii) * L + jj] = f[j];
                                 }
                             }
                         }

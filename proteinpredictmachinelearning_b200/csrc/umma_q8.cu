@@ -10,8 +10,8 @@
 // into its own 128-column TMEM slot (four slots rotate); eight epilogue warps drain a slot, convert
 // the exact int32 block sums to fp32, scale by d_w * d_a and accumulate in registers in block order.
 //
-// Warp roles: warps 0-3 = activation TMA (0), weight TMA (1), MMA issue + TMEM owner (2), idle (3);
-// warps 4-11 = epilogue (two warps per TMEM lane quarter, 64 columns each); warps 12.. = quantizers
+// Warp roles: warps 0-2 = activation TMA (0), weight TMA (1), MMA issue + TMEM owner (2);
+// warps 3-18 = epilogue (four warps per TMEM lane quarter, 32 columns each); warps 19.. = quantizers
 // (groups of four warps, one thread per token row, groups take quant blocks round-robin).
 #include <cuda_fp16.h>
 
@@ -22,11 +22,40 @@ namespace ppml_b200 {
 
 namespace {
 
+// Optional wait profiling (build with -DPPML_Q8_TRACE): CTA 0 adds the cycles each role spends in each
+// wait site to a global table; off in normal builds.
+#ifdef PPML_Q8_TRACE
+__device__ long long g_q8_trace[64];
+#define Q8_WAIT(slot, ...)                                                     \
+    [&]() {                                                                    \
+        const long long t0__ = clock64();                                      \
+        const bool r__ = mbar_wait(__VA_ARGS__);                               \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                      \
+            atomicAdd(reinterpret_cast<unsigned long long*>(&g_q8_trace[slot]), (unsigned long long)(clock64() - t0__)); \
+            atomicAdd(reinterpret_cast<unsigned long long*>(&g_q8_trace[32 + slot]), 1ull); }                         \
+        return r__;                                                            \
+    }()
+#define Q8_WAIT_RELAXED(slot, ...) Q8_WAIT(slot, __VA_ARGS__)
+#define Q8_WAIT_WARP(slot, ...) Q8_WAIT(slot, __VA_ARGS__)
+#define Q8_T0() const long long tq0__ = clock64()
+#define Q8_T1(slot) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                       \
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_q8_trace[slot]), (unsigned long long)(clock64() - tq0__)); \
+        atomicAdd(reinterpret_cast<unsigned long long*>(&g_q8_trace[32 + slot]), 1ull); } } while (0)
+#else
+#define Q8_WAIT(slot, ...) mbar_wait(__VA_ARGS__)
+#define Q8_WAIT_RELAXED(slot, ...) mbar_wait_relaxed(__VA_ARGS__)
+#define Q8_WAIT_WARP(slot, ...) mbar_wait(__VA_ARGS__)
+#define Q8_T0() do {} while (0)
+#define Q8_T1(slot) do {} while (0)
+#endif
+
 constexpr int kTile = 128 * 128;          // bytes: one int8 A tile (128 rows x 128 K) == one weight stage == one raw fp32 stage
 constexpr int kMaxKT = 8;                 // K <= 1024
 constexpr int kMaxStages = 6;
 constexpr int kQuantGroups = 1;          // groups of four quantizer warps, taking quant blocks round-robin
-constexpr int kThreads = 32 * (12 + 4 * kQuantGroups);
+constexpr int kEpiWarps = 16;             // four per TMEM lane quarter, 32 output columns each
+constexpr int kMiscWarps = 3;             // activation TMA, weight TMA, MMA issue
+constexpr int kThreads = 32 * (kMiscWarps + kEpiWarps + 4 * kQuantGroups);
 
 struct Q8Params {
     int Mout, Ntok, K, nblk, KT;
@@ -97,9 +126,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             mbar_init(a_full(k), nb > 0 ? 4 * nb : 1);
             mbar_init(a_empty(k), 1);
         }
-        for (int s = 0; s < 4; ++s) { mbar_init(t_full(s), 1); mbar_init(t_empty(s), 8); }
-        mbar_init(epi_done(0), 8); mbar_init(epi_done(1), 8);
-        mbar_init(dw_full, 8); mbar_init(dw_free, 8);
+        for (int s = 0; s < 4; ++s) { mbar_init(t_full(s), 1); mbar_init(t_empty(s), kEpiWarps); }
+        mbar_init(epi_done(0), kEpiWarps); mbar_init(epi_done(1), kEpiWarps);
+        mbar_init(dw_full, kEpiWarps); mbar_init(dw_free, kEpiWarps);
         *cta_abort = 0;
         fence_barrier_init();
     }
@@ -112,6 +141,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
 
     const int total_items = p.m_tiles * p.groups;
+#ifdef PPML_Q8_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_q8_trace[30] = clock64();
+#endif
 
     if (warp == 0) {
         // ---------------- activation TMA: one 128 x 32 fp32 box per quant block -----------------
@@ -121,7 +153,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 const int mt = item / p.groups;
                 for (int kb = 0; kb < p.nblk; ++kb, ++cnt) {
                     const int s = cnt % p.RS; const uint32_t ph = (cnt / p.RS) & 1u;
-                    if (!mbar_wait(raw_empty(s), ph ^ 1u, cta_abort, p.err, 0x1101)) { ok = false; break; }
+                    if (!Q8_WAIT_RELAXED(0, raw_empty(s), ph ^ 1u, cta_abort, p.err, 0x1101)) { ok = false; break; }
                     mbar_arrive_expect_tx(raw_full(s), kTile);
                     tma_load_3d(smem_base + L.raw_off + s * kTile, &tmX, raw_full(s), kb * 32, mt * 128, 0);
                 }
@@ -139,7 +171,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 for (int nb = nb0; nb < nb1 && ok; ++nb) {
                     for (int ks = 0; ks < p.KT; ++ks, ++cnt) {
                         const int s = cnt % p.BS; const uint32_t ph = (cnt / p.BS) & 1u;
-                        if (!mbar_wait(w_empty(s), ph ^ 1u, cta_abort, p.err, 0x1201)) { ok = false; break; }
+                        if (!Q8_WAIT_RELAXED(1, w_empty(s), ph ^ 1u, cta_abort, p.err, 0x1201)) { ok = false; break; }
                         mbar_arrive_expect_tx(w_full(s), kTile);
                         tma_load_3d(smem_base + L.w_off + s * kTile, &tmW, w_full(s), ks * 128, nb * 128, 0);
                     }
@@ -159,19 +191,21 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 for (int nb = nb0; nb < nb1 && ok; ++nb) {
                     for (int ks = 0; ks < p.KT && ok; ++ks, ++wcnt) {
                         if (nb == nb0) {
-                            if (!mbar_wait(a_full(ks), n_it & 1u, cta_abort, p.err, 0x1301)) { ok = false; break; }
+                            if (!Q8_WAIT(2, a_full(ks), n_it & 1u, cta_abort, p.err, 0x1301)) { ok = false; break; }
                         }
                         const int s = wcnt % p.BS; const uint32_t ph = (wcnt / p.BS) & 1u;
-                        if (!mbar_wait(w_full(s), ph, cta_abort, p.err, 0x1302)) { ok = false; break; }
+                        if (!Q8_WAIT(3, w_full(s), ph, cta_abort, p.err, 0x1302)) { ok = false; break; }
                         tc_fence_after();
                         const uint64_t da = make_smem_desc(smem_base + L.a_off + ks * kTile, 16, 1024, kLayoutSW128);
                         const uint64_t db = make_smem_desc(smem_base + L.w_off + s * kTile, 16, 1024, kLayoutSW128);
                         const int nblk_step = min(4, p.nblk - 4 * ks);
                         for (int j = 0; j < nblk_step; ++j, ++bcnt) {
                             const int slot = bcnt & 3; const uint32_t tph = (bcnt >> 2) & 1u;
-                            if (!mbar_wait(t_empty(slot), tph ^ 1u, cta_abort, p.err, 0x1303)) { ok = false; break; }
+                            // the epilogue re-arms a slot with the integer whose bit pattern is the float
+                            // 1.5 * 2^23; accumulating the block sum onto it yields that float plus the sum
+                            if (!Q8_WAIT(4, t_empty(slot), tph, cta_abort, p.err, 0x1303)) { ok = false; break; }
                             tc_fence_after();
-                            umma<MmaKind::I8>(tmem_base + slot * 128, da + 2u * j, db + 2u * j, idesc, 0u);
+                            umma<MmaKind::I8>(tmem_base + slot * 128, da + 2u * j, db + 2u * j, idesc, 1u);
                             umma_commit(t_full(slot));
                         }
                         if (!ok) break;
@@ -182,15 +216,22 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
         }
         __syncwarp();
-    } else if (warp == 3) {
-        // idle warp of warpgroup 0
-    } else if (warp < 12) {
+    } else if (warp < kMiscWarps + kEpiWarps) {
         // ---------------- epilogue: per-block rescale, fp32 accumulation in registers -------------
         const int q = warp & 3;                       // TMEM lane quarter
-        const int half = (warp - 4) >> 2;             // which 64 of the 128 columns
-        const int etid = threadIdx.x - 4 * 32;        // 0..255
+        const int cg = (warp - kMiscWarps) >> 2;      // which 32 of the 128 columns
+        const int etid = threadIdx.x - kMiscWarps * 32;   // 0..511
         const int row = q * 32 + lane;                // token row inside the tile
         uint32_t bcnt = 0, n_it = 0, nbcnt = 0; bool ok = true;
+        constexpr uint32_t kMagicBits = 0x4B400000u;   // 1.5 * 2^23 as a float; as an integer it is the slot bias
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) {
+            tmem_st32_fill(tmem_base + sl * 128 + cg * 32 + (static_cast<uint32_t>(q * 32) << 16), kMagicBits);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { for (int sl = 0; sl < 4; ++sl) mbar_arrive(t_empty(sl)); }
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
             const int mt = item / p.groups, g = item % p.groups;
             const int nb0 = g * p.blocks_per_group;
@@ -200,109 +241,136 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             for (int nb = nb0; nb < nb1 && ok; ++nb, ++nbcnt) {
                 // stage this column block's weight scales as fp32 [nblk][128]: wait until every
                 // epilogue warp has finished with the previous table, fill, publish
-                if (!mbar_wait(dw_free, (nbcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
-                for (int i = etid; i < p.nblk * 128; i += 256) {
+                if (!Q8_WAIT_WARP(6, dw_free, (nbcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
+                for (int i = etid; i < p.nblk * 128; i += 32 * kEpiWarps) {
                     const int kb = i >> 7, col = i & 127;
                     const int mo = nb * 128 + col;
                     dw_s[i] = (mo < p.Mout) ? __half2float(p.Wd[static_cast<size_t>(mo) * p.nblk + kb]) : 0.0f;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dw_full);
-                if (!mbar_wait(dw_full, nbcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
-                // 64 fp32 accumulators as 32 packed pairs
-                uint64_t acc2[32];
+                if (!Q8_WAIT_WARP(7, dw_full, nbcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
+                // 32 fp32 accumulators as 16 packed pairs
+                uint64_t acc2[16];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) acc2[j] = 0ull;
+                for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
+                const uint64_t neg_magic2 = pack2(-12582912.0f, -12582912.0f);
                 for (int kb = 0; kb < p.nblk; ++kb, ++bcnt) {
                     const int slot = bcnt & 3; const uint32_t tph = (bcnt >> 2) & 1u;
-                    if (!mbar_wait(t_full(slot), tph, cta_abort, p.err, 0x1401)) { ok = false; break; }
+                    if (!Q8_WAIT_WARP(5, t_full(slot), tph, cta_abort, p.err, 0x1401)) { ok = false; break; }
                     tc_fence_after();
                     const float da = __half2float(da_row[kb * 128]);
-                    const uint64_t da2 = pack2(da, da);
-                    const uint64_t neg_magic2 = pack2(-12582912.0f, -12582912.0f);
-                    const ulonglong2* dwp = reinterpret_cast<const ulonglong2*>(dw_s + kb * 128 + half * 64);
+                    const uint32_t taddr = tmem_base + slot * 128 + cg * 32 + (static_cast<uint32_t>(q * 32) << 16);
+                    // two halves of 16 columns keep the live registers under the cap of this 23-warp CTA
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int h = 0; h < 2; ++h) {
                         uint32_t v[16];
-                        tmem_ld16(tmem_base + slot * 128 + half * 64 + c * 16 + (static_cast<uint32_t>(q * 32) << 16), v);
+                        { Q8_T0();
+                        tmem_ld16(taddr + h * 16, v);
                         tmem_ld_wait();
+                        if (h == 1) {
+                            tmem_st32_fill(taddr, kMagicBits);         // re-arm the slot for its next block
+                            tmem_st_wait();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(t_empty(slot));
+                        }
+                        Q8_T1(11); }
+                        Q8_T0();
+#ifndef PPML_Q8_SCALAR_MATH
+                        const uint64_t da2 = pack2(da, da);
+                        const ulonglong2* dwp = reinterpret_cast<const ulonglong2*>(dw_s + kb * 128 + cg * 32 + h * 16);
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
-                            // int32 -> fp32 without the conversion unit: |sum| < 2^22, so the integer added to the
-                            // bit pattern of 1.5 * 2^23 is exactly that float plus the sum
-                            const ulonglong2 w4 = dwp[c * 4 + j4];
-                            const uint64_t f01 = fadd2(pack2(__int_as_float(static_cast<int>(v[j4 * 4 + 0]) + 0x4B400000),
-                                                             __int_as_float(static_cast<int>(v[j4 * 4 + 1]) + 0x4B400000)), neg_magic2);
-                            const uint64_t f23 = fadd2(pack2(__int_as_float(static_cast<int>(v[j4 * 4 + 2]) + 0x4B400000),
-                                                             __int_as_float(static_cast<int>(v[j4 * 4 + 3]) + 0x4B400000)), neg_magic2);
-                            acc2[c * 8 + j4 * 2 + 0] = ffma2(f01, fmul2(w4.x, da2), acc2[c * 8 + j4 * 2 + 0]);
-                            acc2[c * 8 + j4 * 2 + 1] = ffma2(f23, fmul2(w4.y, da2), acc2[c * 8 + j4 * 2 + 1]);
+                            // int32 -> fp32 without the conversion unit: |sum| < 2^22 and the slot was biased by the
+                            // bit pattern of 1.5 * 2^23, so the word read back IS the float 1.5 * 2^23 + sum
+#ifdef PPML_Q8_EXP_NOLDS
+                            const ulonglong2 w4 = make_ulonglong2(neg_magic2, da2);
+#else
+                            const ulonglong2 w4 = dwp[j4];
+#endif
+                            const uint64_t f01 = fadd2(pack2(__uint_as_float(v[j4 * 4 + 0]), __uint_as_float(v[j4 * 4 + 1])), neg_magic2);
+                            const uint64_t f23 = fadd2(pack2(__uint_as_float(v[j4 * 4 + 2]), __uint_as_float(v[j4 * 4 + 3])), neg_magic2);
+                            acc2[h * 8 + j4 * 2 + 0] = ffma2(f01, fmul2(w4.x, da2), acc2[h * 8 + j4 * 2 + 0]);
+                            acc2[h * 8 + j4 * 2 + 1] = ffma2(f23, fmul2(w4.y, da2), acc2[h * 8 + j4 * 2 + 1]);
                         }
+#else
+                        const float4* dwp = reinterpret_cast<const float4*>(dw_s + kb * 128 + cg * 32 + h * 16);
+                        float* accf = reinterpret_cast<float*>(acc2);
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4) {
+                            const float4 w4 = dwp[j4];
+                            accf[h * 16 + j4 * 4 + 0] = fmaf(__uint_as_float(v[j4 * 4 + 0]) - 12582912.0f, w4.x * da, accf[h * 16 + j4 * 4 + 0]);
+                            accf[h * 16 + j4 * 4 + 1] = fmaf(__uint_as_float(v[j4 * 4 + 1]) - 12582912.0f, w4.y * da, accf[h * 16 + j4 * 4 + 1]);
+                            accf[h * 16 + j4 * 4 + 2] = fmaf(__uint_as_float(v[j4 * 4 + 2]) - 12582912.0f, w4.z * da, accf[h * 16 + j4 * 4 + 2]);
+                            accf[h * 16 + j4 * 4 + 3] = fmaf(__uint_as_float(v[j4 * 4 + 3]) - 12582912.0f, w4.w * da, accf[h * 16 + j4 * 4 + 3]);
+                        }
+#endif
+                        Q8_T1(12);
                         if (p.sumi_out != nullptr && tok < p.Ntok) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
-                                const int mo = nb * 128 + half * 64 + c * 16 + j;
+                                const int mo = nb * 128 + cg * 32 + h * 16 + j;
                                 if (mo < p.Mout)
-                                    p.sumi_out[(static_cast<size_t>(tok) * p.Mout + mo) * p.nblk + kb] = static_cast<int>(v[j]);
+                                    p.sumi_out[(static_cast<size_t>(tok) * p.Mout + mo) * p.nblk + kb] = static_cast<int>(v[j] - kMagicBits);
                             }
                         }
                     }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(t_empty(slot));
                 }
-                float acc[64];
+                float acc[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
+                for (int j = 0; j < 16; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
                 if (!ok) break;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dw_free);
+                Q8_T0();
                 if (tok < p.Ntok) {
-                    const int mo0 = nb * 128 + half * 64;
+                    const int mo0 = nb * 128 + cg * 32;
                     if (p.bias != nullptr) {
 #pragma unroll
-                        for (int j = 0; j < 64; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
+                        for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
                     }
                     if (p.c_trans) {
                         float* dst = p.C + static_cast<size_t>(tok) * p.Mout + mo0;
-                        if (p.vec_ok && mo0 + 64 <= p.Mout) {
+                        if (p.vec_ok && mo0 + 32 <= p.Mout) {
 #pragma unroll
-                            for (int j = 0; j < 64; j += 4)
+                            for (int j = 0; j < 32; j += 4)
                                 *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 64; ++j) if (mo0 + j < p.Mout) dst[j] = acc[j];
+                            for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) dst[j] = acc[j];
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 64; ++j)
+                        for (int j = 0; j < 32; ++j)
                             if (mo0 + j < p.Mout) p.C[static_cast<size_t>(mo0 + j) * p.Ntok + tok] = acc[j];
                     }
                 }
+                Q8_T1(13);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(epi_done(n_it & 1));
         }
     } else {
         // ---------------- quantizers: one thread per token row, two groups on alternate blocks ----------
-        const int qg = (warp - 12) >> 2;              // quantizer group
-        const int row = ((warp - 12) & 3) * 32 + lane;
+        const int qg = (warp - kMiscWarps - kEpiWarps) >> 2;   // quantizer group
+        const int row = ((warp - kMiscWarps - kEpiWarps) & 3) * 32 + lane;
         uint32_t base_cnt = 0, n_it = 0; bool ok = true;
         const uint64_t half2c = pack2(0.5f, 0.5f), big2 = pack2(8388608.0f, 8388608.0f);
         const uint64_t nbig2 = pack2(-8388608.0f, -8388608.0f), magic2 = pack2(12582912.0f, 12582912.0f);
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it, base_cnt += p.nblk) {
             if (n_it >= 2) {
-                if (!mbar_wait(epi_done(n_it & 1), ((n_it >> 1) - 1) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
+                if (!Q8_WAIT_WARP(8, epi_done(n_it & 1), ((n_it >> 1) - 1) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
             }
             __half* da_w = da_s + (n_it & 1) * p.nblk * 128 + row;
             for (int kb = qg; kb < p.nblk; kb += kQuantGroups) {
                 const uint32_t cnt = base_cnt + kb;
                 const int ks = kb >> 2;
                 if ((kb & 3) < kQuantGroups) {       // this group's first block of the K step
-                    if (!mbar_wait(a_empty(ks), (n_it & 1u) ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
+                    if (!Q8_WAIT_WARP(9, a_empty(ks), (n_it & 1u) ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
                 }
                 const int s = cnt % p.RS; const uint32_t ph = (cnt / p.RS) & 1u;
-                if (!mbar_wait(raw_full(s), ph, cta_abort, p.err, 0x1503)) { ok = false; break; }
+                if (!Q8_WAIT_WARP(10, raw_full(s), ph, cta_abort, p.err, 0x1503)) { ok = false; break; }
                 const uint8_t* raw = sg + L.raw_off + s * kTile;
                 float x[32];
 #pragma unroll
@@ -359,12 +427,24 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
     }
 
+#ifdef PPML_Q8_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_q8_trace[31] = clock64();
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 }  // namespace
+
+#ifdef PPML_Q8_TRACE
+extern "C" int ppml_b200_q8_trace_read(long long* out64, int reset) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out64, g_q8_trace, sizeof(long long) * 64) != cudaSuccess) return 1;
+    if (reset) { long long z[64] = {0}; cudaMemcpyToSymbol(g_q8_trace, z, sizeof(z)); }
+    return 0;
+}
+#endif
 
 // W: Q8_0R weights ([Mout*nblk*32] int8 plane followed by [Mout*nblk] half scales); X fp32 [Ntok][K];
 // M = weight rows (out features), N = tokens, as in the reference's launcher.
