@@ -6,7 +6,8 @@
  * stream (stream = NULL: the legacy default stream, which is what the reference's CUDABackend
  * uses) and returns a status code: 0 = launched; 1 = bad arguments / unsupported; 2 = K not a
  * multiple of 32 (Q8); 3 = scratch allocation failed; 4 = quantize launch failed; 5 = unknown
- * weight type; 6 = kernel launch failed; 7 = the requested kernel family cannot take this shape.
+ * weight type; 6 = kernel launch failed; 7 = the requested kernel family cannot take this shape;
+ * 9 = the problem exceeds a fixed capacity (only ppml_b200_mul_mat_q8_noalloc).
  * Buffers stay owned by the caller; nothing is retained after the call returns.
  *
  * Each declaration names the reference interface it stands in for (path inside the reference
@@ -76,6 +77,19 @@ int ppml_b200_cast_f32_to_bf16(const float* x, void* y, int64_t n, void* stream)
  * sumi_out (may be NULL) receives the exact int32 block sums as [N][M][K/32]. */
 int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, int K, int wtype, int c_trans,
                          const float* bias, int32_t* sumi_out, int path, int* path_out, void* stream);
+
+/* Q8 mul_mat that never allocates device memory.  It has no counterpart in the reference (whose launcher
+ * grows a cudaMalloc'ed scratch, src/cuda/MulMatQ8Kernel.cu:430-449).  For callers that cannot allocate
+ * at call time -- inside an executor whose arena was planned up front, under a fixed memory budget, or
+ * when another allocator owns all free device memory.  Same arguments and result as
+ * ppml_b200_mul_mat_q8 on its CUDA-core path (dp4a), bias included; the quantized activations go through
+ * a fixed 4 MiB array inside the library image (held by every GPU that loads the library), so
+ * N * (K / 32) * 36 bytes must fit: otherwise status 9 and a message on stderr.  All calls share that
+ * array: issue them on one stream, overlapping calls race.  The first call on a device looks up the
+ * array's address and should be made before any stream capture on that device. */
+#define PPML_B200_NOALLOC_SCRATCH_BYTES (4u << 20)
+int ppml_b200_mul_mat_q8_noalloc(const void* W, const float* X, float* C, int M, int N, int K, int wtype,
+                                 int c_trans, const float* bias, void* stream);
 
 /* Replace quantize_rows_q8_1_cuda / dequantize_q8_0_cuda / dequantize_q8_1_cuda
  * (src/backend/CUDAKernels.cpp:164-166; src/cuda/QuantKernels.cu:86-109).  ne = element count. */

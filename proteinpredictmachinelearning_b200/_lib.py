@@ -8,6 +8,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libppml_b200.so")
 
 PATH_AUTO, PATH_SIMT, PATH_UMMA = 0, 1, 2
 TF32_ROUND, TF32_TMA, TF32_TRUNCATE = 0, 1, 2
+NOALLOC_SCRATCH_BYTES = 4 << 20      # PPML_B200_NOALLOC_SCRATCH_BYTES
 
 
 class FlashCfg(C.Structure):
@@ -28,6 +29,7 @@ SIGNATURES = {
     "ppml_b200_cast_f32_to_f16": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_cast_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_mul_mat_q8": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, C.POINTER(_i), _vp]),
+    "ppml_b200_mul_mat_q8_noalloc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "ppml_b200_quantize_rows_q8_1": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_dequantize_q8_0": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_dequantize_q8_1": (_i, [_vp, _vp, _i64, _vp]),

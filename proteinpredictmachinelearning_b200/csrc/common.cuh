@@ -13,7 +13,7 @@ namespace ppml_b200 {
 // 3 scratch alloc, 4 quantize launch, 5 weight type, 6 kernel launch.
 // ---------------------------------------------------------------------------------------------
 enum : int { ST_OK = 0, ST_BAD_ARGS = 1, ST_BAD_K = 2, ST_SCRATCH = 3, ST_QUANT = 4, ST_WTYPE = 5,
-             ST_LAUNCH = 6, ST_UNSUPPORTED_PATH = 7, ST_DEVICE_ABORT = 8 };
+             ST_LAUNCH = 6, ST_UNSUPPORTED_PATH = 7, ST_DEVICE_ABORT = 8, ST_TOO_LARGE = 9 };
 
 // Device error word: a kernel whose bounded wait ran out stores a non-zero code there and leaves
 // early; ppml_b200_device_status() reads it.  Layout: [0] code, [1] where (role << 8 | site).

@@ -122,6 +122,18 @@ def mul_mat_q8_cuda(W, X, M, wtype=2, c_trans=1, bias=None, path=PATH_AUTO, want
     return (Cout, taken.value, sumi) if want_sumi else (Cout, taken.value)
 
 
+def mul_mat_q8_noalloc(W, X, M, wtype=2, c_trans=1, bias=None, out=None):
+    """Same product as mul_mat_q8_cuda(path=PATH_SIMT), for callers that must not allocate device memory:
+    the quantized activations use a fixed 4 MiB array inside the library.  Raises (status 9) when
+    N * (K / 32) * 36 bytes do not fit.  `out` lets the caller pass its own result buffer."""
+    X = _f32c(X)
+    N, K = X.shape
+    Cout = out if out is not None else torch.empty((N, M) if c_trans else (M, N), device=X.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_mul_mat_q8_noalloc(_p(W), _p(X), _p(Cout), M, N, K, wtype, c_trans, _p(bias), _stream())
+    _check(rc, "mul_mat_q8_noalloc")
+    return Cout
+
+
 def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-9, bias_bcast=False, path=PATH_AUTO):
     """Q [B,h,L,d], K/V [B,h,Lk,d], bias [B,h,L,Lk] (or [h,L,Lk] shared over B with bias_bcast).
     Returns (O, LSE).  Lk != L and bias_bcast go through the extended entry."""
