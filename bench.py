@@ -199,6 +199,9 @@ def run_ours(args):
     Wf = {(k, n): torch.randn((n, k), device=dev, generator=g) * 0.02 for (k, n) in sorted({(s[1], s[2]) for s in sh})}
     W = {kn: ops.quantize_q8_0r(w) for kn, w in Wf.items()}
     Cout = {(m, n): torch.empty((m, n), device=dev) for (m, n) in sorted({(s[0], s[2]) for s in sh})}
+    if args.kernel == "bf16":
+        X16 = {key: t.bfloat16() for key, t in X.items()}
+        W16 = {key: t.bfloat16() for key, t in Wf.items()}
     step_flops = sum(q8_flops(*s) for s in sh)
     step_bytes = sum(q8_bytes(*s) for s in sh)
 
@@ -208,7 +211,14 @@ def run_ours(args):
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            _, taken = ops.mul_mat_q8_cuda(W[(k, n)], X[(m, k)], n, wtype=2, c_trans=1, path=PATH_AUTO, out=Cout[(m, n)])
+            if args.kernel == "q8":
+                _, taken = ops.mul_mat_q8_cuda(W[(k, n)], X[(m, k)], n, wtype=2, c_trans=1, path=PATH_AUTO, out=Cout[(m, n)])
+            elif args.kernel == "tf32":
+                ops.mul_mat_cuda(X[(m, k)], Wf[(k, n)], path=PATH_AUTO, tf32_mode=1, out=Cout[(m, n)])
+                taken = 1
+            else:
+                ops.mul_mat_16(X16[(m, k)], W16[(k, n)], path=PATH_AUTO, out=Cout[(m, n)])
+                taken = 1
             if events is not None:
                 e1.record()
                 events.append(((m, k, n), taken, e0, e1))
@@ -341,6 +351,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="stop after the device-resident region (profiling runs)")
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs)")
+    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16"],
+                    help="profiling runs with --no-e2e: time the fp32 (tf32 tensor-core) or bf16 mul_mat on the same shapes")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
