@@ -63,6 +63,8 @@ struct Q8Params {
     int n_blocks;              // weight column blocks of 128
     int groups, blocks_per_group;
     int RS, BS;                // ring depths
+    int dw_tabs;               // scale tables held in smem: n_blocks (all resident, filled once) or 1 (refilled per column block)
+    int staged;                // 1: results leave through per-warp transposition buffers (row-contiguous stores)
     const __half* Wd;          // weight scales [Mout][nblk]
     float* C;
     const float* bias;
@@ -73,17 +75,21 @@ struct Q8Params {
 };
 
 struct SmemLayout {
-    uint32_t a_off, raw_off, w_off, dw_off, da_off, bar_off, total;
+    uint32_t a_off, raw_off, w_off, dw_off, da_off, st_off, bar_off, total;
 };
 
-__host__ __device__ inline SmemLayout q8_layout(int KT, int nblk, int RS, int BS) {
+constexpr int kStorePitch = 144;                    // bytes per staged row: 32 floats + 16 bytes of padding
+constexpr int kStoreBytes = 32 * kStorePitch;       // one epilogue warp's 32 x 32 transposition buffer
+
+__host__ __device__ inline SmemLayout q8_layout(int KT, int nblk, int RS, int BS, int dw_tabs, int staged) {
     SmemLayout L;
     L.a_off = 0;
     L.raw_off = L.a_off + KT * kTile;
     L.w_off = L.raw_off + RS * kTile;
-    L.dw_off = L.w_off + BS * kTile;                 // float [nblk][128]
-    L.da_off = L.dw_off + nblk * 128 * 4;            // half  [2][nblk][128]
-    L.bar_off = L.da_off + 2 * nblk * 128 * 2;
+    L.dw_off = L.w_off + BS * kTile;                 // float [dw_tabs][nblk][128]
+    L.da_off = L.dw_off + dw_tabs * nblk * 128 * 4;  // half  [2][nblk][128]
+    L.st_off = L.da_off + 2 * nblk * 128 * 2;        // staged stores: 16 x kStoreBytes
+    L.bar_off = L.st_off + (staged ? 16 * kStoreBytes : 0);
     L.bar_off = (L.bar_off + 15u) & ~15u;
     L.total = L.bar_off + 8 * (4 * kMaxStages + 2 * kMaxKT + 8 + 4) + 16;
     return L;
@@ -94,7 +100,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* sg = smem_raw + (smem_base - smem_u32(smem_raw));
-    const SmemLayout L = q8_layout(p.KT, p.nblk, p.RS, p.BS);
+    const SmemLayout L = q8_layout(p.KT, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged);
     const uint32_t bar0 = smem_base + L.bar_off;
     auto raw_full = [&](int s) { return bar0 + 8u * s; };
     auto raw_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
@@ -222,7 +228,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const int cg = (warp - kMiscWarps) >> 2;      // which 32 of the 128 columns
         const int etid = threadIdx.x - kMiscWarps * 32;   // 0..511
         const int row = q * 32 + lane;                // token row inside the tile
-        uint32_t bcnt = 0, n_it = 0, nbcnt = 0; bool ok = true;
+        uint32_t bcnt = 0, n_it = 0, dwcnt = 0; bool ok = true;
+        const bool dw_resident = p.dw_tabs == p.n_blocks;    // (one column block in all: trivially resident)
         constexpr uint32_t kMagicBits = 0x4B400000u;   // 1.5 * 2^23 as a float; as an integer it is the slot bias
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
@@ -232,24 +239,39 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         if (lane == 0) { for (int sl = 0; sl < 4; ++sl) mbar_arrive(t_empty(sl)); }
+        if (dw_resident) {
+            for (int i = etid; i < p.n_blocks * p.nblk * 128; i += 32 * kEpiWarps) {
+                const int nbq = i / (p.nblk * 128), r = i - nbq * p.nblk * 128;
+                const int kb = r >> 7, col = r & 127;
+                const int mo = nbq * 128 + col;
+                dw_s[i] = (mo < p.Mout) ? __half2float(p.Wd[static_cast<size_t>(mo) * p.nblk + kb]) : 0.0f;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dw_full);
+            if (!Q8_WAIT_WARP(7, dw_full, 0u, cta_abort, p.err, 0x1404)) ok = false;
+        }
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
             const int mt = item / p.groups, g = item % p.groups;
             const int nb0 = g * p.blocks_per_group;
             const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
             const int tok = mt * 128 + row;
             const __half* da_row = da_s + (n_it & 1) * p.nblk * 128 + row;
-            for (int nb = nb0; nb < nb1 && ok; ++nb, ++nbcnt) {
-                // stage this column block's weight scales as fp32 [nblk][128]: wait until every
-                // epilogue warp has finished with the previous table, fill, publish
-                if (!Q8_WAIT_WARP(6, dw_free, (nbcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
-                for (int i = etid; i < p.nblk * 128; i += 32 * kEpiWarps) {
-                    const int kb = i >> 7, col = i & 127;
-                    const int mo = nb * 128 + col;
-                    dw_s[i] = (mo < p.Mout) ? __half2float(p.Wd[static_cast<size_t>(mo) * p.nblk + kb]) : 0.0f;
+            for (int nb = nb0; nb < nb1 && ok; ++nb) {
+                // weight scales as fp32 [nblk][128] per column block.  When the tables of all column blocks fit
+                // they were staged once before the first item; otherwise this block's table is refilled here:
+                // wait until every epilogue warp has finished with the previous one, fill, publish.
+                const float* dw_tab = dw_s + (p.dw_tabs > 1 ? nb : 0) * p.nblk * 128;
+                if (!dw_resident) {
+                    if (!Q8_WAIT_WARP(6, dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
+                    for (int i = etid; i < p.nblk * 128; i += 32 * kEpiWarps) {
+                        const int kb = i >> 7, col = i & 127;
+                        const int mo = nb * 128 + col;
+                        dw_s[i] = (mo < p.Mout) ? __half2float(p.Wd[static_cast<size_t>(mo) * p.nblk + kb]) : 0.0f;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(dw_full);
+                    if (!Q8_WAIT_WARP(7, dw_full, dwcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dw_full);
-                if (!Q8_WAIT_WARP(7, dw_full, nbcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
                 // 32 fp32 accumulators as 16 packed pairs
                 uint64_t acc2[16];
 #pragma unroll
@@ -279,7 +301,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                         Q8_T0();
 #ifndef PPML_Q8_SCALAR_MATH
                         const uint64_t da2 = pack2(da, da);
-                        const ulonglong2* dwp = reinterpret_cast<const ulonglong2*>(dw_s + kb * 128 + cg * 32 + h * 16);
+                        const ulonglong2* dwp = reinterpret_cast<const ulonglong2*>(dw_tab + kb * 128 + cg * 32 + h * 16);
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
                             // int32 -> fp32 without the conversion unit: |sum| < 2^22 and the slot was biased by the
@@ -295,7 +317,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             acc2[h * 8 + j4 * 2 + 1] = ffma2(f23, fmul2(w4.y, da2), acc2[h * 8 + j4 * 2 + 1]);
                         }
 #else
-                        const float4* dwp = reinterpret_cast<const float4*>(dw_s + kb * 128 + cg * 32 + h * 16);
+                        const float4* dwp = reinterpret_cast<const float4*>(dw_tab + kb * 128 + cg * 32 + h * 16);
                         float* accf = reinterpret_cast<float*>(acc2);
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
@@ -321,10 +343,34 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
                 for (int j = 0; j < 16; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
                 if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dw_free);
+                if (!dw_resident) { __syncwarp(); if (lane == 0) mbar_arrive(dw_free); ++dwcnt; }
                 Q8_T0();
-                if (tok < p.Ntok) {
+                if (p.c_trans && p.staged) {
+                    // row-contiguous stores: thread = row writes its 32 values into the warp's padded buffer,
+                    // then eight lanes cover one 128-byte row segment, four rows per store instruction
+                    const int mo0 = nb * 128 + cg * 32;
+                    uint8_t* stage = sg + L.st_off + (warp - kMiscWarps) * kStoreBytes;
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(stage + lane * kStorePitch + j * 16) =
+                            make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+                    __syncwarp();
+                    const int cc = lane & 7;
+                    const int col = mo0 + cc * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = (lane >> 3) + 4 * i;
+                        const int trow = mt * 128 + q * 32 + rr;
+                        const float4 val = *reinterpret_cast<const float4*>(stage + rr * kStorePitch + cc * 16);
+                        if (trow < p.Ntok && col < p.Mout)      // staged mode requires Mout % 4 == 0
+                            *reinterpret_cast<float4*>(p.C + static_cast<size_t>(trow) * p.Mout + col) = val;
+                    }
+                    __syncwarp();
+                } else if (tok < p.Ntok) {
                     const int mo0 = nb * 128 + cg * 32;
                     if (p.bias != nullptr) {
 #pragma unroll
@@ -469,10 +515,19 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     }
     p.blocks_per_group = (p.n_blocks + groups - 1) / groups;
     p.groups = (p.n_blocks + p.blocks_per_group - 1) / p.blocks_per_group;
-    // ring depths from what the resident A tile and the scale tables leave
+    p.vec_ok = c_trans && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && (M % 4 == 0);
+    // Shared memory: the resident A tile and the activation-scale table are fixed; then, in this order of
+    // preference, the scale tables of all column blocks (no refill, at most 32 KB), the per-warp store
+    // buffers, and at least four ring stages; what is left goes to the rings.
     const int budget = 226 * 1024;
-    const int fixed = static_cast<int>(q8_layout(p.KT, p.nblk, 0, 0).total) + 1024;
-    int stages = (budget - fixed) / kTile;
+    p.dw_tabs = (p.n_blocks * p.nblk * 512 <= 32 * 1024) ? p.n_blocks : 1;
+    p.staged = p.vec_ok ? 1 : 0;
+    auto stages_for = [&](int tabs, int staged) {
+        return (budget - (static_cast<int>(q8_layout(p.KT, p.nblk, 0, 0, tabs, staged).total) + 1024)) / kTile;
+    };
+    if (stages_for(p.dw_tabs, p.staged) < 4 && p.dw_tabs > 1) p.dw_tabs = 1;
+    if (stages_for(p.dw_tabs, p.staged) < 4) p.staged = 0;
+    int stages = stages_for(p.dw_tabs, p.staged);
     if (stages < 3) return ST_UNSUPPORTED_PATH;
     if (stages > 2 * kMaxStages) stages = 2 * kMaxStages;
     p.RS = stages / 2; p.BS = stages - p.RS;
@@ -480,13 +535,12 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     if (p.BS > kMaxStages) p.BS = kMaxStages;
     const __half* Wd = reinterpret_cast<const __half*>(static_cast<const int8_t*>(W) + static_cast<size_t>(M) * p.nblk * 32);
     p.Wd = Wd; p.C = C; p.bias = bias; p.sumi_out = sumi_out; p.c_trans = c_trans; p.err = err;
-    p.vec_ok = c_trans && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && (M % 4 == 0);
 
     CUtensorMap tmX, tmW;
     if (!make_tmap_3d(&tmX, TmaType::F32, X, K, N, 1, static_cast<uint64_t>(K) * 4, 0, 32, 128, true)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, true)) return ST_UNSUPPORTED_PATH;
 
-    const int smem = static_cast<int>(q8_layout(p.KT, p.nblk, p.RS, p.BS).total) + 1024;
+    const int smem = static_cast<int>(q8_layout(p.KT, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total) + 1024;
     static int configured_smem[64] = {0};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured_smem[dev] < smem) {
