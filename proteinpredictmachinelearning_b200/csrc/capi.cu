@@ -158,7 +158,11 @@ int ppml_b200_flash_attn_forward_ex(const ppml_b200_flash_cfg* cfg, int Lk, int6
     if (!cfg || !Q || !K || !V || !O || !path_ok(path)) return ST_BAD_ARGS;
     if (cfg->B <= 0 || cfg->h <= 0 || cfg->L <= 0 || cfg->d <= 0 || Lk <= 0) return ST_BAD_ARGS;
     const float scale = (cfg->scale > 0.f) ? cfg->scale : 1.0f / std::sqrt(static_cast<float>(cfg->d));
-    if (path == PPML_B200_PATH_UMMA) return ST_UNSUPPORTED_PATH;
+    if (path != PPML_B200_PATH_SIMT) {
+        const int rc = launch_umma_attn(Q, K, V, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
+                                        cfg->softmax_eps, bias_batch_stride, as_stream(stream));
+        if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
+    }
     return launch_attn_rowwarp(Q, K, V, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
                                cfg->softmax_eps, bias_batch_stride, as_stream(stream));
 }

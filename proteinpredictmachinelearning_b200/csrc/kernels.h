@@ -55,6 +55,10 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st);
 int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
                    int* sumi_out, cudaStream_t st);
 
+int launch_umma_attn(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+                     int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
+                     long long bias_batch_stride, cudaStream_t st);
+
 int num_sms();
 
 }  // namespace ppml_b200

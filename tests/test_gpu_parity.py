@@ -219,12 +219,21 @@ def test_mul_mat_q8_full_size_property():
 # ------------------------------------------------------------------------------------------------
 def test_attention_golden(oracle):
     Q, K, V, bi = cases.attn_case(2, 3, 70, 32, seed=3)
-    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=1 / np.sqrt(32.0))
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=1 / np.sqrt(32.0), path=PATH_SIMT)
     assert cases.rel_err(host(O), GOLD["fa_O"]) <= TOL_FP32
     assert np.abs(host(LSE) - GOLD["fa_LSE"]).max() <= 1e-5
-    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None, causal=True)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None, causal=True, path=PATH_SIMT)
     assert cases.rel_err(host(O), GOLD["fa_causal_O"]) <= TOL_FP32
     assert np.abs(host(LSE) - GOLD["fa_causal_LSE"]).max() <= 1e-5
+    # tensor-core path (head dim 32, no bias so that Lk = 70 is admissible): tf32 tolerance
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None, causal=True, path=PATH_UMMA)
+    assert cases.rel_err(host(O), GOLD["fa_causal_O"]) <= TOL_TF32
+    assert np.abs(host(LSE) - GOLD["fa_causal_LSE"]).max() <= 2e-3
+    # with the bias the key count must be a multiple of 4 for the tensor-core path: AUTO takes the CUDA-core kernel
+    with pytest.raises(RuntimeError):
+        ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), path=PATH_UMMA)
+    O, _ = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=1 / np.sqrt(32.0), path=PATH_AUTO)
+    assert cases.rel_err(host(O), GOLD["fa_O"]) <= TOL_FP32
 
 
 @pytest.mark.parametrize("B,h,L,d,Lk,bias,bcast", [
@@ -238,12 +247,43 @@ def test_attention_golden(oracle):
 def test_attention_shapes(oracle, B, h, L, d, Lk, bias, bcast):
     Q, K, V, bi = cases.attn_case(B, h, L, d, Lk=Lk, seed=3, bias=bias, bias_bcast=bcast)
     scale = 1 / np.sqrt(32.0)
-    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None if bi is None else dev(bi), scale=scale, bias_bcast=bcast)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None if bi is None else dev(bi), scale=scale, bias_bcast=bcast,
+                                         path=PATH_SIMT)
     rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast)
     assert cases.rel_err(host(O), rO) <= TOL_FP32
     assert np.abs(host(LSE) - rL).max() <= 1e-5
     legacy = oracle.attention_legacy(Q, K, V, bi, scale, bias_bcast=bcast)   # ground truth when Lq != Lk
     assert cases.rel_err(host(O), legacy) <= TOL_FP32
+
+
+@pytest.mark.parametrize("B,h,L,Lk,bias,bcast,causal", [
+    (4, 8, 256, None, True, True, False),       # full-size rows, one bias shared by the batch
+    (3, 2, 256, None, True, False, False),      # full bias tensor
+    (2, 4, 51, None, False, False, False),      # dev size without bias (51 keys: zero-filled tail, masked)
+    (2, 2, 300, None, True, False, False),      # three key tiles: both S / O buffers are reused
+    (2, 3, 100, 76, True, False, False),        # Lq != Lk
+    (1, 2, 1, 40, False, False, False),         # one query over 40 keys (global column attention)
+    (2, 2, 200, None, False, False, True),      # causal
+])
+def test_attention_tensor_cores(oracle, B, h, L, Lk, bias, bcast, causal):
+    Q, K, V, bi = cases.attn_case(B, h, L, 32, Lk=Lk, seed=3, bias=bias, bias_bcast=bcast)
+    scale = 1 / np.sqrt(32.0)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None if bi is None else dev(bi), scale=scale, bias_bcast=bcast,
+                                         causal=causal, path=PATH_UMMA)
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast, causal=causal)
+    assert cases.rel_err(host(O), rO) <= TOL_TF32
+    assert np.abs(host(LSE) - rL).max() <= 2e-3
+    if not causal:
+        assert cases.rel_err(host(O), oracle.attention_legacy(Q, K, V, bi, scale, bias_bcast=bcast)) <= TOL_TF32
+
+
+def test_attention_tensor_cores_masked_rows():
+    Q, K, V, bi = cases.attn_case(1, 1, 8, 32, Lk=8, seed=7)
+    bi[0, 0, 2, :] = -np.inf                     # fully masked row
+    bi[0, 0, 5, :4] = -np.inf                    # partly masked row
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), path=PATH_UMMA)
+    O, LSE = host(O), host(LSE)
+    assert np.all(O[0, 0, 2] == 0) and LSE[0, 0, 2] == -np.inf and np.isfinite(O).all()
 
 
 def test_attention_fully_masked_row():
