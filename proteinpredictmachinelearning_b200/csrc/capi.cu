@@ -182,7 +182,21 @@ int ppml_b200_out_prod(const float* src0, const float* src1, float* dst,
     if (ne00 <= 0 || ne01 <= 0 || ne02 <= 0 || ne03 <= 0 || ne10 <= 0 || ne12 <= 0 || ne13 <= 0) return ST_BAD_ARGS;
     if (ne11 != ne01 || ne0 != ne00 || ne1 != ne10 || ne2 < ne02 || ne3 < ne03 || ne2 != ne12 || ne3 != ne13) return ST_BAD_ARGS;
     if (ne2 % ne02 || ne3 % ne03) return ST_BAD_ARGS;
-    if (path == PPML_B200_PATH_UMMA) return ST_UNSUPPORTED_PATH;
+    if (path != PPML_B200_PATH_SIMT) {
+        int rc = ST_UNSUPPORTED_PATH;
+        // dst[plane][i1][i0] = sum_k src1[plane][k][i1] * src0[plane][k][i0]: both operands have the row index
+        // contiguous; planes without broadcast only
+        if (ne02 == ne2 && ne03 == ne3 && ne2 * ne3 <= 0x7fffffff && ne00 <= 0x7fffffff && ne10 <= 0x7fffffff && ne01 <= 0x7fffffff) {
+            UmmaGemmArgs a{};
+            a.A = src1; a.B = src0; a.C = dst;
+            a.M = static_cast<int>(ne10); a.N = static_cast<int>(ne00); a.K = static_cast<int>(ne01);
+            a.batch = static_cast<int>(ne2 * ne3);
+            a.lda = ne10; a.ldb = ne00; a.a_batch = ne10 * ne11; a.b_batch = ne00 * ne01;
+            a.ldc = ne0; a.c_batch = ne0 * ne1; a.alpha = 1.0f; a.elem = 0; a.tf32_mode = PPML_B200_TF32_TMA; a.mn_major = 1;
+            rc = launch_umma_gemm(a, as_stream(stream));
+        }
+        if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
+    }
     SimtContract p{};
     p.M = ne00; p.N = ne10; p.K = ne01;
     p.a_sm = 1; p.a_sk = ne00; p.b_sn = 1; p.b_sk = ne10;
@@ -201,11 +215,13 @@ int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t
     cudaStream_t st = as_stream(stream);
     if (path != PPML_B200_PATH_SIMT) {
         int rc = ST_UNSUPPORTED_PATH;
-        if (outgoing && B == 1 && D <= 0x7fffffff && I <= 0x7fffffff && J <= 0x7fffffff && K <= 0x7fffffff) {
+        if (B == 1 && D <= 0x7fffffff && I <= 0x7fffffff && J <= 0x7fffffff && K <= 0x7fffffff) {
             UmmaGemmArgs a{};
             a.A = left; a.B = right; a.C = dst;
             a.M = static_cast<int>(I); a.N = static_cast<int>(J); a.K = static_cast<int>(K); a.batch = static_cast<int>(D);
-            a.lda = K; a.ldb = K; a.a_batch = I * K; a.b_batch = J * K; a.ldc = J; a.c_batch = I * J;
+            if (outgoing) { a.lda = K; a.ldb = K; }                    // left[d][i][k], right[d][j][k]
+            else { a.lda = I; a.ldb = J; a.mn_major = 1; }             // left[d][k][i], right[d][k][j]
+            a.a_batch = I * K; a.b_batch = J * K; a.ldc = J; a.c_batch = I * J;
             a.bias = nullptr; a.alpha = inv_L; a.clamp = 1; a.elem = 0; a.tf32_mode = PPML_B200_TF32_TMA;
             rc = launch_umma_gemm(a, st);
         }

@@ -49,6 +49,7 @@ struct UmmaGemmArgs {
     int opm_D, opm_L;                  // opm_L > 0: blocked outer-product-mean store
     int elem;                          // 0 fp32 (tf32 math), 1 fp16, 2 bf16
     int tf32_mode;                     // fp32 only: 0 round in smem (rna), 1 TMA tf32 type, 2 truncate
+    int mn_major;                      // 1: A[b][k][m], B[b][k][n] (row index contiguous; lda / ldb = k pitch), fp32 only
 };
 int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st);
 

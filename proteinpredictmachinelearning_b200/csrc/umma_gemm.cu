@@ -20,9 +20,9 @@ int num_sms() {
 
 namespace {
 
-template <MmaKind KIND, int BN, Epi EPI, bool CONVERT>
+template <MmaKind KIND, int BN, Epi EPI, bool CONVERT, bool MNMAJOR = false>
 int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, cudaStream_t st) {
-    auto kern = umma_gemm_kernel<KIND, BN, EPI, CONVERT>;
+    auto kern = umma_gemm_kernel<KIND, BN, EPI, CONVERT, MNMAJOR>;
     constexpr int smem = gemm_smem_bytes<BN>();
     static bool configured[64] = {false};
     int dev = 0;
@@ -53,6 +53,15 @@ int launch_bn(int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm
     }
 }
 
+int launch_bn_mn(int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+    switch (BN) {
+        case 32: return launch_one<MmaKind::TF32, 32, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+        case 64: return launch_one<MmaKind::TF32, 64, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+        case 128: return launch_one<MmaKind::TF32, 128, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+        default: return launch_one<MmaKind::TF32, 256, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+    }
+}
+
 int pick_bn(int N) {
     if (N <= 32) return 32;
     if (N <= 64) return 64;
@@ -74,6 +83,25 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st) {
 
     const int BN = pick_bn(a.N);
     const int bk = 128 / es;
+    if (a.mn_major) {
+        // A[b][k][m], B[b][k][n] with the row index contiguous: fp32 operands only (tf32 delivered by TMA)
+        if (a.elem != 0 || a.opm_L > 0) return ST_UNSUPPORTED_PATH;
+        CUtensorMap tmA, tmB;
+        const uint64_t a_bs = (a.batch > 1) ? static_cast<uint64_t>(a.a_batch) * 4 : 0;
+        const uint64_t b_bs = (a.batch > 1) ? static_cast<uint64_t>(a.b_batch) * 4 : 0;
+        if (!make_tmap_3d(&tmA, TmaType::TF32, a.A, a.M, a.K, a.batch, static_cast<uint64_t>(a.lda) * 4, a_bs, 32, 32, 2))
+            return ST_UNSUPPORTED_PATH;
+        if (!make_tmap_3d(&tmB, TmaType::TF32, a.B, a.N, a.K, a.batch, static_cast<uint64_t>(a.ldb) * 4, b_bs, 32, 32, 2))
+            return ST_UNSUPPORTED_PATH;
+        GemmParams p{};
+        p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+        p.k_steps = (a.K + 31) / 32;
+        p.C = a.C; p.ldc = a.ldc; p.c_batch = a.c_batch;
+        p.bias = a.bias; p.alpha = a.alpha; p.clamp = a.clamp;
+        p.err = err;
+        p.vec_ok = ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) && (a.ldc % 4 == 0) && (a.c_batch % 4 == 0) && (a.N % 4 == 0);
+        return launch_bn_mn(BN, tmA, tmB, p, st);
+    }
     TmaType tt = (a.elem == 0) ? (a.tf32_mode == 1 ? TmaType::TF32 : TmaType::F32)
                                : (a.elem == 1 ? TmaType::F16 : TmaType::BF16);
     CUtensorMap tmA, tmB;

@@ -58,7 +58,9 @@ __host__ __device__ constexpr int gemm_smem_bytes() {
            4 * (kEpiStageBytes + kEpiBiasBytes);
 }
 
-template <MmaKind KIND, int BN, Epi EPI, bool CONVERT>
+// MNMAJOR: both operands are stored with the row index (m or n) contiguous and K strided (A[b][k][m],
+// B[b][k][n]); the stage then holds boxes of 32 rows x 32 k in the 32-byte-chunk form of the 128-byte swizzle.
+template <MmaKind KIND, int BN, Epi EPI, bool CONVERT, bool MNMAJOR = false>
 __global__ void __launch_bounds__(CONVERT ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
@@ -123,8 +125,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, cta_abort, p.err, 0x101)) { ok = false; break; }
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
                     mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
-                    tma_load_3d(sa, &tmA, full_bar(s), ks * BK, mt * 128, b);
-                    tma_load_3d(sa + kGemmStageA, &tmB, full_bar(s), ks * BK, nt * BN, b);
+                    if constexpr (!MNMAJOR) {
+                        tma_load_3d(sa, &tmA, full_bar(s), ks * BK, mt * 128, b);
+                        tma_load_3d(sa + kGemmStageA, &tmB, full_bar(s), ks * BK, nt * BN, b);
+                    } else {
+                        // boxes of 32 rows (inner, contiguous) x 32 k: 4 KB each, row blocks 4 KB apart
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) tma_load_3d(sa + i * 4096, &tmA, full_bar(s), mt * 128 + i * 32, ks * 32, b);
+#pragma unroll
+                        for (int i = 0; i < BN / 32; ++i) tma_load_3d(sa + kGemmStageA + i * 4096, &tmB, full_bar(s), nt * BN + i * 32, ks * 32, b);
+                    }
                 }
             }
         }
@@ -134,7 +144,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             uint32_t idesc;
             if constexpr (KIND == MmaKind::I8) idesc = make_idesc(2, 1, 1, 0, 0, 128, BN);
-            else if constexpr (KIND == MmaKind::TF32) idesc = make_idesc(1, 2, 2, 0, 0, 128, BN);
+            else if constexpr (KIND == MmaKind::TF32) idesc = make_idesc(1, 2, 2, MNMAJOR ? 1 : 0, MNMAJOR ? 1 : 0, 128, BN);
             else idesc = make_idesc(1, p.ab_fmt, p.ab_fmt, 0, 0, 128, BN);
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
@@ -150,12 +160,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     if (!mbar_wait(CONVERT ? conv_bar(s) : full_bar(s), ph, cta_abort, p.err, 0x202)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
-                    const uint64_t da = make_smem_desc(sa, 16, 1024, kLayoutSW128);
-                    const uint64_t db = make_smem_desc(sa + kGemmStageA, 16, 1024, kLayoutSW128);
+                    if constexpr (!MNMAJOR) {
+                        const uint64_t da = make_smem_desc(sa, 16, 1024, kLayoutSW128);
+                        const uint64_t db = make_smem_desc(sa + kGemmStageA, 16, 1024, kLayoutSW128);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        // 32 bytes of K per instruction: advance the start address by 2 x 16 bytes
-                        umma<KIND>(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < 4; ++kk) {
+                            // 32 bytes of K per instruction: advance the start address by 2 x 16 bytes
+                            umma<KIND>(d_tmem, da + 2u * kk, db + 2u * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                        }
+                    } else {
+                        // 32-bit operands with the row index contiguous: 128-byte swizzle over 32-byte chunks, whose
+                        // atom is 4 k x 128 bytes.  Row blocks (32 rows) are 4096 bytes apart (leading offset),
+                        // groups of 4 k are 512 bytes apart (stride offset); one instruction consumes 8 k = 1024 bytes.
+                        const uint64_t da = make_smem_desc(sa, 4096, 512, kLayoutSW128Base32);
+                        const uint64_t db = make_smem_desc(sa + kGemmStageA, 4096, 512, kLayoutSW128Base32);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma<KIND>(d_tmem, da + 64u * kk, db + 64u * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));          // stage reusable once these MMAs have read it
                 }

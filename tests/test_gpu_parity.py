@@ -322,6 +322,15 @@ def test_tri_mul_model_shapes(oracle, outgoing, L):
     assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), float(L), outgoing, path=PATH_AUTO)), ref) <= TOL_TF32
 
 
+@pytest.mark.parametrize("outgoing", [True, False])
+def test_tri_mul_tensor_core_ragged(oracle, outgoing):
+    """I, J, K not multiples of the tile (I, J multiples of 4 for the 16-byte rule): zero fill at every edge."""
+    for (D, I, J, K) in [(5, 132, 36, 44), (3, 260, 300, 100)]:
+        l, r = cases.tri_case(D, I, J, K, outgoing=outgoing, seed=D)
+        ref = oracle.tri_mul(l, r, float(K), outgoing)
+        assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), float(K), outgoing, path=PATH_UMMA)), ref) <= TOL_TF32
+
+
 @pytest.mark.parametrize("path,tol", [(PATH_SIMT, TOL_FP32), (PATH_AUTO, TOL_TF32)])
 def test_outer_prod_mean(oracle, path, tol):
     l, r = cases.opm_case(4, 12, 9)
@@ -340,6 +349,13 @@ def test_out_prod(oracle):
     # the reference's "real shape" case (tests/test_cuda.cpp:262-341): ne0 = ne1 = 51, K = 51, 16 x 64 planes (cut to 16 x 4)
     s0, s1 = cases.out_prod_case(51, 51, 51, 16, 4)
     assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1))), oracle.out_prod(s0, s1)) <= TOL_FP32
+    # aligned planes go to the tensor cores (both operands with the row index contiguous); K not a multiple of 32
+    for (n0, n1, k, p2, p3) in [(64, 48, 40, 3, 2), (256, 132, 256, 2, 1), (20, 36, 7, 1, 1)]:
+        s0, s1 = cases.out_prod_case(n0, n1, k, p2, p3)
+        ref = oracle.out_prod(s0, s1)
+        assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1), path=PATH_SIMT)), ref) <= TOL_FP32
+        assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1), path=PATH_UMMA)), ref) <= TOL_TF32
+        assert cases.rel_err(host(ops.out_prod_cuda(dev(s0), dev(s1), path=PATH_AUTO)), ref) <= TOL_TF32
     # known answer of tests/test_cuda.cpp:207-245
     a = (np.arange(12) % 7).astype(np.float32) * 0.5
     b = (np.arange(15) % 9).astype(np.float32) * 0.25 - 1.0
