@@ -62,6 +62,17 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// Same test, but the hardware may keep the thread suspended for up to `ns` nanoseconds while the phase is
+// incomplete: a waiting warp then takes far fewer issue slots from the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_test_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 
 // Bounded wait.  Every spin in these kernels goes through here: after kWaitCycles clock cycles
 // (or as soon as another thread of the CTA has given up) it records where it stopped,
@@ -74,7 +85,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
+#ifdef PPML_WAIT_HINT_NS
+        if (mbar_test_suspend(bar, parity, PPML_WAIT_HINT_NS)) return true;
+#else
         if (mbar_test(bar, parity)) return true;
+#endif
         if ((it & 63u) == 0u) {
             if (*cta_abort) return false;
             if (clock64() - t0 > kWaitCycles) break;
