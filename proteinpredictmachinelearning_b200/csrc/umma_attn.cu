@@ -2,15 +2,17 @@
 //
 //   O = softmax(scale * Q K^T + bias) V,  denominator (l + eps),  LSE = m + log(l + eps)
 //
-// One CTA = one (batch, head, 128-query tile); keys are walked in tiles of 128.
-//   warp 0      TMA: Q tile once, K tiles (128 keys x 32 floats, 128-byte swizzle, tf32 delivered by TMA)
-//   warp 1      MMA issue: S = Q K^T (four K = 8 tf32 MMAs, N = 128) into one of two TMEM S buffers,
-//               then O_part = P V (sixteen K = 8 MMAs, N = 32) into one of two TMEM O buffers
-//   warps 2-5   softmax, one thread per query row: S from TMEM, scale + bias + mask, running max / sum,
-//               P (rounded to tf32) into shared memory as the next MMA's K-major A operand, then
-//               o = alpha * o + O_part in fp32 registers
-//   warps 6-9   stage V^T: V[key][d] is read row-contiguously and written as the K-major B operand
-//               (32 rows of d, keys along K)
+// One CTA = one (batch, head, 128-query tile); keys are walked in tiles of 64.  Two CTAs share an SM (256 TMEM
+// columns, about 100 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads
+// and tensor work.
+//   warp 0      TMA: Q tile once; per key tile K (64 keys x 32 floats, K-major, 128-byte swizzle) and V (the same
+//               box in the 32-byte-chunk swizzle: V[key][d] has d contiguous, which is the "row index contiguous"
+//               form of the B operand of P V, so V needs no transposition); fp32 -> tf32 rounding by the TMA unit
+//   warp 1      MMA issue: S = Q K^T (four K = 8 tf32 MMAs, N = 64) into one of two TMEM S buffers,
+//               then O_part = P V (eight K = 8 MMAs, N = 32) into one of two TMEM O buffers
+//   warps 2-5   softmax, one thread per query row: the 64 scores of the tile from TMEM into registers, scale +
+//               bias + mask, running max / sum, P (rounded to tf32) into shared memory as the next MMA's K-major
+//               A operand, then o = alpha * o + O_part in fp32 registers, one tile late
 // Every wait is bounded; rows past L and keys past Lk are zero-filled by TMA and masked.
 #include <math_constants.h>
 
@@ -22,16 +24,17 @@ namespace ppml_b200 {
 namespace {
 
 constexpr int kD = 32;                       // head dim handled here
-constexpr int kBM = 128, kBN = 128;          // query tile, key tile
-constexpr int kTileQK = 128 * 128;           // bytes: 128 rows x 32 floats
-constexpr int kTileP = 4 * kTileQK;          // P: 128 rows x 128 floats as four 32-float swizzle atoms
-constexpr int kThreads = 320;
+constexpr int kBM = 128, kBN = 64;           // query tile, key tile
+constexpr int kTileQ = 128 * 128;            // bytes: 128 rows x 32 floats
+constexpr int kTileKV = kBN * 128;           // bytes: 64 keys x 32 floats
+constexpr int kTileP = (kBN / 32) * kTileQ;  // P: 128 rows x 64 floats as two 32-float swizzle atoms
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 256;          // S buffers at columns 0 and 64, O_part buffers at 128 and 160
 
 struct AttnParams {
     int B, H, L, Lk;
     int causal;
     float scale, eps;
-    const float* V;
     const float* bias;
     long long bias_batch_stride;
     float* O;
@@ -42,15 +45,16 @@ struct AttnParams {
 
 // smem map (offsets from the 1024-aligned base)
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kTileQK;              // 2 stages
-constexpr int kOffV = kOffK + 2 * kTileQK;          // 2 stages of V^T (32 x 128 floats = 16 KB)
-constexpr int kOffP = kOffV + 2 * kTileQK;          // 1 buffer
+constexpr int kOffK = kOffQ + kTileQ;               // 2 stages
+constexpr int kOffV = kOffK + 2 * kTileKV;          // 2 stages
+constexpr int kOffP = kOffV + 2 * kTileKV;          // 1 buffer
 constexpr int kOffStage = kOffP + kTileP;           // 4 warps x (32 rows x 144 B) output transposition
 constexpr int kOffBar = kOffStage + 4 * 32 * 144;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 
-__global__ void __launch_bounds__(kThreads, 1)
-umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const AttnParams p) {
+__global__ void __launch_bounds__(kThreads, 2)
+umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sb = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* sg = smem_raw + (sb - smem_u32(smem_raw));
@@ -81,7 +85,7 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1);
-            mbar_init(v_full(s), 4); mbar_init(v_empty(s), 1);
+            mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1); mbar_init(s_empty(s), 4);
             mbar_init(o_full(s), 1); mbar_init(o_empty(s), 4);
         }
@@ -89,30 +93,32 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         *cta_abort = 0;
         fence_barrier_init();
     }
-    if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
-    if (warp == 0 && lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmK); }
+    if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S buffers at 0 and 128, O_part buffers at 256 and 288
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, kTileQK);
+            mbar_arrive_expect_tx(q_full, kTileQ);
             tma_load_3d(sb + kOffQ, &tmQ, q_full, 0, q0, bh);
             for (int j = 0; j < k_tiles; ++j) {
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
                 if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) break;
-                mbar_arrive_expect_tx(k_full(s), kTileQK);
-                tma_load_3d(sb + kOffK + s * kTileQK, &tmK, k_full(s), 0, j * kBN, bh);
+                mbar_arrive_expect_tx(k_full(s), kTileKV);
+                tma_load_3d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, bh);
+                if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2102)) break;
+                mbar_arrive_expect_tx(v_full(s), kTileKV);
+                tma_load_3d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, bh);
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc_s = make_idesc(1, 2, 2, 0, 0, 128, kBN);
-            const uint32_t idesc_o = make_idesc(1, 2, 2, 0, 0, 128, kD);
+            const uint32_t idesc_o = make_idesc(1, 2, 2, 0, 1, 128, kD);     // B = V with d (the row index) contiguous
             bool ok = mbar_wait(q_full, 0, cta_abort, p.err, 0x2201);
             // software pipeline: S(j+1) is issued before P(j) V(j), so the softmax of tile j+1 can start
             // while the tensor core finishes tile j
@@ -122,9 +128,9 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (!mbar_wait(s_empty(s), ph ^ 1u, cta_abort, p.err, 0x2203)) return false;
                 tc_fence_after();
                 const uint64_t dq = make_smem_desc(sb + kOffQ, 16, 1024, kLayoutSW128);
-                const uint64_t dk = make_smem_desc(sb + kOffK + s * kTileQK, 16, 1024, kLayoutSW128);
+                const uint64_t dk = make_smem_desc(sb + kOffK + s * kTileKV, 16, 1024, kLayoutSW128);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) umma<MmaKind::TF32>(tmem_base + s * 128, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
+                for (int kk = 0; kk < 4; ++kk) umma<MmaKind::TF32>(tmem_base + s * kBN, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
                 umma_commit(k_empty(s));
                 umma_commit(s_full(s));
                 return true;
@@ -137,13 +143,15 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (!mbar_wait(v_full(s), ph, cta_abort, p.err, 0x2205)) { ok = false; break; }
                 if (!mbar_wait(o_empty(s), ph ^ 1u, cta_abort, p.err, 0x2206)) { ok = false; break; }
                 tc_fence_after();
+                // V tile: 64 key rows of 128 bytes in the 32-byte-chunk swizzle; a group of 4 keys is 512 bytes
+                // (stride offset), one instruction consumes 8 keys = 1024 bytes.  P: two 32-key swizzle atoms.
+                const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW128Base32);
 #pragma unroll
-                for (int a = 0; a < 4; ++a) {            // four 32-key swizzle atoms of P and of V^T
-                    const uint64_t dp = make_smem_desc(sb + kOffP + a * kTileQK, 16, 1024, kLayoutSW128);
-                    const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileQK + a * 4096, 16, 1024, kLayoutSW128);
+                for (int a = 0; a < kBN / 32; ++a) {
+                    const uint64_t dp = make_smem_desc(sb + kOffP + a * kTileQ, 16, 1024, kLayoutSW128);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma<MmaKind::TF32>(tmem_base + 256 + s * kD, dp + 2u * kk, dv + 2u * kk, idesc_o, (a | kk) ? 1u : 0u);
+                        umma<MmaKind::TF32>(tmem_base + 128 + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
                 }
                 umma_commit(p_empty);
                 umma_commit(v_empty(s));
@@ -151,33 +159,13 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
-#include "umma_attn_softmax.inc"
     } else {
-        // ---------------- V^T staging: lane = d, each warp takes every fourth key ------------------------
-        const int vw = warp - 6;
-        const float* Vb = p.V + static_cast<size_t>(bh) * p.Lk * kD;
-        bool ok = true;
-        for (int j = 0; j < k_tiles && ok; ++j) {
-            const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-            if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2401)) { ok = false; break; }
-            uint8_t* vt = sg + kOffV + s * kTileQK;
-#pragma unroll 4
-            for (int kk = vw; kk < kBN; kk += 4) {
-                const int key = j * kBN + kk;
-                const float v = (key < p.Lk) ? tf32_round(Vb[static_cast<size_t>(key) * kD + lane]) : 0.0f;
-                // row = d (lane), column = key inside the tile: atom kk / 32, 16-byte chunk (kk % 32) / 4
-                *reinterpret_cast<float*>(vt + (kk >> 5) * 4096 + sw128_off(lane, (kk & 31) >> 2) + (kk & 3) * 4) = v;
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(v_full(s));
-        }
+#include "umma_attn_softmax.inc"
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
 }  // namespace
@@ -194,13 +182,14 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
     const long long BH = static_cast<long long>(B) * H;
     AttnParams p{};
     p.B = B; p.H = H; p.L = L; p.Lk = Lk; p.causal = causal; p.scale = scale; p.eps = eps;
-    p.V = V; p.bias = bias; p.bias_batch_stride = bias_batch_stride; p.O = O; p.LSE = LSE;
+    p.bias = bias; p.bias_batch_stride = bias_batch_stride; p.O = O; p.LSE = LSE;
     p.q_tiles = (L + kBM - 1) / kBM; p.k_tiles = (Lk + kBN - 1) / kBN; p.err = err;
     const long long grid = BH * p.q_tiles;
     if (grid <= 0 || grid > 0x7fffffffLL) return ST_BAD_ARGS;
-    CUtensorMap tmQ, tmK;
-    if (!make_tmap_3d(&tmQ, TmaType::TF32, Q, kD, L, BH, kD * 4, static_cast<uint64_t>(L) * kD * 4, kD, kBM, true)) return ST_UNSUPPORTED_PATH;
-    if (!make_tmap_3d(&tmK, TmaType::TF32, K, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, true)) return ST_UNSUPPORTED_PATH;
+    CUtensorMap tmQ, tmK, tmV;
+    if (!make_tmap_3d(&tmQ, TmaType::TF32, Q, kD, L, BH, kD * 4, static_cast<uint64_t>(L) * kD * 4, kD, kBM, 1)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_3d(&tmK, TmaType::TF32, K, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 1)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_3d(&tmV, TmaType::TF32, V, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 2)) return ST_UNSUPPORTED_PATH;
     static bool configured[64] = {false};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -210,7 +199,7 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
         }
         configured[dev] = true;
     }
-    umma_attn_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, st>>>(tmQ, tmK, p);
+    umma_attn_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, st>>>(tmQ, tmK, tmV, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
