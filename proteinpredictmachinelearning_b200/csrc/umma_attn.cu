@@ -5,7 +5,7 @@
 // One CTA = one (batch, head, 128-query tile); keys are walked in tiles of 64.  Two CTAs share an SM (256 TMEM
 // columns, about 100 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads
 // and tensor work.
-//   warp 0      TMA: Q tile once; per key tile K (64 keys x 32 floats, K-major, 128-byte swizzle) and V (the same
+//   warp 0      TMA: Q tile once; per key tile the bias tile (128 rows x 64 keys fp32, when a bias is given), K (64 keys x 32 floats, K-major, 128-byte swizzle) and V (the same
 //               box in the 32-byte-chunk swizzle: V[key][d] has d contiguous, which is the "row index contiguous"
 //               form of the B operand of P V, so V needs no transposition); fp32 -> tf32 rounding by the TMA unit
 //   warp 1      MMA issue: S = Q K^T (four K = 8 tf32 MMAs, N = 64) into one of two TMEM S buffers,
@@ -43,18 +43,20 @@ struct AttnParams {
     int* err;
 };
 
-// smem map (offsets from the 1024-aligned base)
+// smem map (offsets from the 1024-aligned base); two CTAs per SM leave about 113 KB each
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kTileQ;               // 2 stages
-constexpr int kOffV = kOffK + 2 * kTileKV;          // 2 stages
-constexpr int kOffP = kOffV + 2 * kTileKV;          // 1 buffer
-constexpr int kOffStage = kOffP + kTileP;           // 4 warps x (32 rows x 144 B) output transposition
-constexpr int kOffBar = kOffStage + 4 * 32 * 144;
+constexpr int kOffK = kOffQ + kTileQ;               // 1 stage (free again as soon as S = Q K^T has been computed)
+constexpr int kOffV = kOffK + kTileKV;              // 2 stages
+constexpr int kOffP = kOffV + 2 * kTileKV;          // 1 buffer; after the last tile it serves as the output
+constexpr int kOffStage = kOffP;                    //   transposition buffer (4 warps x 32 rows x 144 B)
+constexpr int kOffB = kOffP + kTileP;               // bias tile, same layout as P (two 32-key swizzle atoms)
+constexpr int kOffBar = kOffB + kTileP;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
+static_assert(4 * 32 * 144 <= kTileP, "output staging must fit into the P buffer");
 
 __global__ void __launch_bounds__(kThreads, 2)
 umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sb = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* sg = smem_raw + (sb - smem_u32(smem_raw));
@@ -69,8 +71,9 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto o_full = [&](int s) { return bar0 + 8u * (13 + s); };
     auto o_empty = [&](int s) { return bar0 + 8u * (15 + s); };
     const uint32_t p_full = bar0 + 8u * 17, p_empty = bar0 + 8u * 18;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sg + kOffBar + 8 * 19);
-    volatile int* cta_abort = reinterpret_cast<volatile int*>(sg + kOffBar + 8 * 19 + 8);
+    const uint32_t b_full = bar0 + 8u * 19, b_empty = bar0 + 8u * 20;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sg + kOffBar + 8 * 21);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(sg + kOffBar + 8 * 21 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qt = blockIdx.x % p.q_tiles;
@@ -90,11 +93,12 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mbar_init(o_full(s), 1); mbar_init(o_empty(s), 4);
         }
         mbar_init(p_full, 4); mbar_init(p_empty, 1);
+        mbar_init(b_full, 1); mbar_init(b_empty, 4);
         *cta_abort = 0;
         fence_barrier_init();
     }
     if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols); tmem_relinquish(); }
-    if (warp == 0 && lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); if (p.bias != nullptr) prefetch_tmap(&tmB); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -104,11 +108,19 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
             mbar_arrive_expect_tx(q_full, kTileQ);
             tma_load_3d(sb + kOffQ, &tmQ, q_full, 0, q0, bh);
+            const int brow0 = hh * p.L + q0;                         // first bias row of this tile
+            const int bbatch = (p.bias_batch_stride != 0) ? b : 0;
             for (int j = 0; j < k_tiles; ++j) {
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-                if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) break;
-                mbar_arrive_expect_tx(k_full(s), kTileKV);
-                tma_load_3d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, bh);
+                if (p.bias != nullptr) {
+                    if (!mbar_wait(b_empty, (j & 1u) ^ 1u, cta_abort, p.err, 0x2103)) break;
+                    mbar_arrive_expect_tx(b_full, kTileP);
+                    tma_load_3d(sb + kOffB, &tmB, b_full, j * kBN, brow0, bbatch);
+                    tma_load_3d(sb + kOffB + kTileQ, &tmB, b_full, j * kBN + 32, brow0, bbatch);
+                }
+                if (!mbar_wait(k_empty(0), (j & 1u) ^ 1u, cta_abort, p.err, 0x2101)) break;
+                mbar_arrive_expect_tx(k_full(0), kTileKV);
+                tma_load_3d(sb + kOffK, &tmK, k_full(0), 0, j * kBN, bh);
                 if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2102)) break;
                 mbar_arrive_expect_tx(v_full(s), kTileKV);
                 tma_load_3d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, bh);
@@ -124,14 +136,14 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // while the tensor core finishes tile j
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-                if (!mbar_wait(k_full(s), ph, cta_abort, p.err, 0x2202)) return false;
+                if (!mbar_wait(k_full(0), j & 1u, cta_abort, p.err, 0x2202)) return false;
                 if (!mbar_wait(s_empty(s), ph ^ 1u, cta_abort, p.err, 0x2203)) return false;
                 tc_fence_after();
                 const uint64_t dq = make_smem_desc(sb + kOffQ, 16, 1024, kLayoutSW128);
-                const uint64_t dk = make_smem_desc(sb + kOffK + s * kTileKV, 16, 1024, kLayoutSW128);
+                const uint64_t dk = make_smem_desc(sb + kOffK, 16, 1024, kLayoutSW128);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) umma<MmaKind::TF32>(tmem_base + s * kBN, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
-                umma_commit(k_empty(s));
+                umma_commit(k_empty(0));
                 umma_commit(s_full(s));
                 return true;
             };
@@ -186,10 +198,17 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
     p.q_tiles = (L + kBM - 1) / kBM; p.k_tiles = (Lk + kBN - 1) / kBN; p.err = err;
     const long long grid = BH * p.q_tiles;
     if (grid <= 0 || grid > 0x7fffffffLL) return ST_BAD_ARGS;
-    CUtensorMap tmQ, tmK, tmV;
+    CUtensorMap tmQ, tmK, tmV, tmB;
     if (!make_tmap_3d(&tmQ, TmaType::TF32, Q, kD, L, BH, kD * 4, static_cast<uint64_t>(L) * kD * 4, kD, kBM, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmK, TmaType::TF32, K, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmV, TmaType::TF32, V, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 2)) return ST_UNSUPPORTED_PATH;
+    // bias rows are (head, query) pairs, [B or 1][H * L][Lk]; fp32 as it is (no tf32 rounding)
+    tmB = tmQ;
+    if (bias) {
+        const bool per_batch = bias_batch_stride != 0;
+        if (!make_tmap_3d(&tmB, TmaType::F32, bias, Lk, static_cast<uint64_t>(H) * L, per_batch ? B : 1, static_cast<uint64_t>(Lk) * 4,
+                          per_batch ? static_cast<uint64_t>(bias_batch_stride) * 4 : 0, 32, kBM, 1)) return ST_UNSUPPORTED_PATH;
+    }
     static bool configured[64] = {false};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -199,7 +218,7 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
         }
         configured[dev] = true;
     }
-    umma_attn_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, st>>>(tmQ, tmK, tmV, p);
+    umma_attn_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, st>>>(tmQ, tmK, tmV, tmB, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
