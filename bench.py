@@ -312,7 +312,8 @@ def run_ours(args):
                    "N": list(NS), "M": list(MS), "seed": SEED, "sharding": f"token rows, {world} shard(s)",
                    "l2": "working set per step (~0.9 GB) exceeds L2, no explicit flush"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind,
+                     "traffic": Q8_SWEEP_DRAM_BYTES_PER_LAUNCH if not args.only else None,
+                     "algorithmic_bytes_per_launch": step_bytes / max(len(sh), 1), "peak_kind": peak_kind,
                      "kernel": "umma_q8_kernel, all launches of the timed region (sum of algorithmic bytes / sum of durations)"},
         "e2e": {"value": step_flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -342,6 +343,39 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one pass of the sweep (36 launches of umma_q8_kernel) from one ncu
+# capture on a B200, divided by 36; the capture command and the per-launch figures are in
+# profiles/q8_sweep_dram_traffic.md.  Below the algorithmic bytes: part of each result is still in L2 at kernel end.
+Q8_SWEEP_DRAM_BYTES_PER_LAUNCH = 70.4e6
+
+
+def attn_profile(args):
+    """Profiling run (--kernel attn --no-e2e): MSA row attention of configs[2] cut to `--only B,h,L` (default
+    64,8,256), head dim 32, shared pair bias [h, L, L]; prints one JSON line with the CUDA-event time."""
+    import torch
+    from proteinpredictmachinelearning_b200 import ops, PATH_UMMA
+    dev = torch.device("cuda", 0)
+    B, h, L = (int(v) for v in args.only.split(",")) if args.only else (64, 8, 256)
+    g = torch.Generator(device=dev).manual_seed(3)
+    Q, K, V = (torch.randn(B, h, L, 32, device=dev, generator=g) / 32 ** 0.5 for _ in range(3))
+    bias = torch.randn(h, L, L, device=dev, generator=g)
+    f = lambda: ops.flash_attn_forward_cuda(Q, K, V, bias, scale=1 / 32 ** 0.5, bias_bcast=True, path=PATH_UMMA)
+    for _ in range(max(args.warmup, 3)):
+        f()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        f()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / args.steps * 1e3
+    flops = 4.0 * B * h * L * L * 32
+    nbytes = 16.0 * B * h * L * 32 + 4.0 * h * L * L + 4.0 * B * h * L
+    print(json.dumps({"kernel": "umma_attn_kernel", "B": B, "h": h, "L": L, "us": us, "tflops": flops / us / 1e6,
+                      "gbs": nbytes / us / 1e3}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -351,9 +385,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="stop after the device-resident region (profiling runs)")
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs)")
-    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16"],
+    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn"],
                     help="profiling runs with --no-e2e: time the fp32 (tf32 tensor-core) or bf16 mul_mat on the same shapes")
     args = ap.parse_args()
+    if args.kernel == "attn":
+        return attn_profile(args)
     if args.impl == "reference":
         run_reference(args)
     else:
