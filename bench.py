@@ -205,20 +205,24 @@ def run_ours(args):
     step_flops = sum(q8_flops(*s) for s in sh)
     step_bytes = sum(q8_bytes(*s) for s in sh)
 
+    def launch(m, k, n, Xs, Cs):
+        if args.kernel == "q8":
+            _, taken = ops.mul_mat_q8_cuda(W[(k, n)], Xs[(m, k)], n, wtype=2, c_trans=1, path=PATH_AUTO, out=Cs[(m, n)])
+        elif args.kernel == "tf32":
+            ops.mul_mat_cuda(Xs[(m, k)], Wf[(k, n)], path=PATH_AUTO, tf32_mode=1, out=Cs[(m, n)])
+            taken = 1
+        else:
+            ops.mul_mat_16(X16[(m, k)], W16[(k, n)], path=PATH_AUTO, out=Cs[(m, n)])
+            taken = 1
+        return taken
+
     def one_pass(events=None):
         for (m, k, n) in sh:
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            if args.kernel == "q8":
-                _, taken = ops.mul_mat_q8_cuda(W[(k, n)], X[(m, k)], n, wtype=2, c_trans=1, path=PATH_AUTO, out=Cout[(m, n)])
-            elif args.kernel == "tf32":
-                ops.mul_mat_cuda(X[(m, k)], Wf[(k, n)], path=PATH_AUTO, tf32_mode=1, out=Cout[(m, n)])
-                taken = 1
-            else:
-                ops.mul_mat_16(X16[(m, k)], W16[(k, n)], path=PATH_AUTO, out=Cout[(m, n)])
-                taken = 1
+            taken = launch(m, k, n, X, Cout)
             if events is not None:
                 e1.record()
                 events.append(((m, k, n), taken, e0, e1))
@@ -270,21 +274,64 @@ def run_ours(args):
     h2d = sum(t.numel() * 4 for t in Xh.values())
     d2h = sum(t.numel() * 4 for t in Ch.values())
 
-    def e2e_pass():
-        for key, t in Xh.items():
-            X[key].copy_(t, non_blocking=True)
-        one_pass()
-        for key, t in Ch.items():
-            t.copy_(Cout[key], non_blocking=True)
+    # Three streams: host -> device copies, kernels, device -> host copies.  Inputs and results are double-buffered on
+    # the device, so the copies of step i + 1 (in) and of step i (out) overlap; every step still copies all of its
+    # inputs in and all of its results out.
+    Xd = [X, {key: torch.empty_like(t) for key, t in X.items()}]
+    Cd = [Cout, {key: torch.empty_like(t) for key, t in Cout.items()}]
+    comp = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    last_writer = {}
+    for idx, (m, k, n) in enumerate(sh):
+        last_writer[(m, n)] = idx
+    done_comp, done_out = [None, None], [None, None]
+
+    def e2e_step(i):
+        buf = i & 1
+        if done_comp[buf] is not None:
+            s_in.wait_event(done_comp[buf])        # the kernels of step i - 2 have read these inputs
+        ev_in = {}
+        with torch.cuda.stream(s_in):
+            for key, t in Xh.items():
+                Xd[buf][key].copy_(t, non_blocking=True)
+                ev_in[key] = torch.cuda.Event()
+                ev_in[key].record(s_in)
+        if done_out[buf] is not None:
+            comp.wait_event(done_out[buf])         # the results of step i - 2 have left these buffers
+        ev_c, seen = {}, set()
+        for idx, (m, k, n) in enumerate(sh):
+            if (m, k) not in seen:
+                comp.wait_event(ev_in[(m, k)])
+                seen.add((m, k))
+            launch(m, k, n, Xd[buf], Cd[buf])
+            if last_writer[(m, n)] == idx:
+                ev_c[(m, n)] = torch.cuda.Event()
+                ev_c[(m, n)].record(comp)
+        done_comp[buf] = torch.cuda.Event()
+        done_comp[buf].record(comp)
+        with torch.cuda.stream(s_out):
+            for key, ev in ev_c.items():
+                s_out.wait_event(ev)
+                Ch[key].copy_(Cd[buf][key], non_blocking=True)
+            done_out[buf] = torch.cuda.Event()
+            done_out[buf].record(s_out)
+
+    def e2e_drain():
+        for ev in done_out:
+            if ev is not None:
+                comp.wait_event(ev)
 
     e2e_steps = max(1, min(args.steps, 5))
-    e2e_pass()
+    e2e_step(0)
+    e2e_drain()
     barrier()
+    done_comp, done_out = [None, None], [None, None]
     u0 = torch.cuda.Event(enable_timing=True)
     u1 = torch.cuda.Event(enable_timing=True)
     u0.record()
-    for _ in range(e2e_steps):
-        e2e_pass()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2e_drain()
     u1.record()
     barrier()
     e2e_ms = u0.elapsed_time(u1)
