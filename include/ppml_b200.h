@@ -144,6 +144,10 @@ int ppml_b200_out_prod(const float* src0, const float* src1, float* dst,
  * NaN -> 0. */
 int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t D, int64_t I, int64_t J,
                       int64_t K, int64_t B, float inv_L, int outgoing, int path, void* stream);
+/* Same contraction with 16-bit operands (fp16, or bfloat16 when is_bf16 != 0), fp32 accumulation and output.
+ * No counterpart in the reference (its pair track is fp32); same layouts and semantics as above. */
+int ppml_b200_tri_mul_16(const void* left16, const void* right16, float* dst, int64_t D, int64_t I, int64_t J,
+                         int64_t K, int64_t B, float inv_L, int outgoing, int is_bf16, int path, void* stream);
 
 /* ---- OP_OUTER_PROD_MEAN ---------------------------------------------------------------------------
  * Replaces outer_prod_mean_cuda (src/backend/CUDAKernels.cpp:325; src/cuda/PairKernels.cu:177-199,
@@ -151,6 +155,9 @@ int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t
  * right[d2][j][n][b]. */
 int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst, int64_t D, int64_t L,
                               int64_t N, int64_t B, float inv_N, int path, void* stream);
+/* 16-bit operands (fp16 / bfloat16), fp32 accumulation and output; no counterpart in the reference. */
+int ppml_b200_outer_prod_mean_16(const void* left16, const void* right16, float* dst, int64_t D, int64_t L,
+                                 int64_t N, int64_t B, float inv_N, int is_bf16, int path, void* stream);
 
 /* ---- per-shape statistics ----------------------------------------------------------------------------
  * Replace mulmat_stats_cuda_begin / mulmat_stats_cuda_end (src/backend/CUDAKernels.cpp:190-191;

@@ -209,10 +209,9 @@ int ppml_b200_out_prod(const float* src0, const float* src1, float* dst,
     return launch_simt_contract(src0, src1, dst, p, 0, as_stream(stream));
 }
 
-int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t D, int64_t I, int64_t J,
-                      int64_t K, int64_t B, float inv_L, int outgoing, int path, void* stream) {
+static int tri_mul_any(const void* left, const void* right, float* dst, int64_t D, int64_t I, int64_t J,
+                       int64_t K, int64_t B, float inv_L, int outgoing, int path, int elem, cudaStream_t st) {
     if (!left || !right || !dst || D <= 0 || I <= 0 || J <= 0 || K <= 0 || B <= 0 || !path_ok(path)) return ST_BAD_ARGS;
-    cudaStream_t st = as_stream(stream);
     if (path != PPML_B200_PATH_SIMT) {
         int rc = ST_UNSUPPORTED_PATH;
         if (B == 1 && D <= 0x7fffffff && I <= 0x7fffffff && J <= 0x7fffffff && K <= 0x7fffffff) {
@@ -222,7 +221,7 @@ int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t
             if (outgoing) { a.lda = K; a.ldb = K; }                    // left[d][i][k], right[d][j][k]
             else { a.lda = I; a.ldb = J; a.mn_major = 1; }             // left[d][k][i], right[d][k][j]
             a.a_batch = I * K; a.b_batch = J * K; a.ldc = J; a.c_batch = I * J;
-            a.bias = nullptr; a.alpha = inv_L; a.clamp = 1; a.elem = 0; a.tf32_mode = PPML_B200_TF32_TMA;
+            a.bias = nullptr; a.alpha = inv_L; a.clamp = 1; a.elem = elem; a.tf32_mode = PPML_B200_TF32_TMA;
             rc = launch_umma_gemm(a, st);
         }
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
@@ -236,13 +235,22 @@ int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t
     p.a_s2 = 1; p.a_s3 = I * K * B; p.a_div2 = 1; p.a_div3 = 1;
     p.b_s2 = 1; p.b_s3 = J * K * B; p.c_s2 = 1; p.c_s3 = I * J * B;
     p.alpha = inv_L; p.clamp = 1;
-    return launch_simt_contract(left, right, dst, p, 0, st);
+    return launch_simt_contract(left, right, dst, p, elem, st);
 }
 
-int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst, int64_t D, int64_t L,
-                              int64_t N, int64_t B, float inv_N, int path, void* stream) {
+int ppml_b200_tri_mul(const float* left, const float* right, float* dst, int64_t D, int64_t I, int64_t J,
+                      int64_t K, int64_t B, float inv_L, int outgoing, int path, void* stream) {
+    return tri_mul_any(left, right, dst, D, I, J, K, B, inv_L, outgoing, path, 0, as_stream(stream));
+}
+
+int ppml_b200_tri_mul_16(const void* left16, const void* right16, float* dst, int64_t D, int64_t I, int64_t J,
+                         int64_t K, int64_t B, float inv_L, int outgoing, int is_bf16, int path, void* stream) {
+    return tri_mul_any(left16, right16, dst, D, I, J, K, B, inv_L, outgoing, path, is_bf16 ? 2 : 1, as_stream(stream));
+}
+
+static int outer_prod_mean_any(const void* left, const void* right, float* dst, int64_t D, int64_t L,
+                               int64_t N, int64_t B, float inv_N, int path, int elem, cudaStream_t st) {
     if (!left || !right || !dst || D <= 0 || L <= 0 || N <= 0 || B <= 0 || !path_ok(path)) return ST_BAD_ARGS;
-    cudaStream_t st = as_stream(stream);
     if (path != PPML_B200_PATH_SIMT) {
         int rc = ST_UNSUPPORTED_PATH;
         if (B == 1 && D * L <= 0x7fffffff && N <= 0x7fffffff) {
@@ -250,7 +258,7 @@ int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst,
             a.A = left; a.B = right; a.C = dst;
             a.M = static_cast<int>(D * L); a.N = static_cast<int>(D * L); a.K = static_cast<int>(N); a.batch = 1;
             a.lda = N; a.ldb = N; a.ldc = D * L; a.alpha = inv_N;
-            a.opm_D = static_cast<int>(D); a.opm_L = static_cast<int>(L); a.elem = 0; a.tf32_mode = PPML_B200_TF32_TMA;
+            a.opm_D = static_cast<int>(D); a.opm_L = static_cast<int>(L); a.elem = elem; a.tf32_mode = PPML_B200_TF32_TMA;
             rc = launch_umma_gemm(a, st);
         }
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
@@ -262,7 +270,17 @@ int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst,
     p.a_s2 = 1; p.a_div2 = 1; p.a_div3 = 1; p.b_s2 = 1; p.c_s2 = 1;
     p.alpha = inv_N;
     p.opm_D = D; p.opm_L = L; p.opm_B = B;
-    return launch_simt_contract(left, right, dst, p, 0, st);
+    return launch_simt_contract(left, right, dst, p, elem, st);
+}
+
+int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst, int64_t D, int64_t L,
+                              int64_t N, int64_t B, float inv_N, int path, void* stream) {
+    return outer_prod_mean_any(left, right, dst, D, L, N, B, inv_N, path, 0, as_stream(stream));
+}
+
+int ppml_b200_outer_prod_mean_16(const void* left16, const void* right16, float* dst, int64_t D, int64_t L,
+                                 int64_t N, int64_t B, float inv_N, int is_bf16, int path, void* stream) {
+    return outer_prod_mean_any(left16, right16, dst, D, L, N, B, inv_N, path, is_bf16 ? 2 : 1, as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

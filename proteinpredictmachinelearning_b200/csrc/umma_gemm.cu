@@ -53,7 +53,14 @@ int launch_bn(int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm
     }
 }
 
-int launch_bn_mn(int BN, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+int launch_bn_mn(int BN, bool half, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+    if (half) {
+        switch (BN) {
+            case 32: case 64: return launch_one<MmaKind::F16, 64, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+            case 128: return launch_one<MmaKind::F16, 128, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+            default: return launch_one<MmaKind::F16, 256, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
+        }
+    }
     switch (BN) {
         case 32: return launch_one<MmaKind::TF32, 32, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
         case 64: return launch_one<MmaKind::TF32, 64, Epi::ROW_MAJOR, false, true>(tmA, tmB, p, st);
@@ -84,23 +91,28 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st) {
     const int BN = pick_bn(a.N);
     const int bk = 128 / es;
     if (a.mn_major) {
-        // A[b][k][m], B[b][k][n] with the row index contiguous: fp32 operands only (tf32 delivered by TMA)
-        if (a.elem != 0 || a.opm_L > 0) return ST_UNSUPPORTED_PATH;
+        // A[b][k][m], B[b][k][n] with the row index contiguous: fp32 operands become tf32 in the TMA unit and use
+        // the 32-byte-chunk swizzle, 16-bit operands the ordinary 128-byte swizzle
+        if (a.opm_L > 0) return ST_UNSUPPORTED_PATH;
         CUtensorMap tmA, tmB;
-        const uint64_t a_bs = (a.batch > 1) ? static_cast<uint64_t>(a.a_batch) * 4 : 0;
-        const uint64_t b_bs = (a.batch > 1) ? static_cast<uint64_t>(a.b_batch) * 4 : 0;
-        if (!make_tmap_3d(&tmA, TmaType::TF32, a.A, a.M, a.K, a.batch, static_cast<uint64_t>(a.lda) * 4, a_bs, 32, 32, 2))
+        const bool half = a.elem != 0;
+        const TmaType tt = !half ? TmaType::TF32 : (a.elem == 1 ? TmaType::F16 : TmaType::BF16);
+        const uint32_t box = half ? 64 : 32;
+        const uint64_t a_bs = (a.batch > 1) ? static_cast<uint64_t>(a.a_batch) * es : 0;
+        const uint64_t b_bs = (a.batch > 1) ? static_cast<uint64_t>(a.b_batch) * es : 0;
+        if (!make_tmap_3d(&tmA, tt, a.A, a.M, a.K, a.batch, static_cast<uint64_t>(a.lda) * es, a_bs, box, box, half ? 1 : 2))
             return ST_UNSUPPORTED_PATH;
-        if (!make_tmap_3d(&tmB, TmaType::TF32, a.B, a.N, a.K, a.batch, static_cast<uint64_t>(a.ldb) * 4, b_bs, 32, 32, 2))
+        if (!make_tmap_3d(&tmB, tt, a.B, a.N, a.K, a.batch, static_cast<uint64_t>(a.ldb) * es, b_bs, box, box, half ? 1 : 2))
             return ST_UNSUPPORTED_PATH;
         GemmParams p{};
         p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
-        p.k_steps = (a.K + 31) / 32;
+        p.k_steps = (a.K + bk - 1) / bk;
+        p.ab_fmt = (a.elem == 2) ? 1 : 0;
         p.C = a.C; p.ldc = a.ldc; p.c_batch = a.c_batch;
         p.bias = a.bias; p.alpha = a.alpha; p.clamp = a.clamp;
         p.err = err;
         p.vec_ok = ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) && (a.ldc % 4 == 0) && (a.c_batch % 4 == 0) && (a.N % 4 == 0);
-        return launch_bn_mn(BN, tmA, tmB, p, st);
+        return launch_bn_mn(BN, half, tmA, tmB, p, st);
     }
     TmaType tt = (a.elem == 0) ? (a.tf32_mode == 1 ? TmaType::TF32 : TmaType::F32)
                                : (a.elem == 1 ? TmaType::F16 : TmaType::BF16);

@@ -59,7 +59,8 @@ __host__ __device__ constexpr int gemm_smem_bytes() {
 }
 
 // MNMAJOR: both operands are stored with the row index (m or n) contiguous and K strided (A[b][k][m],
-// B[b][k][n]); the stage then holds boxes of 32 rows x 32 k in the 32-byte-chunk form of the 128-byte swizzle.
+// B[b][k][n]); the stage then holds boxes of 128 bytes of rows x BK k: 32 rows x 32 k in the 32-byte-chunk form
+// of the 128-byte swizzle for fp32 operands, 64 rows x 64 k in the ordinary 128-byte swizzle for 16-bit ones.
 template <MmaKind KIND, int BN, Epi EPI, bool CONVERT, bool MNMAJOR = false>
 __global__ void __launch_bounds__(CONVERT ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -129,11 +130,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         tma_load_3d(sa, &tmA, full_bar(s), ks * BK, mt * 128, b);
                         tma_load_3d(sa + kGemmStageA, &tmB, full_bar(s), ks * BK, nt * BN, b);
                     } else {
-                        // boxes of 32 rows (inner, contiguous) x 32 k: 4 KB each, row blocks 4 KB apart
+                        // boxes of BK rows (inner, contiguous: 128 bytes) x BK k, one after the other
+                        constexpr int kBox = BK * 128;
+                        static_assert(BN % BK == 0, "row-contiguous operands: BN must be a multiple of the box width");
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) tma_load_3d(sa + i * 4096, &tmA, full_bar(s), mt * 128 + i * 32, ks * 32, b);
+                        for (int i = 0; i < 128 / BK; ++i) tma_load_3d(sa + i * kBox, &tmA, full_bar(s), mt * 128 + i * BK, ks * BK, b);
 #pragma unroll
-                        for (int i = 0; i < BN / 32; ++i) tma_load_3d(sa + kGemmStageA + i * 4096, &tmB, full_bar(s), nt * BN + i * 32, ks * 32, b);
+                        for (int i = 0; i < BN / BK; ++i) tma_load_3d(sa + kGemmStageA + i * kBox, &tmB, full_bar(s), nt * BN + i * BK, ks * BK, b);
                     }
                 }
             }
@@ -145,7 +148,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t idesc;
             if constexpr (KIND == MmaKind::I8) idesc = make_idesc(2, 1, 1, 0, 0, 128, BN);
             else if constexpr (KIND == MmaKind::TF32) idesc = make_idesc(1, 2, 2, MNMAJOR ? 1 : 0, MNMAJOR ? 1 : 0, 128, BN);
-            else idesc = make_idesc(1, p.ab_fmt, p.ab_fmt, 0, 0, 128, BN);
+            else idesc = make_idesc(1, p.ab_fmt, p.ab_fmt, MNMAJOR ? 1 : 0, MNMAJOR ? 1 : 0, 128, BN);
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
@@ -172,11 +175,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         // 32-bit operands with the row index contiguous: 128-byte swizzle over 32-byte chunks, whose
                         // atom is 4 k x 128 bytes.  Row blocks (32 rows) are 4096 bytes apart (leading offset),
                         // groups of 4 k are 512 bytes apart (stride offset); one instruction consumes 8 k = 1024 bytes.
-                        const uint64_t da = make_smem_desc(sa, 4096, 512, kLayoutSW128Base32);
-                        const uint64_t db = make_smem_desc(sa + kGemmStageA, 4096, 512, kLayoutSW128Base32);
+                        // 16-bit operands: the ordinary 128-byte swizzle, atom 8 k x 128 bytes; row blocks (64 rows) 8192
+                        // bytes apart, groups of 8 k 1024 bytes apart, one instruction consumes 16 k = 2048 bytes.
+                        constexpr uint32_t kLbo = BK * 128, kSbo = (KIND == MmaKind::TF32) ? 512 : 1024;
+                        constexpr uint32_t kLay = (KIND == MmaKind::TF32) ? kLayoutSW128Base32 : kLayoutSW128;
+                        constexpr uint32_t kAdv = (KIND == MmaKind::TF32) ? 64u : 128u;
+                        const uint64_t da = make_smem_desc(sa, kLbo, kSbo, kLay);
+                        const uint64_t db = make_smem_desc(sa + kGemmStageA, kLbo, kSbo, kLay);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk)
-                            umma<KIND>(d_tmem, da + 64u * kk, db + 64u * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
+                            umma<KIND>(d_tmem, da + kAdv * kk, db + kAdv * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));          // stage reusable once these MMAs have read it
                 }

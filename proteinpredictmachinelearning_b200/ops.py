@@ -170,7 +170,12 @@ def out_prod_cuda(s0, s1, path=PATH_AUTO):
 def tri_mul_cuda(left, right, L, outgoing, path=PATH_AUTO):
     """Flat layout, D outermost, B innermost: outgoing left [D,I,K,B], right [D,J,K,B]; incoming left
     [D,K,I,B], right [D,K,J,B] -> dst [D,I,J,B]."""
-    left, right = _f32c(left), _f32c(right)
+    half = left.dtype in (torch.float16, torch.bfloat16)      # 16-bit operands: fp32 accumulation and output
+    if half:
+        assert right.dtype == left.dtype
+        left, right = left.contiguous(), right.contiguous()
+    else:
+        left, right = _f32c(left), _f32c(right)
     if outgoing:
         D, I, K, B = left.shape
         J = right.shape[1]
@@ -178,17 +183,30 @@ def tri_mul_cuda(left, right, L, outgoing, path=PATH_AUTO):
         D, K, I, B = left.shape
         J = right.shape[2]
     dst = torch.empty((D, I, J, B), device=left.device, dtype=torch.float32)
-    rc = _lib.load().ppml_b200_tri_mul(_p(left), _p(right), _p(dst), D, I, J, K, B, 1.0 / float(L), int(bool(outgoing)),
-                                       path, _stream())
+    if half:
+        rc = _lib.load().ppml_b200_tri_mul_16(_p(left), _p(right), _p(dst), D, I, J, K, B, 1.0 / float(L), int(bool(outgoing)),
+                                              int(left.dtype == torch.bfloat16), path, _stream())
+    else:
+        rc = _lib.load().ppml_b200_tri_mul(_p(left), _p(right), _p(dst), D, I, J, K, B, 1.0 / float(L), int(bool(outgoing)),
+                                           path, _stream())
     _check(rc, "tri_mul")
     return dst
 
 
 def outer_prod_mean_cuda(left, right, path=PATH_AUTO):
     """left/right flat [D,L,N,B] -> [D*D, L, L, B], mean over N."""
-    left, right = _f32c(left), _f32c(right)
+    half = left.dtype in (torch.float16, torch.bfloat16)      # 16-bit operands: fp32 accumulation and output
+    if half:
+        assert right.dtype == left.dtype
+        left, right = left.contiguous(), right.contiguous()
+    else:
+        left, right = _f32c(left), _f32c(right)
     D, L, N, B = left.shape
     dst = torch.empty((D * D, L, L, B), device=left.device, dtype=torch.float32)
-    rc = _lib.load().ppml_b200_outer_prod_mean(_p(left), _p(right), _p(dst), D, L, N, B, 1.0 / float(N), path, _stream())
+    if half:
+        rc = _lib.load().ppml_b200_outer_prod_mean_16(_p(left), _p(right), _p(dst), D, L, N, B, 1.0 / float(N),
+                                                      int(left.dtype == torch.bfloat16), path, _stream())
+    else:
+        rc = _lib.load().ppml_b200_outer_prod_mean(_p(left), _p(right), _p(dst), D, L, N, B, 1.0 / float(N), path, _stream())
     _check(rc, "outer_prod_mean")
     return dst

@@ -331,6 +331,33 @@ def test_tri_mul_tensor_core_ragged(oracle, outgoing):
         assert cases.rel_err(host(ops.tri_mul_cuda(dev(l), dev(r), float(K), outgoing, path=PATH_UMMA)), ref) <= TOL_TF32
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("outgoing", [True, False])
+def test_tri_mul_16bit(oracle, dtype, outgoing):
+    """16-bit operands: against the fp32 checker fed the rounded operands (1e-5) and the unrounded ones (1e-2)."""
+    for (D, I, J, K) in [(4, 128, 128, 128), (3, 136, 72, 40), (2, 256, 256, 256)]:
+        l, r = cases.tri_case(D, I, J, K, outgoing=outgoing, seed=11 + D)
+        l16, r16 = dev(l).to(dtype), dev(r).to(dtype)
+        ref16 = oracle.tri_mul(host(l16.float()), host(r16.float()), float(K), outgoing)
+        ref32 = oracle.tri_mul(l, r, float(K), outgoing)
+        for path in (PATH_SIMT, PATH_UMMA, PATH_AUTO):
+            got = host(ops.tri_mul_cuda(l16, r16, float(K), outgoing, path=path))
+            assert cases.rel_err(got, ref16) <= TOL_FP32, (D, I, J, K, path)
+            assert cases.rel_err(got, ref32) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_outer_prod_mean_16bit(oracle, dtype):
+    for (D, L, N) in [(4, 40, 64), (8, 51, 8), (16, 64, 256)]:
+        l, r = cases.opm_case(D, L, N, seed=5 + D)
+        l16, r16 = dev(l).to(dtype), dev(r).to(dtype)
+        ref16 = oracle.outer_prod_mean(host(l16.float()), host(r16.float()))
+        for path in (PATH_SIMT, PATH_AUTO):
+            got = host(ops.outer_prod_mean_cuda(l16, r16, path=path))
+            assert cases.rel_err(got, ref16) <= TOL_FP32, (D, L, N, path)
+        assert cases.rel_err(got, oracle.outer_prod_mean(l, r)) <= 1e-2
+
+
 @pytest.mark.parametrize("path,tol", [(PATH_SIMT, TOL_FP32), (PATH_AUTO, TOL_TF32)])
 def test_outer_prod_mean(oracle, path, tol):
     l, r = cases.opm_case(4, 12, 9)
