@@ -44,12 +44,16 @@ __device__ long long g_q8_trace[64];
 constexpr int kTile = 128 * 128;          // bytes: one int8 A tile (128 rows x 128 K) == one weight stage == one raw fp32 stage
 constexpr int kMaxKT = 8;                 // K <= 1024
 constexpr int kMaxStages = 6;
-constexpr int kQuantWarps = 2;            // 64 token rows each
+// Two warp layouts (template parameter QW = number of quantizer warps):
+//   QW = 2: warp 0 TMA, 1 MMA, 2-3 quantizers (two token rows per thread), 4-19 epilogue: 20 warps, 96 registers;
+//           for items with several column blocks, where the epilogue is the limiter and must not spill.
+//   QW = 4: warps 0-3 quantizers (one row per thread), 4-19 epilogue, 20 TMA, 21 MMA: 22 warps, 80 registers;
+//           for items with a single column block, where the quantizer is the limiter.
 constexpr int kEpiWarps = 16;             // four per TMEM lane quarter, 32 output columns each
-constexpr int kFirstQuantWarp = 2;
-constexpr int kFirstEpiWarp = kFirstQuantWarp + kQuantWarps;      // a multiple of 4: warp % 4 is the lane quarter
-constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
-static_assert(kFirstEpiWarp % 4 == 0, "epilogue warps must start at a multiple of four");
+constexpr int kFirstEpiWarp = 4;          // a multiple of 4: warp % 4 is the lane quarter
+template <int QW> struct Roles;
+template <> struct Roles<2> { static constexpr int kFirstQuantWarp = 2, kTmaWarp = 0, kMmaWarp = 1, kThreads = 32 * 20; };
+template <> struct Roles<4> { static constexpr int kFirstQuantWarp = 0, kTmaWarp = 20, kMmaWarp = 21, kThreads = 32 * 22; };
 
 struct Q8Params {
     int Mout, Ntok, K, nblk, KT;
@@ -57,7 +61,8 @@ struct Q8Params {
     int n_blocks;              // weight column blocks of 128
     int groups, blocks_per_group;
     int RS, BS;                // ring depths
-    int abuf;                  // copies of the quantized A tile (2: the next item is quantized while this one multiplies)
+    int AR;                    // 16 KB slots of quantized A, used as a ring over (item, K step): KT = resident, 2 KT = resident
+                               // and double-buffered across items, 3 = a short ring (items with a single column block)
     int dw_tabs;               // scale tables held in smem: n_blocks (all resident, filled once) or 1 (refilled per column block)
     int staged;                // 1: results leave through per-warp transposition buffers (row-contiguous stores)
     const __half* Wd;          // weight scales [Mout][nblk]
@@ -76,10 +81,10 @@ struct SmemLayout {
 constexpr int kStoreBytes = 32 * 64;                // one epilogue warp's 32 rows x 16 columns transposition buffer
 constexpr int kNumBarriers = 4 * kMaxStages + 4 * kMaxKT + 8 + 4;
 
-__host__ __device__ inline SmemLayout q8_layout(int KT, int nblk, int RS, int BS, int abuf, int dw_tabs, int staged) {
+__host__ __device__ inline SmemLayout q8_layout(int AR, int nblk, int RS, int BS, int dw_tabs, int staged) {
     SmemLayout L;
     L.a_off = 0;
-    L.raw_off = L.a_off + abuf * KT * kTile;
+    L.raw_off = L.a_off + AR * kTile;
     L.w_off = L.raw_off + RS * kTile;
     L.c_off = L.w_off + BS * kTile;                  // 4 KB of the byte 0x80: both operands of the offset MMA
     L.dw_off = L.c_off + 4096;                       // float [dw_tabs][nblk][128]
@@ -152,20 +157,85 @@ __device__ __forceinline__ float quantize_row(const uint8_t* raw, uint8_t* at, i
     return d;
 }
 
-template <bool SUMI>      // SUMI: also write the raw int32 block sums (tests)
-__global__ void __launch_bounds__(kThreads, 1)
+// Two rows at a time (rows `row` and `row + 32`): the two dependency chains interleave, which roughly doubles the
+// instruction-level parallelism of the quantizer warps.
+__device__ __forceinline__ void quantize_rows2(const uint8_t* raw, uint8_t* at, int row, int c0, float& d_out0, float& d_out1) {
+    float x[2][32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const float4 t = *reinterpret_cast<const float4*>(raw + sw128_off(row + 32 * u, c));
+            x[u][4 * c] = t.x; x[u][4 * c + 1] = t.y; x[u][4 * c + 2] = t.z; x[u][4 * c + 3] = t.w;
+        }
+    }
+    float vpos[2], vneg[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) { vpos[u] = fmaxf(x[u][0], x[u][1]); vneg[u] = fminf(x[u][0], x[u][1]); }
+#pragma unroll
+    for (int i = 2; i < 32; i += 2) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) { vpos[u] = max3(vpos[u], x[u][i], x[u][i + 1]); vneg[u] = min3(vneg[u], x[u][i], x[u][i + 1]); }
+    }
+    uint64_t inv2[2];
+    float d[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const float amax = fmaxf(vpos[u], -vneg[u]);
+        float vmax;
+        if (vpos[u] == -vneg[u] && amax != 0.0f) {        // +a and -a both present: the first one wins
+            vmax = 0.0f;
+#pragma unroll
+            for (int i = 31; i >= 0; --i) if (fabsf(x[u][i]) == amax) vmax = x[u][i];
+        } else {
+            vmax = (vpos[u] == amax) ? vpos[u] : vneg[u];
+        }
+        d[u] = (amax == 0.0f) ? 0.0f : vmax * -0.0078125f;
+        const float inv = (d[u] == 0.0f) ? 0.0f : 1.0f / d[u];
+        inv2[u] = pack2(inv, inv);
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        uint32_t packed[2][4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                int qi[4];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int i0 = 16 * hf + 4 * w + 2 * e;
+                    const uint64_t y2 = fmul2(pack2(x[u][i0], x[u][i0 + 1]), inv2[u]);
+                    const uint64_t h2 = (y2 & 0x8000000080000000ull) | 0x3F0000003F000000ull;     // copysign(0.5, y)
+                    float t0, t1;
+                    unpack2(fadd2_rz(y2, h2), t0, t1);
+                    qi[2 * e] = f2i_rz(t0);
+                    qi[2 * e + 1] = f2i_rz(t1);
+                }
+                packed[u][w] = pack_s8(qi[1], qi[0], pack_s8(qi[3], qi[2], 0u));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            *reinterpret_cast<uint4*>(at + sw128_off(row + 32 * u, c0 + hf)) = make_uint4(packed[u][0], packed[u][1], packed[u][2], packed[u][3]);
+    }
+    d_out0 = d[0]; d_out1 = d[1];
+}
+
+template <bool SUMI, int QW>      // SUMI: also write the raw int32 block sums (tests); QW: quantizer warps
+__global__ void __launch_bounds__(Roles<QW>::kThreads, 1)
 umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Q8Params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* sg = smem_raw + (smem_base - smem_u32(smem_raw));
-    const SmemLayout L = q8_layout(p.KT, p.nblk, p.RS, p.BS, p.abuf, p.dw_tabs, p.staged);
+    const SmemLayout L = q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged);
     const uint32_t bar0 = smem_base + L.bar_off;
     auto raw_full = [&](int s) { return bar0 + 8u * s; };
     auto raw_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
     auto w_full = [&](int s) { return bar0 + 8u * (2 * kMaxStages + s); };
     auto w_empty = [&](int s) { return bar0 + 8u * (3 * kMaxStages + s); };
-    auto a_full = [&](int buf, int k) { return bar0 + 8u * (4 * kMaxStages + buf * kMaxKT + k); };
-    auto a_empty = [&](int buf, int k) { return bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + buf * kMaxKT + k); };
+    auto a_full = [&](int slot) { return bar0 + 8u * (4 * kMaxStages + slot); };                  // slot < 2 * kMaxKT
+    auto a_empty = [&](int slot) { return bar0 + 8u * (4 * kMaxStages + 2 * kMaxKT + slot); };
     auto t_full = [&](int s) { return bar0 + 8u * (4 * kMaxStages + 4 * kMaxKT + s); };
     auto t_empty = [&](int s) { return bar0 + 8u * (4 * kMaxStages + 4 * kMaxKT + 4 + s); };
     auto epi_done = [&](int b) { return bar0 + 8u * (4 * kMaxStages + 4 * kMaxKT + 8 + b); };
@@ -179,18 +249,17 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     __half* da_s = reinterpret_cast<__half*>(sg + L.da_off);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kQuantWarps = QW, kFirstQuantWarp = Roles<QW>::kFirstQuantWarp;
+    constexpr int kTmaWarp = Roles<QW>::kTmaWarp, kMmaWarp = Roles<QW>::kMmaWarp, kThreads = Roles<QW>::kThreads;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), kQuantWarps);
             mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1);
         }
-        for (int k = 0; k < kMaxKT; ++k) {
-            int nb = p.nblk - 4 * k; nb = nb < 0 ? 0 : (nb > 4 ? 4 : nb);
-            for (int b = 0; b < 2; ++b) {
-                mbar_init(a_full(b, k), nb > 0 ? kQuantWarps * nb : 1);
-                mbar_init(a_empty(b, k), 1);
-            }
+        for (int k = 0; k < 2 * kMaxKT; ++k) {
+            mbar_init(a_full(k), kQuantWarps * 4);       // four arrivals per quantizer warp and K step (a short last step pads)
+            mbar_init(a_empty(k), 1);
         }
         for (int s = 0; s < 4; ++s) { mbar_init(t_full(s), 1); mbar_init(t_empty(s), kEpiWarps); }
         mbar_init(epi_done(0), kEpiWarps); mbar_init(epi_done(1), kEpiWarps);
@@ -198,8 +267,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         *cta_abort = 0;
         fence_barrier_init();
     }
-    if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
-    if (warp == 0 && lane == 0) { prefetch_tmap(&tmX); prefetch_tmap(&tmW); }
+    if (warp == kMmaWarp) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
+    if (warp == kTmaWarp && lane == 0) { prefetch_tmap(&tmX); prefetch_tmap(&tmW); }
     for (int i = threadIdx.x; i < 1024; i += kThreads) reinterpret_cast<uint32_t*>(sg + L.c_off)[i] = 0x80808080u;
     fence_proxy_async_smem();
     tc_fence_before();
@@ -209,7 +278,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
     const int total_items = p.m_tiles * p.groups;
 
-    if (warp == 0) {
+    if (warp == kTmaWarp) {
         // ---------------- both TMA streams, one thread: activations (128 x 32 fp32 per quant block) and
         // weights (128 rows x 128 int8 per K step).  Each ring is served as soon as its next stage is free.
         if (lane == 0) {
@@ -258,7 +327,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issue: one instruction per quant block, each into a fresh TMEM slot ----------
         if (lane == 0) {
             const uint32_t idesc = make_idesc(2, 1, 1, 0, 0, 128, 128);
@@ -270,24 +339,25 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const uint32_t idesc_off = make_idesc(2, 0, 0, 0, 0, 128, 128);
             const uint64_t dc = make_smem_desc(smem_base + L.c_off, 128, 256, 0);
             uint32_t bcnt = 0, n_it = 0, w_ph = 0; int w_s = 0; bool ok = true;
+            uint32_t a_slot0 = 0, a_par0 = 0;           // slot and parity of K step 0 of the current item
             TR_DECL;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
                 const int g = item % p.groups;
                 const int nb0 = g * p.blocks_per_group;
                 const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
-                const int buf = (p.abuf == 2) ? static_cast<int>(n_it & 1u) : 0;
-                const uint32_t a_par = ((p.abuf == 2) ? (n_it >> 1) : n_it) & 1u;
                 for (int nb = nb0; nb < nb1 && ok; ++nb) {
-                    for (int ks = 0; ks < p.KT; ++ks) {
+                    uint32_t a_slot = a_slot0, a_par = a_par0;              // A slots form a ring over (item, K step)
+                    for (int ks = 0; ks < p.KT; ++ks, a_slot = (a_slot + 1 == static_cast<uint32_t>(p.AR)) ? 0u : a_slot + 1u,
+                                                    a_par ^= (a_slot == 0u) ? 1u : 0u) {
                         TR(0);
                         if (nb == nb0) {
-                            if (!mbar_wait(a_full(buf, ks), a_par, cta_abort, p.err, 0x1301)) { ok = false; break; }
+                            if (!mbar_wait(a_full(a_slot), a_par, cta_abort, p.err, 0x1301)) { ok = false; break; }
                         }
                         TR(1);
                         if (!mbar_wait(w_full(w_s), w_ph, cta_abort, p.err, 0x1302)) { ok = false; break; }
                         TR(2);
                         tc_fence_after();
-                        const uint64_t da = da0 + static_cast<uint64_t>((buf * p.KT + ks) * (kTile >> 4));
+                        const uint64_t da = da0 + static_cast<uint64_t>(a_slot * (kTile >> 4));
                         const uint64_t db = db0 + static_cast<uint64_t>(w_s * (kTile >> 4));
                         const int nstep = min(4, p.nblk - 4 * ks);
                         if (nstep == 4 && (bcnt & 3u) == 0u) {
@@ -318,51 +388,55 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                         if (!ok) break;
                         umma_commit(w_empty(w_s));
                         if (++w_s == p.BS) { w_s = 0; w_ph ^= 1u; }
-                        if (nb == nb1 - 1) umma_commit(a_empty(buf, ks));
+                        if (nb == nb1 - 1) umma_commit(a_empty(a_slot));
                     }
                 }
+                for (int ks = 0; ks < p.KT; ++ks) { if (++a_slot0 == static_cast<uint32_t>(p.AR)) { a_slot0 = 0; a_par0 ^= 1u; } }
             }
             TR(0);
             TR_FLUSH(0, true);
         }
         __syncwarp();
-    } else if (warp < kFirstEpiWarp) {
+    } else if (warp >= kFirstQuantWarp && warp < kFirstQuantWarp + kQuantWarps) {
         // ---------------- quantizers: warp 2 owns token rows 0-63 of the tile, warp 3 rows 64-127 ------------
-        const int row0 = (warp - kFirstQuantWarp) * 64 + lane;
+        const int row0 = (warp - kFirstQuantWarp) * (128 / kQuantWarps) + lane;
         uint32_t n_it = 0, x_ph = 0; int x_s = 0; bool ok = true;
+        uint32_t a_slot = 0, a_par = 0;                 // ring position of the K step being quantized
         TR_DECL;
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
             TR(0);
             if (n_it >= 2) {    // the scale table of this parity was last read by the epilogue two items ago
                 if (!mbar_wait(epi_done(n_it & 1u), ((n_it >> 1) - 1u) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
             }
-            const int buf = (p.abuf == 2) ? static_cast<int>(n_it & 1u) : 0;
-            const uint32_t a_par = ((p.abuf == 2) ? (n_it >> 1) : n_it) & 1u;
             __half* da_w = da_s + (n_it & 1u) * p.nblk * 128;
             TR(1);
             for (int kb = 0; kb < p.nblk; ++kb) {
-                const int ks = kb >> 2;
                 TR(0);
-                if ((kb & 3) == 0) {     // the tensor core must have finished with this K step of the previous user
-                    if (!mbar_wait(a_empty(buf, ks), a_par ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
+                if ((kb & 3) == 0) {     // the tensor core must have finished with the previous user of this slot
+                    if (!mbar_wait(a_empty(a_slot), a_par ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
                 }
                 TR(2);
                 if (!mbar_wait(raw_full(x_s), x_ph, cta_abort, p.err, 0x1503)) { ok = false; break; }
                 TR(3);
                 const uint8_t* raw = sg + L.raw_off + x_s * kTile;
-                uint8_t* at = sg + L.a_off + (buf * p.KT + ks) * kTile;
+                uint8_t* at = sg + L.a_off + a_slot * kTile;
                 const int c0 = (kb & 3) * 2;
                 float d0 = 1.0f, d1 = 1.0f;
                 if (!(PPML_Q8_ABL & 2)) {
-                    d0 = quantize_row(raw, at, row0, c0);
-                    d1 = quantize_row(raw, at, row0 + 32, c0);
+                    if (kQuantWarps == 4) d0 = quantize_row(raw, at, row0, c0);
+                    else quantize_rows2(raw, at, row0, c0, d0, d1);
                 }
                 da_w[kb * 128 + row0] = __float2half_rn(d0);
-                da_w[kb * 128 + row0 + 32] = __float2half_rn(d1);
+                if (kQuantWarps == 2) da_w[kb * 128 + row0 + 32] = __float2half_rn(d1);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(raw_empty(x_s)); mbar_arrive(a_full(buf, ks)); }
+                if (lane == 0) {
+                    mbar_arrive(raw_empty(x_s));
+                    mbar_arrive(a_full(a_slot));
+                    if (kb == p.nblk - 1) { for (int pad = (kb & 3) + 1; pad < 4; ++pad) mbar_arrive(a_full(a_slot)); }
+                }
                 if (++x_s == p.RS) { x_s = 0; x_ph ^= 1u; }
+                if ((kb & 3) == 3 || kb == p.nblk - 1) { if (++a_slot == static_cast<uint32_t>(p.AR)) { a_slot = 0; a_par ^= 1u; } }
                 TR(4);
             }
         }
@@ -556,7 +630,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == kMmaWarp) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 }  // namespace
@@ -598,19 +672,26 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     // two rings, and an option is dropped when fewer than five stages would remain.
     const int budget = 226 * 1024;
     const int total_items = p.m_tiles * p.groups;
-    p.abuf = (p.KT <= 2 && total_items > sms) ? 2 : 1;
+    int abuf = (p.KT <= 2 && total_items > sms) ? 2 : 1;
+    const bool ring = p.blocks_per_group == 1 && p.KT >= 3;    // every item has one column block: A is consumed once
+    p.AR = ring ? 3 : p.KT * abuf;
     p.dw_tabs = (p.n_blocks * p.nblk * 512 <= 32 * 1024) ? p.n_blocks : 1;
     p.staged = p.vec_ok ? 1 : 0;
     auto stages_for = [&]() {
-        return (budget - (static_cast<int>(q8_layout(p.KT, p.nblk, 0, 0, p.abuf, p.dw_tabs, p.staged).total) + 1024)) / kTile;
+        return (budget - (static_cast<int>(q8_layout(p.AR, p.nblk, 0, 0, p.dw_tabs, p.staged).total) + 1024)) / kTile;
     };
     if (stages_for() < 5 && p.dw_tabs > 1) p.dw_tabs = 1;
-    if (stages_for() < 5 && p.abuf > 1) p.abuf = 1;
+    if (stages_for() < 5 && abuf > 1) { abuf = 1; p.AR = p.KT; }
     if (stages_for() < 4) p.staged = 0;
     int stages = stages_for();
     if (stages < 3) return ST_UNSUPPORTED_PATH;
     if (stages > 2 * kMaxStages) stages = 2 * kMaxStages;
-    p.BS = stages / 2; p.RS = stages - p.BS;        // the activation ring carries the HBM stream: it gets the odd stage
+    if (p.blocks_per_group == 1) {
+        // the weights of an item are one pass over K: two stages suffice, the activation ring carries the HBM stream
+        p.BS = 2; p.RS = stages - 2;
+    } else {
+        p.BS = stages / 2; p.RS = stages - p.BS;
+    }
     if (p.RS > kMaxStages) p.RS = kMaxStages;
     if (p.BS > kMaxStages) p.BS = kMaxStages;
     const __half* Wd = reinterpret_cast<const __half*>(static_cast<const int8_t*>(W) + static_cast<size_t>(M) * p.nblk * 32);
@@ -620,20 +701,22 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     if (!make_tmap_3d(&tmX, TmaType::F32, X, K, N, 1, static_cast<uint64_t>(K) * 4, 0, 32, 128, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
 
-    const int smem = static_cast<int>(q8_layout(p.KT, p.nblk, p.RS, p.BS, p.abuf, p.dw_tabs, p.staged).total) + 1024;
+    const int smem = static_cast<int>(q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total) + 1024;
     static int configured_smem[64] = {0};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured_smem[dev] < smem) {
-        if (cudaFuncSetAttribute(umma_q8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(umma_q8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+        if (cudaFuncSetAttribute(umma_q8_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(umma_q8_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(umma_q8_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
             cudaGetLastError();
             return ST_LAUNCH;
         }
         configured_smem[dev] = 227 * 1024;
     }
     const int grid = total_items < sms ? total_items : sms;
-    if (sumi_out != nullptr) umma_q8_kernel<true><<<grid, kThreads, smem, st>>>(tmX, tmW, p);
-    else umma_q8_kernel<false><<<grid, kThreads, smem, st>>>(tmX, tmW, p);
+    if (sumi_out != nullptr) umma_q8_kernel<true, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, p);
+    else if (p.blocks_per_group == 1) umma_q8_kernel<false, 4><<<grid, Roles<4>::kThreads, smem, st>>>(tmX, tmW, p);
+    else umma_q8_kernel<false, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
