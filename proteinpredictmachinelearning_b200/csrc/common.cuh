@@ -80,16 +80,13 @@ __device__ __forceinline__ bool mbar_test_suspend(uint32_t bar, uint32_t parity,
 // through to the common exit, which still frees TMEM.
 constexpr long long kWaitCycles = 3000000000LL;   // about 1.5 s at the maximum SM clock
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort, int* err, int site) {
-    if (mbar_test(bar, parity)) return true;
-
+// The polling loop lives in a function of its own (not inlined): a wait that succeeds at once costs one
+// instruction and a branch at the call site, and the loop, the clock reads and the abort path do not bloat
+// every role loop.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* cta_abort, int* err, int site) {
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
-#ifdef PPML_WAIT_HINT_NS
-        if (mbar_test_suspend(bar, parity, PPML_WAIT_HINT_NS)) return true;
-#else
         if (mbar_test(bar, parity)) return true;
-#endif
         if ((it & 63u) == 0u) {
             if (*cta_abort) return false;
             if (clock64() - t0 > kWaitCycles) break;
@@ -100,6 +97,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     err[1] = site;
     __threadfence();
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* cta_abort, int* err, int site) {
+    if (mbar_test(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, cta_abort, err, site);
 }
 
 // Same policy for roles that usually wait long (producers running ahead of a slow consumer): backs
