@@ -253,6 +253,18 @@ __device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) {
     return (r >> 3) * 1024u + (r & 7u) * 128u + ((c ^ (r & 7u)) << 4);
 }
 
+// ---- shared-memory loads through 32-bit shared addresses (one address register, no generic-pointer math) ----
+__device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ uint16_t lds_u16(uint32_t saddr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(saddr));
+    return v;
+}
+
 // ---- packed fp32 pairs (one issue slot for two lanes of add / mul / fma) ------------------------
 __device__ __forceinline__ uint64_t pack2(float a, float b) {
     uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r;

@@ -468,12 +468,12 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const int nb0 = g * p.blocks_per_group;
             const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
             const int tok = mt * 128 + row;
-            const __half* da_row = da_s + (n_it & 1u) * p.nblk * 128 + row;
+            const uint32_t da_a0 = smem_base + L.da_off + ((n_it & 1u) * p.nblk * 128 + row) * 2;      // this row's d_a, block 0
             for (int nb = nb0; nb < nb1 && ok; ++nb) {
                 // weight scales as fp32 [nblk][128] per column block.  When the tables of all column blocks fit
                 // they were staged once before the first item; otherwise this block's table is refilled here:
                 // wait until every epilogue warp has finished with the previous one, fill, publish.
-                const float* dw_tab = dw_s + (p.dw_tabs > 1 ? nb : 0) * p.nblk * 128 + cg * 32;
+                const uint32_t dw_a0 = smem_base + L.dw_off + ((p.dw_tabs > 1 ? nb : 0) * p.nblk * 128 + cg * 32) * 4;
                 if (!dw_resident) {
                     if (!mbar_wait(dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
                     for (int i = etid; i < p.nblk * 128; i += 32 * kEpiWarps) {
@@ -495,7 +495,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 //   acc = fma(g, d_w * 2^49, acc)                                                = acc + s * d_a * d_w
                 // The per-thread scalar d_a goes first so that only the second fma needs a table value.
                 auto rescale = [&](const uint32_t (&v)[16], int h, int kb, float da, float dc) {
-                    const float4* dwp = reinterpret_cast<const float4*>(dw_tab + kb * 128 + h * 16);
+                    const uint32_t dwp = dw_a0 + (kb * 128 + h * 16) * 4;
                     if (SUMI && tok < p.Ntok) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -511,7 +511,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     }
 #pragma unroll
                     for (int j4 = 0; j4 < 4; ++j4) {
-                        const float4 w4 = dwp[j4];
+                        const float4 w4 = lds_f4(dwp + j4 * 16);
                         acc[h * 16 + j4 * 4 + 0] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 0]), da, dc), w4.x, acc[h * 16 + j4 * 4 + 0]);
                         acc[h * 16 + j4 * 4 + 1] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 1]), da, dc), w4.y, acc[h * 16 + j4 * 4 + 1]);
                         acc[h * 16 + j4 * 4 + 2] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 2]), da, dc), w4.z, acc[h * 16 + j4 * 4 + 2]);
@@ -529,7 +529,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 // one block: `slot` holds it, `nslot` / `npar` are slot and parity of the block after it
                 auto one_block = [&](int kb, uint32_t slot, uint32_t nslot, uint32_t npar, bool has_next) -> bool {
                     TR(0);
-                    const float da = __half2float(da_row[kb * 128]) * kTwo100;
+                    const float da = __half2float(__ushort_as_half(lds_u16(da_a0 + kb * 256))) * kTwo100;
                     const float dc = da * __uint_as_float(0x80080000u);      // -2^-130 * (d_a * 2^100)
                     TR(5);
                     tmem_ld_wait();
