@@ -67,6 +67,24 @@ def test_mul_mat_tf32_umma(oracle, M, K, N, bias):
     assert cases.rel_err(got, ref) <= TOL_TF32
 
 
+# the (M, K, N) shapes that carry most OP_MUL_MAT executions of the dev-size forward (L = 51, MSA depth 8), incl. the
+# SE3 radial MLPs with K = 33 (row pitch not a multiple of 16 bytes) and the skinny N = 8 / 32 heads
+CENSUS_SHAPES = [(2601, 128, 256), (2601, 128, 128), (2601, 256, 128), (408, 256, 256), (2550, 32, 1024), (2601, 64, 128),
+                 (2550, 32, 256), (408, 256, 1024), (408, 1024, 256), (2550, 32, 32), (2550, 33, 32), (2601, 128, 8)]
+
+
+@pytest.mark.parametrize("M,K,N", CENSUS_SHAPES)
+def test_mul_mat_dev_forward_census(oracle, M, K, N):
+    """Default dispatch (what the executor gets): tensor cores where TMA can address the operands, CUDA cores otherwise."""
+    a, b, bi = cases.mul_mat_case(M, K, N, seed=1, bias=True)
+    ref = oracle.mul_mat_f32(a, b, bi)
+    assert cases.rel_err(host(ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_AUTO)), ref) <= TOL_TF32
+    assert cases.rel_err(host(ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_SIMT)), ref) <= TOL_FP32
+    a16, b16 = dev(a).bfloat16(), dev(b).bfloat16()
+    ref16 = oracle.mul_mat_f32(host(a16.float()), host(b16.float()), bi)
+    assert cases.rel_err(host(ops.mul_mat_16(a16, b16, dev(bi), path=PATH_AUTO)), ref16) <= TOL_FP32
+
+
 def test_mul_mat_umma_rejects_unaligned_k_and_auto_falls_back(oracle):
     a, b, bi = cases.mul_mat_case(255, 33, 32, seed=1)
     with pytest.raises(RuntimeError):
