@@ -3,14 +3,15 @@
 //   O = softmax(scale * Q K^T + bias) V,  denominator (l + eps),  LSE = m + log(l + eps)
 //
 // One CTA = one (batch, head, 128-query tile); keys are walked in tiles of 64.  Two CTAs share an SM (256 TMEM
-// columns, about 100 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads
-// and tensor work.
-//   warp 0      TMA: Q tile once; per key tile the bias tile (128 rows x 64 keys fp32, when a bias is given), K (64 keys x 32 floats, K-major, 128-byte swizzle) and V (the same
+// columns, about 105 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads and
+// tensor work.  (Key tiles of 32 with three CTAs per SM, -DPPML_ATTN_BN=32, measured 5-15 % slower.)
+//   warp 0      TMA: Q tile once; per key tile the bias tile (128 rows x kBN keys fp32, when a bias is
+//               given), K (kBN keys x 32 floats, K-major, 128-byte swizzle) and V (the same
 //               box in the 32-byte-chunk swizzle: V[key][d] has d contiguous, which is the "row index contiguous"
 //               form of the B operand of P V, so V needs no transposition); fp32 -> tf32 rounding by the TMA unit
-//   warp 1      MMA issue: S = Q K^T (four K = 8 tf32 MMAs, N = 64) into one of two TMEM S buffers,
-//               then O_part = P V (eight K = 8 MMAs, N = 32) into one of two TMEM O buffers
-//   warps 2-5   softmax, one thread per query row: the 64 scores of the tile from TMEM into registers, scale +
+//   warp 1      MMA issue: S = Q K^T (four K = 8 tf32 MMAs, N = kBN) into one of two TMEM S buffers,
+//               then O_part = P V (kBN / 8 MMAs of K = 8, N = 32) into one of two TMEM O buffers
+//   warps 2-5   softmax, one thread per query row: the scores of the tile from TMEM into registers, scale +
 //               bias + mask, running max / sum, P (rounded to tf32) into shared memory as the next MMA's K-major
 //               A operand, then o = alpha * o + O_part in fp32 registers, one tile late
 // Every wait is bounded; rows past L and keys past Lk are zero-filled by TMA and masked.
@@ -24,12 +25,24 @@ namespace ppml_b200 {
 namespace {
 
 constexpr int kD = 32;                       // head dim handled here
-constexpr int kBM = 128, kBN = 64;           // query tile, key tile
+#ifndef PPML_ATTN_BN
+#define PPML_ATTN_BN 64
+#endif
+constexpr int kBM = 128, kBN = PPML_ATTN_BN;  // query tile, key tile (32: three CTAs per SM, 64: two)
 constexpr int kTileQ = 128 * 128;            // bytes: 128 rows x 32 floats
-constexpr int kTileKV = kBN * 128;           // bytes: 64 keys x 32 floats
+constexpr int kTileKV = kBN * 128;           // bytes: kBN keys x 32 floats
 constexpr int kTileP = (kBN / 32) * kTileQ;  // P: 128 rows x 64 floats as two 32-float swizzle atoms
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 256;          // S buffers at columns 0 and 64, O_part buffers at 128 and 160
+constexpr uint32_t kTmemCols = (kBN == 32) ? 128 : 256;   // S buffers at columns 0 and kBN, O_part buffers at 2 kBN and 2 kBN + 32
+constexpr int kCtasPerSm = (kBN == 32) ? 3 : 2;
+
+// 2^x on the transcendental unit (about 2 ulp); results below the normal range flush to 0, 2^-inf = 0
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r;
+}
 
 struct AttnParams {
     int B, H, L, Lk;
@@ -48,13 +61,13 @@ constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kTileQ;               // 1 stage (free again as soon as S = Q K^T has been computed)
 constexpr int kOffV = kOffK + kTileKV;              // 2 stages
 constexpr int kOffP = kOffV + 2 * kTileKV;          // 1 buffer; after the last tile it serves as the output
-constexpr int kOffStage = kOffP;                    //   transposition buffer (4 warps x 32 rows x 144 B)
+constexpr int kOffStage = kOffP;                    //   transposition buffer (4 warps x 32 rows x 128 B, XOR-swizzled)
 constexpr int kOffB = kOffP + kTileP;               // bias tile, same layout as P (two 32-key swizzle atoms)
 constexpr int kOffBar = kOffB + kTileP;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
-static_assert(4 * 32 * 144 <= kTileP, "output staging must fit into the P buffer");
+static_assert(4 * 32 * 128 <= kTileP, "output staging must fit into the P buffer");
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -115,8 +128,9 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (p.bias != nullptr) {
                     if (!mbar_wait(b_empty, (j & 1u) ^ 1u, cta_abort, p.err, 0x2103)) break;
                     mbar_arrive_expect_tx(b_full, kTileP);
-                    tma_load_3d(sb + kOffB, &tmB, b_full, j * kBN, brow0, bbatch);
-                    tma_load_3d(sb + kOffB + kTileQ, &tmB, b_full, j * kBN + 32, brow0, bbatch);
+#pragma unroll
+                    for (int a = 0; a < kBN / 32; ++a)
+                        tma_load_3d(sb + kOffB + a * kTileQ, &tmB, b_full, j * kBN + 32 * a, brow0, bbatch);
                 }
                 if (!mbar_wait(k_empty(0), (j & 1u) ^ 1u, cta_abort, p.err, 0x2101)) break;
                 mbar_arrive_expect_tx(k_full(0), kTileKV);
@@ -163,7 +177,7 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     const uint64_t dp = make_smem_desc(sb + kOffP + a * kTileQ, 16, 1024, kLayoutSW128);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma<MmaKind::TF32>(tmem_base + 128 + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
+                        umma<MmaKind::TF32>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
                 }
                 umma_commit(p_empty);
                 umma_commit(v_empty(s));
