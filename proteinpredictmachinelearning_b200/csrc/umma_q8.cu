@@ -360,18 +360,23 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                         const uint64_t da = da0 + static_cast<uint64_t>(a_slot * (kTile >> 4));
                         const uint64_t db = db0 + static_cast<uint64_t>(w_s * (kTile >> 4));
                         const int nstep = min(4, p.nblk - 4 * ks);
-                        if (nstep == 4 && (bcnt & 3u) == 0u) {
-                            // a full K step starting at slot 0: slots, barriers and descriptors are compile-time offsets
+                        if ((p.nblk & 3) == 0) {
+                            // K a multiple of 128: every K step is four blocks on slots 0..3, handed over in pairs
+                            // (slots 0-1 behind barrier 0, slots 2-3 behind barrier 2): half as many handshakes, and
+                            // slots, barriers and descriptors are compile-time offsets
                             const uint32_t par = ((bcnt >> 2) & 1u) ^ 1u;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
+                            for (int g = 0; g < 2; ++g) {
                                 TR(0);
-                                if (!mbar_wait(t_empty(j), par, cta_abort, p.err, 0x1303)) { ok = false; break; }
+                                if (!mbar_wait(t_empty(2 * g), par, cta_abort, p.err, 0x1303)) { ok = false; break; }
                                 TR(3);
                                 tc_fence_after();
-                                umma<MmaKind::I8>(tmem_base + j * 128u, da + 2u * j, db + 2u * j, idesc, 0u);
-                                umma<MmaKind::I8>(tmem_base + j * 128u, dc, dc, idesc_off, 1u);
-                                umma_commit(t_full(j));
+#pragma unroll
+                                for (int j = 2 * g; j < 2 * g + 2; ++j) {
+                                    umma<MmaKind::I8>(tmem_base + j * 128u, da + 2u * j, db + 2u * j, idesc, 0u);
+                                    umma<MmaKind::I8>(tmem_base + j * 128u, dc, dc, idesc_off, 1u);
+                                }
+                                umma_commit(t_full(2 * g));
                             }
                             bcnt += 4;
                         } else
@@ -526,8 +531,11 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 TR(1);
                 tc_fence_after();
                 tmem_ld16(taddr0 + (bcnt & 3u) * 128u, va);
-                // one block: `slot` holds it, `nslot` / `npar` are slot and parity of the block after it
-                auto one_block = [&](int kb, uint32_t slot, uint32_t nslot, uint32_t npar, bool has_next) -> bool {
+                // One block held by `slot`; the next block's first half is loaded from `nslot` in the middle.  `rel_bar`
+                // (when not 0) is arrived on once this block is in registers, `acq_bar` (when not 0) is waited for
+                // with parity `acq_par` before the next block is touched.
+                auto one_block = [&](int kb, uint32_t slot, uint32_t nslot, bool has_next, uint32_t rel_bar, uint32_t acq_bar,
+                                     uint32_t acq_par) -> bool {
                     TR(0);
                     const float da = __half2float(__ushort_as_half(lds_u16(da_a0 + kb * 256))) * kTwo100;
                     const float dc = da * __uint_as_float(0x80080000u);      // -2^-130 * (d_a * 2^100)
@@ -540,14 +548,18 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     TR(3);
                     tmem_ld_wait();
                     TR(2);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(t_empty(slot));       // the slot may take its next block already
+                    if (rel_bar != 0u) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(rel_bar);         // the slot(s) may take their next blocks already
+                    }
                     TR(6);
                     if (has_next) {
-                        if (!mbar_wait(t_full(nslot), npar, cta_abort, p.err, 0x1401)) return false;
-                        TR(1);
-                        tc_fence_after();
+                        if (acq_bar != 0u) {
+                            if (!mbar_wait(acq_bar, acq_par, cta_abort, p.err, 0x1401)) return false;
+                            TR(1);
+                            tc_fence_after();
+                        }
                         tmem_ld16(taddr0 + nslot * 128u, va);
                         TR(5);
                     }
@@ -555,19 +567,21 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     TR(3);
                     return true;
                 };
-                if ((p.nblk & 3) == 0 && (bcnt & 3u) == 0u) {
-                    // groups of four blocks on slots 0..3: slot numbers and TMEM offsets are compile-time constants
+                if ((p.nblk & 3) == 0) {
+                    // groups of four blocks on slots 0..3, handed over in pairs; slot numbers and TMEM offsets are
+                    // compile-time constants
                     for (int kb0 = 0; kb0 < p.nblk && ok; kb0 += 4, bcnt += 4) {
                         const uint32_t par = (bcnt >> 2) & 1u;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (!one_block(kb0 + j, j, (j + 1) & 3, j == 3 ? (par ^ 1u) : par, kb0 + j + 1 < p.nblk)) { ok = false; break; }
-                        }
+                        const bool more = kb0 + 4 < p.nblk;
+                        if (!one_block(kb0 + 0, 0, 1, true, 0u, 0u, 0u) ||
+                            !one_block(kb0 + 1, 1, 2, true, t_empty(0), t_full(2), par) ||
+                            !one_block(kb0 + 2, 2, 3, true, 0u, 0u, 0u) ||
+                            !one_block(kb0 + 3, 3, 0, more, t_empty(2), t_full(0), par ^ 1u)) { ok = false; break; }
                     }
                 } else {
                     for (int kb = 0; kb < p.nblk; ++kb, ++bcnt) {
                         const uint32_t nx = bcnt + 1u;
-                        if (!one_block(kb, bcnt & 3u, nx & 3u, (nx >> 2) & 1u, kb + 1 < p.nblk)) { ok = false; break; }
+                        if (!one_block(kb, bcnt & 3u, nx & 3u, kb + 1 < p.nblk, t_empty(bcnt & 3u), t_full(nx & 3u), (nx >> 2) & 1u)) { ok = false; break; }
                     }
                 }
                 if (!ok) break;
