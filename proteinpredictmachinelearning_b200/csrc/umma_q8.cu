@@ -531,18 +531,22 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 TR(1);
                 tc_fence_after();
                 tmem_ld16(taddr0 + (bcnt & 3u) * 128u, va);
+                uint16_t da_raw = lds_u16(da_a0);                     // d_a of block 0 of this row
                 // One block held by `slot`; the next block's first half is loaded from `nslot` in the middle.  `rel_bar`
                 // (when not 0) is arrived on once this block is in registers, `acq_bar` (when not 0) is waited for
                 // with parity `acq_par` before the next block is touched.
                 auto one_block = [&](int kb, uint32_t slot, uint32_t nslot, bool has_next, uint32_t rel_bar, uint32_t acq_bar,
                                      uint32_t acq_par) -> bool {
                     TR(0);
-                    const float da = __half2float(__ushort_as_half(lds_u16(da_a0 + kb * 256))) * kTwo100;
+                    const float da = __half2float(__ushort_as_half(da_raw)) * kTwo100;
                     const float dc = da * __uint_as_float(0x80080000u);      // -2^-130 * (d_a * 2^100)
                     TR(5);
                     tmem_ld_wait();
                     TR(2);
                     tmem_ld16(taddr0 + slot * 128u + 16u, vb);
+                    // the next block's scale, in flight during the math; only when that block is already known to be
+                    // complete (same pair): its scale is written by the quantizer just before its MMA can be issued
+                    if (has_next && acq_bar == 0u) da_raw = lds_u16(da_a0 + (kb + 1) * 256);
                     TR(5);
                     rescale(va, 0, kb, da, dc);
                     TR(3);
@@ -559,6 +563,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             if (!mbar_wait(acq_bar, acq_par, cta_abort, p.err, 0x1401)) return false;
                             TR(1);
                             tc_fence_after();
+                            da_raw = lds_u16(da_a0 + (kb + 1) * 256);
                         }
                         tmem_ld16(taddr0 + nslot * 128u, va);
                         TR(5);
