@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1]): the Q8 block-quantized mul_mat sweep -- weights W[N,K] ~
+Workload (the reference's Q8 benchmark configuration): the Q8 block-quantized mul_mat sweep -- weights W[N,K] ~
 N(0, 0.02) quantized to int8 blocks of 32 with an fp16 scale (planar Q8_0R), activations X[M,K] ~ N(0,1)
 quantized on the fly; K in {128, 256, 1024}, N in {128, 256, 512, 1024}, M in {408, 2601, 65536}; seed 2.
 One step = one pass over all 36 shapes.  `value` is the whole-job rate with inputs resident in HBM;

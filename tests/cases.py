@@ -1,5 +1,5 @@
 """Seeded synthetic inputs shared by the golden-fixture generator and the parity tests.  The shapes
-and value distributions are those BASELINE.json's configs give (dev-size forward shapes, the Q8
+and value distributions are those of the benchmark configurations (dev-size forward shapes, the Q8
 sweep, axial attention, pair-track contractions), scaled down where a CPU checker must finish in
 seconds."""
 import numpy as np

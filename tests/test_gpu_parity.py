@@ -2,9 +2,9 @@
 
 Tolerances (normalised error = max|got-ref| / max|ref|):
   CUDA-core fp32 kernels        1e-5   (same summation order, FMA contraction only)
-  tf32 tensor-core kernels      1e-3   (BASELINE: fp32/tf32 within 1e-3)
+  tf32 tensor-core kernels      1e-3   (the required bound for fp32 / tf32)
   fp16 / bf16 operand kernels   1e-5 against the checker fed the same 16-bit operands
-                                1e-2 against the fp32 product (BASELINE: bf16 within 1e-2)
+                                1e-2 against the fp32 product (the required bound for bf16)
   Q8: quantized bytes, scales and int32 block sums bit-exact; fp32 result 1e-5
 """
 import os
@@ -216,7 +216,7 @@ def test_mul_mat_q8_weight_layouts(oracle, wtype, c_trans):
 
 
 def test_mul_mat_q8_full_size_property():
-    """M = 65536 tokens (BASELINE sweep size): tensor-core and dp4a paths must agree exactly on the
+    """M = 65536 tokens (the sweep's largest size): tensor-core and dp4a paths must agree exactly on the
     block sums' consequence -- the fp32 outputs agree to rounding -- and a row permutation of X
     permutes the rows of C."""
     g = torch.Generator(device="cuda").manual_seed(2)
