@@ -58,21 +58,25 @@ struct AttnParams {
 
 // smem map (offsets from the 1024-aligned base); two CTAs per SM leave about 113 KB each
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kTileQ;               // 1 stage (free again as soon as S = Q K^T has been computed)
-constexpr int kOffV = kOffK + kTileKV;              // 2 stages
+constexpr int kOffK = kOffQ + kTileQ;               // 2 stages
+constexpr int kOffV = kOffK + 2 * kTileKV;          // 2 stages
 constexpr int kOffP = kOffV + 2 * kTileKV;          // 1 buffer; after the last tile it serves as the output
 constexpr int kOffStage = kOffP;                    //   transposition buffer (4 warps x 32 rows x 128 B, XOR-swizzled)
 constexpr int kOffB = kOffP + kTileP;               // bias tile, same layout as P (two 32-key swizzle atoms)
 constexpr int kOffBar = kOffB + kTileP;
-constexpr int kSmemBytes = kOffBar + 256 + 1024;
+constexpr int kSmemBytes = kOffBar + 256;             // the dynamic shared memory is declared 1024-byte aligned: no slack
 static_assert(4 * 32 * 128 <= kTileP, "output staging must fit into the P buffer");
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, const AttnParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t sb = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* sg = smem_raw + (sb - smem_u32(smem_raw));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t sb = smem_u32(smem_raw);
+    uint8_t* sg = smem_raw;
+    if ((sb & 1023u) != 0u) {                    // the swizzled tiles need a 1024-byte aligned base: refuse to run otherwise
+        if (threadIdx.x == 0) { p.err[0] = ST_DEVICE_ABORT; p.err[1] = 0x2001; }
+        return;
+    }
     const uint32_t bar0 = sb + kOffBar;
     const uint32_t q_full = bar0;
     auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
@@ -132,9 +136,9 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     for (int a = 0; a < kBN / 32; ++a)
                         tma_load_3d(sb + kOffB + a * kTileQ, &tmB, b_full, j * kBN + 32 * a, brow0, bbatch);
                 }
-                if (!mbar_wait(k_empty(0), (j & 1u) ^ 1u, cta_abort, p.err, 0x2101)) break;
-                mbar_arrive_expect_tx(k_full(0), kTileKV);
-                tma_load_3d(sb + kOffK, &tmK, k_full(0), 0, j * kBN, bh);
+                if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) break;
+                mbar_arrive_expect_tx(k_full(s), kTileKV);
+                tma_load_3d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, bh);
                 if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2102)) break;
                 mbar_arrive_expect_tx(v_full(s), kTileKV);
                 tma_load_3d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, bh);
@@ -150,14 +154,14 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // while the tensor core finishes tile j
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-                if (!mbar_wait(k_full(0), j & 1u, cta_abort, p.err, 0x2202)) return false;
+                if (!mbar_wait(k_full(s), ph, cta_abort, p.err, 0x2202)) return false;
                 if (!mbar_wait(s_empty(s), ph ^ 1u, cta_abort, p.err, 0x2203)) return false;
                 tc_fence_after();
                 const uint64_t dq = make_smem_desc(sb + kOffQ, 16, 1024, kLayoutSW128);
-                const uint64_t dk = make_smem_desc(sb + kOffK, 16, 1024, kLayoutSW128);
+                const uint64_t dk = make_smem_desc(sb + kOffK + s * kTileKV, 16, 1024, kLayoutSW128);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) umma<MmaKind::TF32>(tmem_base + s * kBN, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
-                umma_commit(k_empty(0));
+                umma_commit(k_empty(s));
                 umma_commit(s_full(s));
                 return true;
             };
