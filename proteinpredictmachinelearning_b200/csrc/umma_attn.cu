@@ -6,7 +6,7 @@
 // columns, about 105 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads and
 // tensor work.  (Key tiles of 32 with three CTAs per SM, -DPPML_ATTN_BN=32, measured 5-15 % slower.)
 //   warp 0      TMA: Q tile once; per key tile the bias tile (128 rows x kBN keys fp32, when a bias is
-//               given), K (kBN keys x 32 floats, K-major, 128-byte swizzle) and V (the same
+//               given; it lands in the P buffer of that tile and is overwritten in place by P), K (kBN keys x 32 floats, K-major, 128-byte swizzle) and V (the same
 //               box in the 32-byte-chunk swizzle: V[key][d] has d contiguous, which is the "row index contiguous"
 //               form of the B operand of P V, so V needs no transposition); fp32 -> tf32 rounding by the TMA unit
 //   warp 1      MMA issue: S = Q K^T (four K = 8 tf32 MMAs, N = kBN) into one of two TMEM S buffers,
@@ -60,10 +60,11 @@ struct AttnParams {
 constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kTileQ;               // 2 stages
 constexpr int kOffV = kOffK + 2 * kTileKV;          // 2 stages
-constexpr int kOffP = kOffV + 2 * kTileKV;          // 1 buffer; after the last tile it serves as the output
-constexpr int kOffStage = kOffP;                    //   transposition buffer (4 warps x 32 rows x 128 B, XOR-swizzled)
-constexpr int kOffB = kOffP + kTileP;               // bias tile, same layout as P (two 32-key swizzle atoms)
-constexpr int kOffBar = kOffB + kTileP;
+constexpr int kOffP = kOffV + 2 * kTileKV;          // 2 buffers of bias-then-P: TMA puts the bias tile of key tile j into
+                                                    //   buffer j % 2 in the layout of P, every softmax thread reads its bias
+                                                    //   values and later writes its P values over them.  After the last tile
+constexpr int kOffStage = kOffP;                    //   buffer 0 is the output transposition buffer (4 x 32 rows x 128 B)
+constexpr int kOffBar = kOffP + 2 * kTileP;
 constexpr int kSmemBytes = kOffBar + 256;             // the dynamic shared memory is declared 1024-byte aligned: no slack
 static_assert(4 * 32 * 128 <= kTileP, "output staging must fit into the P buffer");
 
@@ -87,10 +88,11 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto s_empty = [&](int s) { return bar0 + 8u * (11 + s); };
     auto o_full = [&](int s) { return bar0 + 8u * (13 + s); };
     auto o_empty = [&](int s) { return bar0 + 8u * (15 + s); };
-    const uint32_t p_full = bar0 + 8u * 17, p_empty = bar0 + 8u * 18;
-    const uint32_t b_full = bar0 + 8u * 19, b_empty = bar0 + 8u * 20;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sg + kOffBar + 8 * 21);
-    volatile int* cta_abort = reinterpret_cast<volatile int*>(sg + kOffBar + 8 * 21 + 8);
+    auto p_full = [&](int s) { return bar0 + 8u * (17 + s); };
+    auto p_empty = [&](int s) { return bar0 + 8u * (19 + s); };
+    auto b_full = [&](int s) { return bar0 + 8u * (21 + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sg + kOffBar + 8 * 23);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(sg + kOffBar + 8 * 23 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qt = blockIdx.x % p.q_tiles;
@@ -108,9 +110,9 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
             mbar_init(s_full(s), 1); mbar_init(s_empty(s), 4);
             mbar_init(o_full(s), 1); mbar_init(o_empty(s), 4);
+            mbar_init(p_full(s), 4); mbar_init(p_empty(s), 1);
+            mbar_init(b_full(s), 1);
         }
-        mbar_init(p_full, 4); mbar_init(p_empty, 1);
-        mbar_init(b_full, 1); mbar_init(b_empty, 4);
         *cta_abort = 0;
         fence_barrier_init();
     }
@@ -130,11 +132,12 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int j = 0; j < k_tiles; ++j) {
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
                 if (p.bias != nullptr) {
-                    if (!mbar_wait(b_empty, (j & 1u) ^ 1u, cta_abort, p.err, 0x2103)) break;
-                    mbar_arrive_expect_tx(b_full, kTileP);
+                    // buffer s is free again once P(j - 2) V(j - 2) has read it
+                    if (!mbar_wait(p_empty(s), ph ^ 1u, cta_abort, p.err, 0x2103)) break;
+                    mbar_arrive_expect_tx(b_full(s), kTileP);
 #pragma unroll
                     for (int a = 0; a < kBN / 32; ++a)
-                        tma_load_3d(sb + kOffB + a * kTileQ, &tmB, b_full, j * kBN + 32 * a, brow0, bbatch);
+                        tma_load_3d(sb + kOffP + s * kTileP + a * kTileQ, &tmB, b_full(s), j * kBN + 32 * a, brow0, bbatch);
                 }
                 if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) break;
                 mbar_arrive_expect_tx(k_full(s), kTileKV);
@@ -169,7 +172,7 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int j = 0; j < k_tiles && ok; ++j) {
                 if (j + 1 < k_tiles) { if (!issue_s(j + 1)) { ok = false; break; } }
                 const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-                if (!mbar_wait(p_full, j & 1u, cta_abort, p.err, 0x2204)) { ok = false; break; }
+                if (!mbar_wait(p_full(s), ph, cta_abort, p.err, 0x2204)) { ok = false; break; }
                 if (!mbar_wait(v_full(s), ph, cta_abort, p.err, 0x2205)) { ok = false; break; }
                 if (!mbar_wait(o_empty(s), ph ^ 1u, cta_abort, p.err, 0x2206)) { ok = false; break; }
                 tc_fence_after();
@@ -178,12 +181,12 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW128Base32);
 #pragma unroll
                 for (int a = 0; a < kBN / 32; ++a) {
-                    const uint64_t dp = make_smem_desc(sb + kOffP + a * kTileQ, 16, 1024, kLayoutSW128);
+                    const uint64_t dp = make_smem_desc(sb + kOffP + s * kTileP + a * kTileQ, 16, 1024, kLayoutSW128);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
                         umma<MmaKind::TF32>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
                 }
-                umma_commit(p_empty);
+                umma_commit(p_empty(s));
                 umma_commit(v_empty(s));
                 umma_commit(o_full(s));
             }
