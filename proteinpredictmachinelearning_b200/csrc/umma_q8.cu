@@ -60,6 +60,7 @@ struct Q8Params {
     int m_tiles;               // token tiles
     int n_blocks;              // weight column blocks of 128
     int groups, blocks_per_group;
+    int flat;                  // 1: every CTA takes a contiguous range of (token tile, column block) units (see item_at)
     int RS, BS;                // ring depths
     int AR;                    // 16 KB slots of quantized A, used as a ring over (item, K step): KT = resident, 2 KT = resident
                                // and double-buffered across items, 3 = a short ring (items with a single column block)
@@ -277,18 +278,44 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
 
     const int total_items = p.m_tiles * p.groups;
+    // The k-th work item of this CTA: token tile `mt`, weight column blocks [nb0, nb1).  Two schedules:
+    //   strided: item = (token tile, column-block group), CTA c takes items c, c + grid, c + 2 grid, ...
+    //   flat:    the (token tile, column block) units in row-major order are cut into `grid` contiguous ranges of
+    //            equal length (to within one unit) and a range is walked token tile by token tile; a token tile cut
+    //            by a range boundary is quantized by both neighbours.  Balances the load when there are several,
+    //            but not a multiple of `grid`, token tiles per CTA.
+    // Every role walks the same sequence.
+    auto item_at = [&](uint32_t k, int& mt, int& nb0, int& nb1) -> bool {
+        if (p.flat) {
+            const long long nB = p.n_blocks, U = static_cast<long long>(p.m_tiles) * nB;
+            const long long u0 = U * blockIdx.x / gridDim.x, u1 = U * (blockIdx.x + 1) / gridDim.x;
+            if (u1 <= u0) return false;
+            mt = static_cast<int>(u0 / nB) + static_cast<int>(k);
+            const long long lo = max(u0, mt * nB), hi = min(u1, (mt + 1) * nB);
+            if (lo >= hi) return false;
+            nb0 = static_cast<int>(lo - mt * nB); nb1 = static_cast<int>(hi - mt * nB);
+            return true;
+        }
+        const long long item = blockIdx.x + static_cast<long long>(k) * gridDim.x;
+        if (item >= total_items) return false;
+        mt = static_cast<int>(item / p.groups);
+        nb0 = static_cast<int>(item % p.groups) * p.blocks_per_group;
+        nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
+        return true;
+    };
 
     if (warp == kTmaWarp) {
         // ---------------- both TMA streams, one thread: activations (128 x 32 fp32 per quant block) and
         // weights (128 rows x 128 int8 per K step).  Each ring is served as soon as its next stage is free.
         if (lane == 0) {
-            int x_item = blockIdx.x, x_kb = 0, x_s = 0; uint32_t x_ph = 0;
-            bool x_done = x_item >= total_items;
-            int x_row0 = x_done ? 0 : (x_item / p.groups) * 128;
-            int w_item = blockIdx.x, w_ks = 0, w_s = 0; uint32_t w_ph = 0;
-            bool w_done = w_item >= total_items;
-            int w_nb = 0, w_nb1 = 0;
-            if (!w_done) { w_nb = (w_item % p.groups) * p.blocks_per_group; w_nb1 = min(w_nb + p.blocks_per_group, p.n_blocks); }
+            uint32_t x_it = 0, w_it = 0;                 // item counters of the two streams
+            int x_kb = 0, x_s = 0; uint32_t x_ph = 0;
+            int x_mt = 0, x_nb0 = 0, x_nb1 = 0;
+            bool x_done = !item_at(x_it, x_mt, x_nb0, x_nb1);
+            int x_row0 = x_mt * 128;
+            int w_ks = 0, w_s = 0; uint32_t w_ph = 0;
+            int w_mt = 0, w_nb = 0, w_nb1 = 0;
+            bool w_done = !item_at(w_it, w_mt, w_nb, w_nb1);
             long long t0 = 0; uint32_t idle = 0;
             while (!(x_done && w_done)) {
                 bool progress = false;
@@ -297,8 +324,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     tma_load_3d(smem_base + L.raw_off + x_s * kTile, &tmX, raw_full(x_s), x_kb * 32, x_row0, 0);
                     if (++x_s == p.RS) { x_s = 0; x_ph ^= 1u; }
                     if (++x_kb == p.nblk) {
-                        x_kb = 0; x_item += gridDim.x; x_done = x_item >= total_items;
-                        if (!x_done) x_row0 = (x_item / p.groups) * 128;
+                        x_kb = 0; x_done = !item_at(++x_it, x_mt, x_nb0, x_nb1);
+                        x_row0 = x_mt * 128;
                     }
                     progress = true;
                 }
@@ -308,10 +335,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     if (++w_s == p.BS) { w_s = 0; w_ph ^= 1u; }
                     if (++w_ks == p.KT) {
                         w_ks = 0;
-                        if (++w_nb == w_nb1) {
-                            w_item += gridDim.x; w_done = w_item >= total_items;
-                            if (!w_done) { w_nb = (w_item % p.groups) * p.blocks_per_group; w_nb1 = min(w_nb + p.blocks_per_group, p.n_blocks); }
-                        }
+                        if (++w_nb == w_nb1) w_done = !item_at(++w_it, w_mt, w_nb, w_nb1);
                     }
                     progress = true;
                 }
@@ -341,10 +365,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             uint32_t bcnt = 0, n_it = 0, w_ph = 0; int w_s = 0; bool ok = true;
             uint32_t a_slot0 = 0, a_par0 = 0;           // slot and parity of K step 0 of the current item
             TR_DECL;
-            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
-                const int g = item % p.groups;
-                const int nb0 = g * p.blocks_per_group;
-                const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
+            int mt = 0, nb0 = 0, nb1 = 0;
+            for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
                 for (int nb = nb0; nb < nb1 && ok; ++nb) {
                     uint32_t a_slot = a_slot0, a_par = a_par0;              // A slots form a ring over (item, K step)
                     for (int ks = 0; ks < p.KT; ++ks, a_slot = (a_slot + 1 == static_cast<uint32_t>(p.AR)) ? 0u : a_slot + 1u,
@@ -408,7 +430,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         uint32_t n_it = 0, x_ph = 0; int x_s = 0; bool ok = true;
         uint32_t a_slot = 0, a_par = 0;                 // ring position of the K step being quantized
         TR_DECL;
-        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
+        int mt = 0, nb0 = 0, nb1 = 0;
+        for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
             TR(0);
             if (n_it >= 2) {    // the scale table of this parity was last read by the epilogue two items ago
                 if (!mbar_wait(epi_done(n_it & 1u), ((n_it >> 1) - 1u) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
@@ -468,10 +491,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (!mbar_wait(dw_full, 0u, cta_abort, p.err, 0x1404)) ok = false;
         }
         TR_DECL;
-        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++n_it) {
-            const int mt = item / p.groups, g = item % p.groups;
-            const int nb0 = g * p.blocks_per_group;
-            const int nb1 = min(nb0 + p.blocks_per_group, p.n_blocks);
+        int mt = 0, nb0 = 0, nb1 = 0;
+        for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
             const int tok = mt * 128 + row;
             const uint32_t da_a0 = smem_base + L.da_off + ((n_it & 1u) * p.nblk * 128 + row) * 2;      // this row's d_a, block 0
             for (int nb = nb0; nb < nb1 && ok; ++nb) {
@@ -691,6 +712,9 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     // two rings, and an option is dropped when fewer than five stages would remain.
     const int budget = 226 * 1024;
     const int total_items = p.m_tiles * p.groups;
+    // more token tiles than SMs and enough work per token tile (column blocks x K steps; measured break-even at 8) that
+    // quantizing the cut tiles twice pays off: cut the work into equal contiguous ranges instead
+    p.flat = (p.groups == 1 && p.n_blocks * p.KT >= 8 && p.m_tiles > sms && p.m_tiles % sms != 0) ? 1 : 0;
     int abuf = (p.KT <= 2 && total_items > sms) ? 2 : 1;
     const bool ring = p.blocks_per_group == 1 && p.KT >= 3;    // every item has one column block: A is consumed once
     p.AR = ring ? 3 : p.KT * abuf;
