@@ -2,7 +2,7 @@
 //
 //   O = softmax(scale * Q K^T + bias) V,  denominator (l + eps),  LSE = m + log(l + eps)
 //
-// One CTA = one (batch, head, 128-query tile); keys are walked in tiles of 64.  Two CTAs share an SM (256 TMEM
+// Work item = one (batch, head, 128-query tile); keys are walked in tiles of 64.  CTAs are persistent, two per SM (256 TMEM
 // columns, about 105 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads and
 // tensor work.  (Key tiles of 32 with three CTAs per SM, -DPPML_ATTN_BN=32, measured 5-15 % slower.)
 //   warp 0      TMA: Q tile once; per key tile the bias tile (128 rows x kBN keys fp32, when a bias is
@@ -53,6 +53,7 @@ struct AttnParams {
     float* O;
     float* LSE;
     int q_tiles, k_tiles;
+    int total_items;             // B * H * q_tiles
     int* err;
 };
 
@@ -62,11 +63,9 @@ constexpr int kOffK = kOffQ + kTileQ;               // 2 stages
 constexpr int kOffV = kOffK + 2 * kTileKV;          // 2 stages
 constexpr int kOffP = kOffV + 2 * kTileKV;          // 2 buffers of bias-then-P: TMA puts the bias tile of key tile j into
                                                     //   buffer j % 2 in the layout of P, every softmax thread reads its bias
-                                                    //   values and later writes its P values over them.  After the last tile
-constexpr int kOffStage = kOffP;                    //   buffer 0 is the output transposition buffer (4 x 32 rows x 128 B)
+                                                    //   values and later writes its P values over them
 constexpr int kOffBar = kOffP + 2 * kTileP;
 constexpr int kSmemBytes = kOffBar + 256;             // the dynamic shared memory is declared 1024-byte aligned: no slack
-static_assert(4 * 32 * 128 <= kTileP, "output staging must fit into the P buffer");
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -79,7 +78,7 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         return;
     }
     const uint32_t bar0 = sb + kOffBar;
-    const uint32_t q_full = bar0;
+    const uint32_t q_full = bar0, q_empty = bar0 + 8u * 23;
     auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
     auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
@@ -91,20 +90,24 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto p_full = [&](int s) { return bar0 + 8u * (17 + s); };
     auto p_empty = [&](int s) { return bar0 + 8u * (19 + s); };
     auto b_full = [&](int s) { return bar0 + 8u * (21 + s); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sg + kOffBar + 8 * 23);
-    volatile int* cta_abort = reinterpret_cast<volatile int*>(sg + kOffBar + 8 * 23 + 8);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sg + kOffBar + 8 * 24);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(sg + kOffBar + 8 * 24 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = blockIdx.x % p.q_tiles;
-    const int bh = blockIdx.x / p.q_tiles;
-    const int b = bh / p.H, hh = bh - b * p.H;
-    const int q0 = qt * kBM;
-    // causal: keys beyond the last query row of the tile are never needed
-    int k_tiles = p.k_tiles;
-    if (p.causal) { const int last = min(q0 + kBM, p.L); k_tiles = min(k_tiles, (min(last, p.Lk) + kBN - 1) / kBN); }
+    // Work item = (batch * head, 128-query tile).  The CTA is persistent: it walks items blockIdx.x, + gridDim.x, ...
+    // and every ring (K, V, S, P / bias, O) keeps running across item boundaries, so the loads and the first score
+    // product of the next item overlap the softmax tail and the output stores of the current one.
+    auto item_info = [&](int item, int& bh, int& q0, int& ktl) {
+        const int qt = item % p.q_tiles;
+        bh = item / p.q_tiles;
+        q0 = qt * kBM;
+        ktl = p.k_tiles;
+        // causal: keys beyond the last query row of the tile are never needed
+        if (p.causal) { const int last = min(q0 + kBM, p.L); ktl = min(ktl, (min(last, p.Lk) + kBN - 1) / kBN); }
+    };
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        mbar_init(q_full, 1); mbar_init(q_empty, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1);
             mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
@@ -125,26 +128,35 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, kTileQ);
-            tma_load_3d(sb + kOffQ, &tmQ, q_full, 0, q0, bh);
-            const int brow0 = hh * p.L + q0;                         // first bias row of this tile
-            const int bbatch = (p.bias_batch_stride != 0) ? b : 0;
-            for (int j = 0; j < k_tiles; ++j) {
-                const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-                if (p.bias != nullptr) {
-                    // buffer s is free again once P(j - 2) V(j - 2) has read it
-                    if (!mbar_wait(p_empty(s), ph ^ 1u, cta_abort, p.err, 0x2103)) break;
-                    mbar_arrive_expect_tx(b_full(s), kTileP);
+            uint32_t tc = 0, ic = 0;                     // key tiles and items issued so far
+            bool ok = true;
+            for (int item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, ++ic) {
+                int bh, q0, k_tiles;
+                item_info(item, bh, q0, k_tiles);
+                const int b = bh / p.H, hh = bh - b * p.H;
+                // the Q tile is free once the score products of the previous item have been computed
+                if (!mbar_wait(q_empty, (ic & 1u) ^ 1u, cta_abort, p.err, 0x2100)) break;
+                mbar_arrive_expect_tx(q_full, kTileQ);
+                tma_load_3d(sb + kOffQ, &tmQ, q_full, 0, q0, bh);
+                const int brow0 = hh * p.L + q0;                         // first bias row of this tile
+                const int bbatch = (p.bias_batch_stride != 0) ? b : 0;
+                for (int j = 0; j < k_tiles; ++j, ++tc) {
+                    const int s = tc & 1; const uint32_t ph = (tc >> 1) & 1u;
+                    if (p.bias != nullptr) {
+                        // buffer s is free again once the P V product two tiles back has read it
+                        if (!mbar_wait(p_empty(s), ph ^ 1u, cta_abort, p.err, 0x2103)) { ok = false; break; }
+                        mbar_arrive_expect_tx(b_full(s), kTileP);
 #pragma unroll
-                    for (int a = 0; a < kBN / 32; ++a)
-                        tma_load_3d(sb + kOffP + s * kTileP + a * kTileQ, &tmB, b_full(s), j * kBN + 32 * a, brow0, bbatch);
+                        for (int a = 0; a < kBN / 32; ++a)
+                            tma_load_3d(sb + kOffP + s * kTileP + a * kTileQ, &tmB, b_full(s), j * kBN + 32 * a, brow0, bbatch);
+                    }
+                    if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) { ok = false; break; }
+                    mbar_arrive_expect_tx(k_full(s), kTileKV);
+                    tma_load_3d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, bh);
+                    if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2102)) { ok = false; break; }
+                    mbar_arrive_expect_tx(v_full(s), kTileKV);
+                    tma_load_3d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, bh);
                 }
-                if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) break;
-                mbar_arrive_expect_tx(k_full(s), kTileKV);
-                tma_load_3d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, bh);
-                if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2102)) break;
-                mbar_arrive_expect_tx(v_full(s), kTileKV);
-                tma_load_3d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, bh);
             }
         }
         __syncwarp();
@@ -152,11 +164,12 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc_s = make_idesc(1, 2, 2, 0, 0, 128, kBN);
             const uint32_t idesc_o = make_idesc(1, 2, 2, 0, 1, 128, kD);     // B = V with d (the row index) contiguous
-            bool ok = mbar_wait(q_full, 0, cta_abort, p.err, 0x2201);
+            uint32_t ts = 0, tp = 0, ic = 0;             // score products / P V products / items issued so far
+            bool ok = true;
             // software pipeline: S(j+1) is issued before P(j) V(j), so the softmax of tile j+1 can start
             // while the tensor core finishes tile j
-            auto issue_s = [&](int j) -> bool {
-                const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
+            auto issue_s = [&]() -> bool {
+                const int s = ts & 1; const uint32_t ph = (ts >> 1) & 1u;
                 if (!mbar_wait(k_full(s), ph, cta_abort, p.err, 0x2202)) return false;
                 if (!mbar_wait(s_empty(s), ph ^ 1u, cta_abort, p.err, 0x2203)) return false;
                 tc_fence_after();
@@ -166,29 +179,39 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 for (int kk = 0; kk < 4; ++kk) umma<MmaKind::TF32>(tmem_base + s * kBN, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
                 umma_commit(k_empty(s));
                 umma_commit(s_full(s));
+                ++ts;
                 return true;
             };
-            if (ok && k_tiles > 0) ok = issue_s(0);
-            for (int j = 0; j < k_tiles && ok; ++j) {
-                if (j + 1 < k_tiles) { if (!issue_s(j + 1)) { ok = false; break; } }
-                const int s = j & 1; const uint32_t ph = (j >> 1) & 1u;
-                if (!mbar_wait(p_full(s), ph, cta_abort, p.err, 0x2204)) { ok = false; break; }
-                if (!mbar_wait(v_full(s), ph, cta_abort, p.err, 0x2205)) { ok = false; break; }
-                if (!mbar_wait(o_empty(s), ph ^ 1u, cta_abort, p.err, 0x2206)) { ok = false; break; }
-                tc_fence_after();
-                // V tile: 64 key rows of 128 bytes in the 32-byte-chunk swizzle; a group of 4 keys is 512 bytes
-                // (stride offset), one instruction consumes 8 keys = 1024 bytes.  P: two 32-key swizzle atoms.
-                const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW128Base32);
+            for (int item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, ++ic) {
+                int bh, q0, k_tiles;
+                item_info(item, bh, q0, k_tiles);
+                if (!mbar_wait(q_full, ic & 1u, cta_abort, p.err, 0x2201)) { ok = false; break; }
+                if (!issue_s()) { ok = false; break; }
+                if (k_tiles == 1) umma_commit(q_empty);          // every score product of this item has been issued
+                for (int j = 0; j < k_tiles && ok; ++j, ++tp) {
+                    if (j + 1 < k_tiles) {
+                        if (!issue_s()) { ok = false; break; }
+                        if (j + 2 == k_tiles) umma_commit(q_empty);
+                    }
+                    const int s = tp & 1; const uint32_t ph = (tp >> 1) & 1u;
+                    if (!mbar_wait(p_full(s), ph, cta_abort, p.err, 0x2204)) { ok = false; break; }
+                    if (!mbar_wait(v_full(s), ph, cta_abort, p.err, 0x2205)) { ok = false; break; }
+                    if (!mbar_wait(o_empty(s), ph ^ 1u, cta_abort, p.err, 0x2206)) { ok = false; break; }
+                    tc_fence_after();
+                    // V tile: 64 key rows of 128 bytes in the 32-byte-chunk swizzle; a group of 4 keys is 512 bytes
+                    // (stride offset), one instruction consumes 8 keys = 1024 bytes.  P: two 32-key swizzle atoms.
+                    const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW128Base32);
 #pragma unroll
-                for (int a = 0; a < kBN / 32; ++a) {
-                    const uint64_t dp = make_smem_desc(sb + kOffP + s * kTileP + a * kTileQ, 16, 1024, kLayoutSW128);
+                    for (int a = 0; a < kBN / 32; ++a) {
+                        const uint64_t dp = make_smem_desc(sb + kOffP + s * kTileP + a * kTileQ, 16, 1024, kLayoutSW128);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma<MmaKind::TF32>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma<MmaKind::TF32>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
+                    }
+                    umma_commit(p_empty(s));
+                    umma_commit(v_empty(s));
+                    umma_commit(o_full(s));
                 }
-                umma_commit(p_empty(s));
-                umma_commit(v_empty(s));
-                umma_commit(o_full(s));
             }
         }
         __syncwarp();
@@ -217,8 +240,11 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
     p.B = B; p.H = H; p.L = L; p.Lk = Lk; p.causal = causal; p.scale = scale; p.eps = eps;
     p.bias = bias; p.bias_batch_stride = bias_batch_stride; p.O = O; p.LSE = LSE;
     p.q_tiles = (L + kBM - 1) / kBM; p.k_tiles = (Lk + kBN - 1) / kBN; p.err = err;
-    const long long grid = BH * p.q_tiles;
-    if (grid <= 0 || grid > 0x7fffffffLL) return ST_BAD_ARGS;
+    const long long items = BH * p.q_tiles;
+    if (items <= 0 || items > 0x7fffffffLL || Lk <= 0) return ST_BAD_ARGS;
+    p.total_items = static_cast<int>(items);
+    const long long resident = static_cast<long long>(kCtasPerSm) * num_sms();     // persistent CTAs
+    const long long grid = items < resident ? items : resident;
     CUtensorMap tmQ, tmK, tmV, tmB;
     if (!make_tmap_3d(&tmQ, TmaType::TF32, Q, kD, L, BH, kD * 4, static_cast<uint64_t>(L) * kD * 4, kD, kBM, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmK, TmaType::TF32, K, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 1)) return ST_UNSUPPORTED_PATH;
