@@ -54,6 +54,7 @@ struct AttnParams {
     float* LSE;
     int q_tiles, k_tiles;
     int total_items;             // B * H * q_tiles
+    int o_align32;               // O is 32-byte aligned: rows can be written with 256-bit stores
     int* err;
 };
 
@@ -243,6 +244,7 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
     const long long items = BH * p.q_tiles;
     if (items <= 0 || items > 0x7fffffffLL || Lk <= 0) return ST_BAD_ARGS;
     p.total_items = static_cast<int>(items);
+    p.o_align32 = (reinterpret_cast<uintptr_t>(O) & 31u) == 0 ? 1 : 0;
     const long long resident = static_cast<long long>(kCtasPerSm) * num_sms();     // persistent CTAs
     const long long grid = items < resident ? items : resident;
     CUtensorMap tmQ, tmK, tmV, tmB;
