@@ -128,6 +128,13 @@ int ppml_b200_flash_attn_forward_ex(const ppml_b200_flash_cfg* cfg, int Lk, int6
                                     const float* Q, const float* K, const float* V, const float* bias,
                                     float* O, float* LSE, int path, void* stream);
 
+/* The extended form with 16-bit Q/K/V (fp16, or bfloat16 when is_bf16 != 0): products on the 16-bit tensor-core
+ * path, softmax in fp32, bias / O / LSE fp32.  No counterpart in the reference (its tensor type enum has no
+ * 16-bit attention, include/ppml/Tensor.h:35-64); same layouts and semantics as above. */
+int ppml_b200_flash_attn_forward_16(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
+                                    const void* Q16, const void* K16, const void* V16, const float* bias,
+                                    float* O, float* LSE, int is_bf16, int path, void* stream);
+
 /* ---- OP_OUT_PROD -------------------------------------------------------------------------------
  * Replaces out_prod_cuda (src/backend/CUDAKernels.cpp:201; src/cuda/OutProdKernel.cu:211-260):
  * dst[i0,i1,i2,i3] = sum_k s0[i0,k,i2/(ne2/ne02),i3/(ne3/ne03)] * s1[i1,k,i2,i3]; dims in the graph's

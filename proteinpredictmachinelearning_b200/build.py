@@ -25,7 +25,7 @@ def _stale(obj, src):
     if not os.path.exists(obj):
         return True
     t = os.path.getmtime(obj)
-    deps = [src] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    deps = [src] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     deps.append(os.path.join(HERE, "..", "include", "ppml_b200.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 

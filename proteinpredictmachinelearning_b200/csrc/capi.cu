@@ -152,19 +152,33 @@ int ppml_b200_quantize_q8_0r(const float* w_dev, void* q8_0r_dev, int64_t ne, vo
 }
 int64_t ppml_b200_q8_0r_bytes(int64_t numel) { return numel / 32 * 34; }
 
-int ppml_b200_flash_attn_forward_ex(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
-                                    const float* Q, const float* K, const float* V, const float* bias,
-                                    float* O, float* LSE, int path, void* stream) {
+namespace {
+// elem: 0 = fp32, 1 = bf16, 2 = fp16 Q/K/V
+int flash_attn_any(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride, const void* Q, const void* K,
+                   const void* V, int elem, const float* bias, float* O, float* LSE, int path, void* stream) {
     if (!cfg || !Q || !K || !V || !O || !path_ok(path)) return ST_BAD_ARGS;
     if (cfg->B <= 0 || cfg->h <= 0 || cfg->L <= 0 || cfg->d <= 0 || Lk <= 0) return ST_BAD_ARGS;
     const float scale = (cfg->scale > 0.f) ? cfg->scale : 1.0f / std::sqrt(static_cast<float>(cfg->d));
     if (path != PPML_B200_PATH_SIMT) {
-        const int rc = launch_umma_attn(Q, K, V, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
-                                        cfg->softmax_eps, bias_batch_stride, as_stream(stream));
+        const int rc = launch_umma_attn(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0,
+                                        scale, cfg->softmax_eps, bias_batch_stride, as_stream(stream));
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
     }
-    return launch_attn_rowwarp(Q, K, V, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
+    return launch_attn_rowwarp(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
                                cfg->softmax_eps, bias_batch_stride, as_stream(stream));
+}
+}  // namespace
+
+int ppml_b200_flash_attn_forward_ex(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
+                                    const float* Q, const float* K, const float* V, const float* bias,
+                                    float* O, float* LSE, int path, void* stream) {
+    return flash_attn_any(cfg, Lk, bias_batch_stride, Q, K, V, 0, bias, O, LSE, path, stream);
+}
+
+int ppml_b200_flash_attn_forward_16(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
+                                    const void* Q16, const void* K16, const void* V16, const float* bias,
+                                    float* O, float* LSE, int is_bf16, int path, void* stream) {
+    return flash_attn_any(cfg, Lk, bias_batch_stride, Q16, K16, V16, is_bf16 ? 1 : 2, bias, O, LSE, path, stream);
 }
 
 int ppml_b200_flash_attn_forward(const ppml_b200_flash_cfg* cfg, const float* Q, const float* K, const float* V,

@@ -204,7 +204,7 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_fmt, uint32_t a_fmt
 // Shared-memory operand descriptor (64 bit): [0,14) start address >> 4, [16,30) leading byte
 // offset >> 4, [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) layout
 // (0 = no swizzle / interleaved, 2 = 128-byte swizzle over 16-byte chunks, 1 = 128-byte swizzle over
-// 32-byte chunks: the layout of 32-bit operands whose row index is contiguous).
+// 32-byte chunks: the layout of 32-bit operands whose row index is contiguous, 4 = 64-byte swizzle).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                    uint32_t layout) {
     uint64_t d = 0;
@@ -217,6 +217,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 }
 constexpr uint32_t kLayoutSW128 = 2;
 constexpr uint32_t kLayoutSW128Base32 = 1;
+constexpr uint32_t kLayoutSW64 = 4;           // 64-byte swizzle over 16-byte chunks: tiles whose rows are 64 bytes
 
 enum class MmaKind { TF32, F16, I8 };
 

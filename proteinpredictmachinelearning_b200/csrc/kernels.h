@@ -33,7 +33,8 @@ int launch_quantize_q8_0r(const float* w, void* out, long long ne, cudaStream_t 
 int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaStream_t st);
 int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
                    const float* bias, int* sumi_out, cudaStream_t st);
-int launch_attn_rowwarp(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+// elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16; bias, O and LSE are fp32
+int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                         long long bias_batch_stride, cudaStream_t st);
 
@@ -56,7 +57,7 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st);
 int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
                    int* sumi_out, cudaStream_t st);
 
-int launch_umma_attn(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                      long long bias_batch_stride, cudaStream_t st);
 

@@ -317,8 +317,13 @@ int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int 
 // O = softmax(scale * Q K^T + bias) V with denominator (l + eps); LSE = m + log(l + eps);
 // a row with no unmasked key gives O = 0, LSE = -inf.
 // =============================================================================================
+__device__ __forceinline__ float attn_ld(const float* p) { return *p; }
+__device__ __forceinline__ float attn_ld(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ float attn_ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <typename T>
 __global__ void __launch_bounds__(128)
-attn_rowwarp_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                     const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
                     int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride) {
     extern __shared__ float qs[];                    // [4][d]
@@ -326,11 +331,11 @@ attn_rowwarp_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
     const int i = blockIdx.x * 4 + warp;
     const int hh = blockIdx.y, b = blockIdx.z;
     const size_t bh = static_cast<size_t>(b) * H + hh;
-    const float* Qb = Q + bh * static_cast<size_t>(L) * d;
-    const float* Kb = K + bh * static_cast<size_t>(Lk) * d;
-    const float* Vb = V + bh * static_cast<size_t>(Lk) * d;
+    const T* Qb = Q + bh * static_cast<size_t>(L) * d;
+    const T* Kb = K + bh * static_cast<size_t>(Lk) * d;
+    const T* Vb = V + bh * static_cast<size_t>(Lk) * d;
     float* myq = qs + warp * d;
-    if (i < L) for (int dd = lane; dd < d; dd += 32) myq[dd] = Qb[static_cast<size_t>(i) * d + dd];
+    if (i < L) for (int dd = lane; dd < d; dd += 32) myq[dd] = attn_ld(Qb + static_cast<size_t>(i) * d + dd);
     __syncwarp();
     if (i >= L) return;
     const float* Bb = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
@@ -342,9 +347,9 @@ attn_rowwarp_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
         const int j = j0 + lane;
         float s = -CUDART_INF_F;
         if (j < jmax) {
-            const float* k = Kb + static_cast<size_t>(j) * d;
+            const T* k = Kb + static_cast<size_t>(j) * d;
             float dot = 0.0f;
-            for (int dd = 0; dd < d; ++dd) dot = fmaf(myq[dd], k[dd], dot);
+            for (int dd = 0; dd < d; ++dd) dot = fmaf(myq[dd], attn_ld(k + dd), dot);
             s = dot * scale;
             if (Bb) s += Bb[j];
         }
@@ -364,11 +369,11 @@ attn_rowwarp_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
         const int nj = (jmax - j0 < 32) ? (jmax - j0) : 32;
         for (int jj = 0; jj < nj; ++jj) {
             const float p = __shfl_sync(0xffffffffu, pj, jj);
-            const float* v = Vb + static_cast<size_t>(j0 + jj) * d;
+            const T* v = Vb + static_cast<size_t>(j0 + jj) * d;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int dd = lane + 32 * t;
-                if (dd < d) acc[t] = fmaf(p, v[dd], acc[t]);
+                if (dd < d) acc[t] = fmaf(p, attn_ld(v + dd), acc[t]);
             }
         }
     }
@@ -385,13 +390,22 @@ attn_rowwarp_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
     }
 }
 
-int launch_attn_rowwarp(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                         long long bias_batch_stride, cudaStream_t st) {
-    if (d > 128 || H > 65535 || B > 65535) return ST_BAD_ARGS;
+    if (d > 128 || H > 65535 || B > 65535 || elem < 0 || elem > 2) return ST_BAD_ARGS;
     dim3 grid((L + 3) / 4, H, B);
-    attn_rowwarp_kernel<<<grid, 128, 4 * d * sizeof(float), st>>>(Q, K, V, bias, O, LSE, H, L, Lk, d, causal, scale,
-                                                                 eps, bias_batch_stride);
+    const size_t smem = 4 * d * sizeof(float);
+    if (elem == 0)
+        attn_rowwarp_kernel<float><<<grid, 128, smem, st>>>(static_cast<const float*>(Q), static_cast<const float*>(K),
+            static_cast<const float*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride);
+    else if (elem == 1)
+        attn_rowwarp_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(Q),
+            static_cast<const __nv_bfloat16*>(K), static_cast<const __nv_bfloat16*>(V), bias, O, LSE, H, L, Lk, d, causal,
+            scale, eps, bias_batch_stride);
+    else
+        attn_rowwarp_kernel<__half><<<grid, 128, smem, st>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
+            static_cast<const __half*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 

@@ -4,7 +4,10 @@
 //
 // Work item = one (batch, head, 128-query tile); keys are walked in tiles of 64.  CTAs are persistent, two per SM (256 TMEM
 // columns, about 105 KB of shared memory, 192 threads each), so one CTA's softmax overlaps the other's loads and
-// tensor work.  (Key tiles of 32 with three CTAs per SM, -DPPML_ATTN_BN=32, measured 5-15 % slower.)
+// tensor work.  (Key tiles of 32 with three CTAs per SM measured 5-15 % slower.)
+// Operands: fp32 Q/K/V on kind::tf32 (rounded by the TMA unit), or bf16 / fp16 Q/K/V on kind::f16 with P in the same
+// 16-bit type; scores, softmax, running sums and the output are fp32 in both cases.  The 16-bit tiles have rows of
+// 64 bytes, so Q and K use the 64-byte swizzle (K-major) and V the same swizzle in its row-index-contiguous form.
 //   warp 0      TMA: Q tile once; per key tile the bias tile (128 rows x kBN keys fp32, when a bias is
 //               given; it lands in the P buffer of that tile and is overwritten in place by P), K (kBN keys x 32 floats, K-major, 128-byte swizzle) and V (the same
 //               box in the 32-byte-chunk swizzle: V[key][d] has d contiguous, which is the "row index contiguous"
@@ -25,16 +28,37 @@ namespace ppml_b200 {
 namespace {
 
 constexpr int kD = 32;                       // head dim handled here
-#ifndef PPML_ATTN_BN
-#define PPML_ATTN_BN 64
-#endif
-constexpr int kBM = 128, kBN = PPML_ATTN_BN;  // query tile, key tile (32: three CTAs per SM, 64: two)
-constexpr int kTileQ = 128 * 128;            // bytes: 128 rows x 32 floats
-constexpr int kTileKV = kBN * 128;           // bytes: kBN keys x 32 floats
-constexpr int kTileP = (kBN / 32) * kTileQ;  // P: 128 rows x 64 floats as two 32-float swizzle atoms
+constexpr int kBM = 128, kBN = 64;           // query tile, key tile
+constexpr int kSubP = 128 * 128;             // bytes: 128 rows of one 128-byte swizzle atom (32 floats or 64 16-bit values)
+constexpr int kTileP = (kBN / 32) * kSubP;   // bias tile: 128 rows x 64 floats as two 32-float atoms; fp32 P has the same
+                                             //   shape, 16-bit P is the first atom alone
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = (kBN == 32) ? 128 : 256;   // S buffers at columns 0 and kBN, O_part buffers at 2 kBN and 2 kBN + 32
-constexpr int kCtasPerSm = (kBN == 32) ? 3 : 2;
+constexpr uint32_t kTmemCols = 256;          // S buffers at columns 0 and kBN, O_part buffers at 2 kBN and 2 kBN + 32
+constexpr int kCtasPerSm = 2;
+
+// ELEM: 0 = fp32 operands (tf32 products), 1 = bf16, 2 = fp16.  Shared-memory map (offsets from the 1024-aligned
+// base); two CTAs per SM leave about 113 KB each.
+template <int ELEM>
+struct Cfg {
+    static constexpr bool k16 = ELEM != 0;
+    static constexpr int kRow = k16 ? 64 : 128;              // bytes of one Q / K / V row of 32 elements
+    static constexpr int kTileQ = kBM * kRow;
+    static constexpr int kTileKV = kBN * kRow;
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffK = kOffQ + kTileQ;             // 2 stages
+    static constexpr int kOffV = kOffK + 2 * kTileKV;        // 2 stages
+    // 2 buffers of bias-then-P: TMA puts the bias tile of key tile j into buffer j % 2 in the layout of fp32 P, every
+    // softmax thread reads its bias values and later writes its P values over them
+    static constexpr int kOffP = kOffV + 2 * kTileKV;
+    static constexpr int kOffBar = kOffP + 2 * kTileP;
+    static constexpr int kSmemBytes = kOffBar + 256;         // the dynamic shared memory is declared 1024-byte aligned: no slack
+    static constexpr uint32_t kFmt = ELEM == 0 ? 2u : (ELEM == 1 ? 1u : 0u);      // operand format field of the instruction
+    static constexpr MmaKind kKind = k16 ? MmaKind::F16 : MmaKind::TF32;
+    static constexpr uint32_t kLayQK = k16 ? kLayoutSW64 : kLayoutSW128;
+    static constexpr uint32_t kSboQK = k16 ? 512u : 1024u;   // 8 rows of the swizzle atom
+    static constexpr int kStepsS = k16 ? 2 : 4;              // instructions per score product (K = 16 or 8 of the 32)
+    static_assert(kOffP % 1024 == 0 && kOffK % 512 == 0 && kOffV % 512 == 0, "tile alignment");
+};
 
 // 2^x on the transcendental unit (about 2 ulp); results below the normal range flush to 0, 2^-inf = 0
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -42,6 +66,15 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r;
+}
+
+// two probabilities as one 32-bit word of the operand type, the first in the low half (the lower key index)
+template <int ELEM>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    uint32_t w;
+    if constexpr (ELEM == 1) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+    return w;
 }
 
 struct AttnParams {
@@ -58,19 +91,13 @@ struct AttnParams {
     int* err;
 };
 
-// smem map (offsets from the 1024-aligned base); two CTAs per SM leave about 113 KB each
-constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kTileQ;               // 2 stages
-constexpr int kOffV = kOffK + 2 * kTileKV;          // 2 stages
-constexpr int kOffP = kOffV + 2 * kTileKV;          // 2 buffers of bias-then-P: TMA puts the bias tile of key tile j into
-                                                    //   buffer j % 2 in the layout of P, every softmax thread reads its bias
-                                                    //   values and later writes its P values over them
-constexpr int kOffBar = kOffP + 2 * kTileP;
-constexpr int kSmemBytes = kOffBar + 256;             // the dynamic shared memory is declared 1024-byte aligned: no slack
-
+template <int ELEM>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, const AttnParams p) {
+    using C = Cfg<ELEM>;
+    constexpr int kOffQ = C::kOffQ, kOffK = C::kOffK, kOffV = C::kOffV, kOffP = C::kOffP, kOffBar = C::kOffBar;
+    constexpr int kTileQ = C::kTileQ, kTileKV = C::kTileKV;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t sb = smem_u32(smem_raw);
     uint8_t* sg = smem_raw;
@@ -149,7 +176,7 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         mbar_arrive_expect_tx(b_full(s), kTileP);
 #pragma unroll
                         for (int a = 0; a < kBN / 32; ++a)
-                            tma_load_3d(sb + kOffP + s * kTileP + a * kTileQ, &tmB, b_full(s), j * kBN + 32 * a, brow0, bbatch);
+                            tma_load_3d(sb + kOffP + s * kTileP + a * kSubP, &tmB, b_full(s), j * kBN + 32 * a, brow0, bbatch);
                     }
                     if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) { ok = false; break; }
                     mbar_arrive_expect_tx(k_full(s), kTileKV);
@@ -163,8 +190,8 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc_s = make_idesc(1, 2, 2, 0, 0, 128, kBN);
-            const uint32_t idesc_o = make_idesc(1, 2, 2, 0, 1, 128, kD);     // B = V with d (the row index) contiguous
+            const uint32_t idesc_s = make_idesc(1, C::kFmt, C::kFmt, 0, 0, 128, kBN);
+            const uint32_t idesc_o = make_idesc(1, C::kFmt, C::kFmt, 0, 1, 128, kD);     // B = V with d (the row index) contiguous
             uint32_t ts = 0, tp = 0, ic = 0;             // score products / P V products / items issued so far
             bool ok = true;
             // software pipeline: S(j+1) is issued before P(j) V(j), so the softmax of tile j+1 can start
@@ -174,10 +201,11 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (!mbar_wait(k_full(s), ph, cta_abort, p.err, 0x2202)) return false;
                 if (!mbar_wait(s_empty(s), ph ^ 1u, cta_abort, p.err, 0x2203)) return false;
                 tc_fence_after();
-                const uint64_t dq = make_smem_desc(sb + kOffQ, 16, 1024, kLayoutSW128);
-                const uint64_t dk = make_smem_desc(sb + kOffK + s * kTileKV, 16, 1024, kLayoutSW128);
+                const uint64_t dq = make_smem_desc(sb + kOffQ, 16, C::kSboQK, C::kLayQK);
+                const uint64_t dk = make_smem_desc(sb + kOffK + s * kTileKV, 16, C::kSboQK, C::kLayQK);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) umma<MmaKind::TF32>(tmem_base + s * kBN, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
+                for (int kk = 0; kk < C::kStepsS; ++kk)      // 32 bytes of every row per instruction
+                    umma<C::kKind>(tmem_base + s * kBN, dq + 2u * kk, dk + 2u * kk, idesc_s, kk ? 1u : 0u);
                 umma_commit(k_empty(s));
                 umma_commit(s_full(s));
                 ++ts;
@@ -199,15 +227,25 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     if (!mbar_wait(v_full(s), ph, cta_abort, p.err, 0x2205)) { ok = false; break; }
                     if (!mbar_wait(o_empty(s), ph ^ 1u, cta_abort, p.err, 0x2206)) { ok = false; break; }
                     tc_fence_after();
-                    // V tile: 64 key rows of 128 bytes in the 32-byte-chunk swizzle; a group of 4 keys is 512 bytes
-                    // (stride offset), one instruction consumes 8 keys = 1024 bytes.  P: two 32-key swizzle atoms.
-                    const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW128Base32);
+                    if constexpr (C::k16) {
+                        // V tile: 64 key rows of 64 bytes in the 64-byte swizzle; a group of 8 keys is 512 bytes (stride
+                        // offset), one instruction consumes 16 keys = 1024 bytes.  P: one atom of 64 keys.
+                        const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW64);
+                        const uint64_t dp = make_smem_desc(sb + kOffP + s * kTileP, 16, 1024, kLayoutSW128);
 #pragma unroll
-                    for (int a = 0; a < kBN / 32; ++a) {
-                        const uint64_t dp = make_smem_desc(sb + kOffP + s * kTileP + a * kTileQ, 16, 1024, kLayoutSW128);
+                        for (int kk = 0; kk < kBN / 16; ++kk)
+                            umma<MmaKind::F16>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * kk, idesc_o, kk ? 1u : 0u);
+                    } else {
+                        // V tile: 64 key rows of 128 bytes in the 32-byte-chunk swizzle; a group of 4 keys is 512 bytes
+                        // (stride offset), one instruction consumes 8 keys = 1024 bytes.  P: two 32-key swizzle atoms.
+                        const uint64_t dv = make_smem_desc(sb + kOffV + s * kTileKV, 4096, 512, kLayoutSW128Base32);
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            umma<MmaKind::TF32>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
+                        for (int a = 0; a < kBN / 32; ++a) {
+                            const uint64_t dp = make_smem_desc(sb + kOffP + s * kTileP + a * kSubP, 16, 1024, kLayoutSW128);
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk)
+                                umma<MmaKind::TF32>(tmem_base + 2 * kBN + s * kD, dp + 2u * kk, dv + 64u * (a * 4 + kk), idesc_o, (a | kk) ? 1u : 0u);
+                        }
                     }
                     umma_commit(p_empty(s));
                     umma_commit(v_empty(s));
@@ -227,10 +265,32 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 }  // namespace
 
-int launch_umma_attn(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE,
+namespace {
+
+template <int ELEM>
+int launch_attn_elem(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmB,
+                     const AttnParams& p, unsigned grid, cudaStream_t st) {
+    static bool configured[64] = {false};
+    int dev = 0; cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(umma_attn_kernel<ELEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<ELEM>::kSmemBytes) != cudaSuccess) {
+            cudaGetLastError();
+            return ST_LAUNCH;
+        }
+        configured[dev] = true;
+    }
+    umma_attn_kernel<ELEM><<<grid, kThreads, Cfg<ELEM>::kSmemBytes, st>>>(tmQ, tmK, tmV, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+}  // namespace
+
+// elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16 (bias, O and LSE are fp32 in every case)
+int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                      long long bias_batch_stride, cudaStream_t st) {
     if (d != kD) return ST_UNSUPPORTED_PATH;
+    if (elem < 0 || elem > 2) return ST_BAD_ARGS;
     if ((reinterpret_cast<uintptr_t>(Q) & 15u) || (reinterpret_cast<uintptr_t>(K) & 15u) ||
         (reinterpret_cast<uintptr_t>(V) & 15u) || (reinterpret_cast<uintptr_t>(O) & 15u)) return ST_UNSUPPORTED_PATH;
     if (bias && ((reinterpret_cast<uintptr_t>(bias) & 15u) || (Lk % 4) || (bias_batch_stride % 4))) return ST_UNSUPPORTED_PATH;
@@ -246,11 +306,15 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
     p.total_items = static_cast<int>(items);
     p.o_align32 = (reinterpret_cast<uintptr_t>(O) & 31u) == 0 ? 1 : 0;
     const long long resident = static_cast<long long>(kCtasPerSm) * num_sms();     // persistent CTAs
-    const long long grid = items < resident ? items : resident;
+    const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
     CUtensorMap tmQ, tmK, tmV, tmB;
-    if (!make_tmap_3d(&tmQ, TmaType::TF32, Q, kD, L, BH, kD * 4, static_cast<uint64_t>(L) * kD * 4, kD, kBM, 1)) return ST_UNSUPPORTED_PATH;
-    if (!make_tmap_3d(&tmK, TmaType::TF32, K, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 1)) return ST_UNSUPPORTED_PATH;
-    if (!make_tmap_3d(&tmV, TmaType::TF32, V, kD, Lk, BH, kD * 4, static_cast<uint64_t>(Lk) * kD * 4, kD, kBN, 2)) return ST_UNSUPPORTED_PATH;
+    // fp32 rows are 128 bytes (128-byte swizzle; V in its 32-byte-chunk form), 16-bit rows 64 bytes (64-byte swizzle)
+    const TmaType ty = elem == 0 ? TmaType::TF32 : (elem == 1 ? TmaType::BF16 : TmaType::F16);
+    const uint64_t row = static_cast<uint64_t>(kD) * (elem == 0 ? 4 : 2);
+    const int sw_qk = elem == 0 ? 1 : 3, sw_v = elem == 0 ? 2 : 3;
+    if (!make_tmap_3d(&tmQ, ty, Q, kD, L, BH, row, static_cast<uint64_t>(L) * row, kD, kBM, sw_qk)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_3d(&tmK, ty, K, kD, Lk, BH, row, static_cast<uint64_t>(Lk) * row, kD, kBN, sw_qk)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_3d(&tmV, ty, V, kD, Lk, BH, row, static_cast<uint64_t>(Lk) * row, kD, kBN, sw_v)) return ST_UNSUPPORTED_PATH;
     // bias rows are (head, query) pairs, [B or 1][H * L][Lk]; fp32 as it is (no tf32 rounding)
     tmB = tmQ;
     if (bias) {
@@ -258,17 +322,9 @@ int launch_umma_attn(const float* Q, const float* K, const float* V, const float
         if (!make_tmap_3d(&tmB, TmaType::F32, bias, Lk, static_cast<uint64_t>(H) * L, per_batch ? B : 1, static_cast<uint64_t>(Lk) * 4,
                           per_batch ? static_cast<uint64_t>(bias_batch_stride) * 4 : 0, 32, kBM, 1)) return ST_UNSUPPORTED_PATH;
     }
-    static bool configured[64] = {false};
-    int dev = 0; cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(umma_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
-            cudaGetLastError();
-            return ST_LAUNCH;
-        }
-        configured[dev] = true;
-    }
-    umma_attn_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, st>>>(tmQ, tmK, tmV, tmB, p);
-    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+    if (elem == 0) return launch_attn_elem<0>(tmQ, tmK, tmV, tmB, p, grid, st);
+    if (elem == 1) return launch_attn_elem<1>(tmQ, tmK, tmV, tmB, p, grid, st);
+    return launch_attn_elem<2>(tmQ, tmK, tmV, tmB, p, grid, st);
 }
 
 }  // namespace ppml_b200

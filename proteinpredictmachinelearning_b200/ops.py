@@ -134,20 +134,32 @@ def mul_mat_q8_noalloc(W, X, M, wtype=2, c_trans=1, bias=None, out=None):
     return Cout
 
 
-def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-9, bias_bcast=False, path=PATH_AUTO):
+def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-9, bias_bcast=False, path=PATH_AUTO, out=None):
     """Q [B,h,L,d], K/V [B,h,Lk,d], bias [B,h,L,Lk] (or [h,L,Lk] shared over B with bias_bcast).
-    Returns (O, LSE).  Lk != L and bias_bcast go through the extended entry."""
-    Q, K, V = _f32c(Q), _f32c(K), _f32c(V)
+    Returns (O, LSE).  Lk != L and bias_bcast go through the extended entry.  `out` is an optional contiguous
+    fp32 destination of Q's shape (any 16-byte-aligned address)."""
+    half = Q.dtype in (torch.float16, torch.bfloat16)         # 16-bit Q/K/V: fp32 softmax, bias, output
+    if half:
+        assert K.dtype == Q.dtype and V.dtype == Q.dtype
+        Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+    else:
+        Q, K, V = _f32c(Q), _f32c(K), _f32c(V)
     B, h, L, d = Q.shape
     Lk = K.shape[2]
-    O = torch.empty_like(Q)
+    O = torch.empty(Q.shape, device=Q.device, dtype=torch.float32) if out is None else out
+    assert O.is_contiguous() and O.dtype == torch.float32 and O.shape == Q.shape
     LSE = torch.empty((B, h, L), device=Q.device, dtype=torch.float32)
     cfg = FlashCfg(B, h, L, d, int(causal), float(scale), float(eps), 64, 64)
     lib = _lib.load()
-    if Lk == L and not bias_bcast:
+    if bias is not None:
+        bias = _f32c(bias)
+    stride = 0 if (bias is None or bias_bcast) else h * L * Lk
+    if half:
+        rc = lib.ppml_b200_flash_attn_forward_16(C.byref(cfg), Lk, stride, _p(Q), _p(K), _p(V), _p(bias), _p(O), _p(LSE),
+                                                 int(Q.dtype == torch.bfloat16), path, _stream())
+    elif Lk == L and not bias_bcast:
         rc = lib.ppml_b200_flash_attn_forward(C.byref(cfg), _p(Q), _p(K), _p(V), _p(bias), _p(O), _p(LSE), path, _stream())
     else:
-        stride = 0 if (bias is None or bias_bcast) else h * L * Lk
         rc = lib.ppml_b200_flash_attn_forward_ex(C.byref(cfg), Lk, stride, _p(Q), _p(K), _p(V), _p(bias), _p(O), _p(LSE),
                                                  path, _stream())
     _check(rc, "flash_attn_forward")

@@ -304,6 +304,50 @@ def test_attention_tensor_cores_masked_rows():
     assert np.all(O[0, 0, 2] == 0) and LSE[0, 0, 2] == -np.inf and np.isfinite(O).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,h,L,d,Lk,bias,bcast,causal", [
+    (4, 8, 256, 32, None, True, True, False),      # full-size rows, one bias shared by the batch
+    (3, 2, 256, 32, None, True, False, False),     # full bias tensor
+    (2, 4, 51, 32, None, False, False, False),     # dev size without bias (zero-filled key tail, masked)
+    (2, 2, 300, 32, None, True, False, False),     # three key tiles: every ring wraps
+    (2, 3, 100, 32, 76, True, False, False),       # Lq != Lk
+    (2, 2, 200, 32, None, False, False, True),     # causal
+    (2, 2, 40, 8, None, True, False, False),       # head dim 8: CUDA-core kernel on 16-bit operands
+])
+def test_attention_16bit(oracle, dtype, B, h, L, d, Lk, bias, bcast, causal):
+    """16-bit Q/K/V: against the fp32 checker fed the rounded operands (P is rounded to 16 bits on the tensor-core
+    path, hence 1e-2 there) and against the unrounded ones (1e-2)."""
+    Q, K, V, bi = cases.attn_case(B, h, L, d, Lk=Lk, seed=5, bias=bias, bias_bcast=bcast)
+    scale = 1 / np.sqrt(32.0)
+    q16, k16, v16 = dev(Q).to(dtype), dev(K).to(dtype), dev(V).to(dtype)
+    r16, l16 = oracle.flash_attn(host(q16.float()), host(k16.float()), host(v16.float()), bi, scale=scale, bias_bcast=bcast,
+                                 causal=causal)
+    r32, _ = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast, causal=causal)
+    b = None if bi is None else dev(bi)
+    for path in (PATH_SIMT, PATH_AUTO) + ((PATH_UMMA,) if d == 32 else ()):
+        O, LSE = ops.flash_attn_forward_cuda(q16, k16, v16, b, scale=scale, bias_bcast=bcast, causal=causal, path=path)
+        tol = TOL_FP32 if (path == PATH_SIMT or d != 32) else 1e-2
+        assert cases.rel_err(host(O), r16) <= tol, (path, cases.rel_err(host(O), r16))
+        assert np.abs(host(LSE) - l16).max() <= (1e-5 if tol == TOL_FP32 else 2e-3)
+        assert cases.rel_err(host(O), r32) <= 1e-2
+    if d != 32:
+        with pytest.raises(RuntimeError):
+            ops.flash_attn_forward_cuda(q16, k16, v16, b, scale=scale, path=PATH_UMMA)
+
+
+def test_attention_output_at_16_byte_offset(oracle):
+    """The destination only has to be 16-byte aligned: an address that is not a multiple of 32 takes the 128-bit stores."""
+    import torch
+    Q, K, V, bi = cases.attn_case(2, 2, 100, 32, seed=11)
+    buf = torch.zeros(Q.size + 8, device="cuda", dtype=torch.float32)
+    out = buf[4:4 + Q.size].view(*Q.shape)
+    assert out.data_ptr() % 32 == 16
+    O, _ = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=1 / np.sqrt(32.0), path=PATH_UMMA, out=out)
+    rO, _ = oracle.flash_attn(Q, K, V, bi, scale=1 / np.sqrt(32.0))
+    assert cases.rel_err(host(O), rO) <= TOL_TF32
+    assert float(buf[:4].abs().max()) == 0 and float(buf[-4:].abs().max()) == 0
+
+
 def test_attention_fully_masked_row():
     Q, K, V, bi = cases.attn_case(1, 1, 4, 8, seed=7)
     bi[0, 0, 2, :] = -np.inf
