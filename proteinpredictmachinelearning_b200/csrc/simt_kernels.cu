@@ -390,10 +390,224 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
     }
 }
 
+// =============================================================================================
+// Small head dims (4, 8, 16: the extra-MSA blocks use 8): one thread per query row, 128 rows per CTA.  Keys are
+// walked in tiles of 32; the K and V tiles are staged in shared memory as fp32 (every thread reads the same key, so
+// the reads are broadcasts), the 32 scores of a tile stay in registers, and the running maximum / sum / output
+// accumulator are per-thread scalars: no shuffles and no cross-lane reductions.  Same arithmetic contract as the
+// kernel above; exp is 2^((s - m) log2 e) on the transcendental unit.
+// =============================================================================================
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
+                      const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
+                      int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride) {
+    constexpr int kTile = 32;
+    constexpr float kLog2e = 1.4426950408889634f;
+    __shared__ __align__(16) float ks[kTile * D];
+    __shared__ __align__(16) float vs[kTile * D];
+    const int i = blockIdx.x * 128 + threadIdx.x;
+    const int hh = blockIdx.y, b = blockIdx.z;
+    const size_t bh = static_cast<size_t>(b) * H + hh;
+    const T* Kb = K + bh * static_cast<size_t>(Lk) * D;
+    const T* Vb = V + bh * static_cast<size_t>(Lk) * D;
+    const bool row_ok = i < L;
+    float q[D];
+#pragma unroll
+    for (int dd = 0; dd < D; ++dd) q[dd] = row_ok ? attn_ld(Q + (bh * L + i) * D + dd) * scale : 0.0f;
+    // bias: every warp brings the 32 x 32 tile of its own rows through shared memory (row by row, 128 contiguous bytes
+    // per load) and each thread then reads its row back with 16-byte loads; the pitch of 36 floats keeps both sides
+    // free of bank conflicts
+    constexpr int kPitch = 36;
+    __shared__ __align__(16) float bs[128 * kPitch];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wrow0 = blockIdx.x * 128 + warp * 32;              // first query row of this warp
+    const float* Bw = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
+                                 (static_cast<size_t>(hh) * L + wrow0) * static_cast<size_t>(Lk) : nullptr;
+    const int jmax = row_ok ? (causal ? min(i + 1, Lk) : Lk) : 0;
+    // keys needed by any row of this CTA
+    const int last_row = min(blockIdx.x * 128 + 127, L - 1);
+    const int jend = causal ? min(last_row + 1, Lk) : Lk;
+    float m = -CUDART_INF_F, l = 0.0f;
+    float acc[D];
+#pragma unroll
+    for (int dd = 0; dd < D; ++dd) acc[dd] = 0.0f;
+    for (int j0 = 0; j0 < jend; j0 += kTile) {
+        __syncthreads();                             // the previous tile has been consumed
+        for (int e = threadIdx.x; e < kTile * D; e += 128) {
+            const int j = j0 + e / D;
+            ks[e] = (j < Lk) ? attn_ld(Kb + static_cast<size_t>(j0) * D + e) : 0.0f;
+            vs[e] = (j < Lk) ? attn_ld(Vb + static_cast<size_t>(j0) * D + e) : 0.0f;
+        }
+        if (Bw) {
+            const bool col_ok = j0 + lane < Lk;
+#pragma unroll 8
+            for (int rr = 0; rr < 32; ++rr)
+                bs[(warp * 32 + rr) * kPitch + lane] =
+                    (col_ok && wrow0 + rr < L) ? __ldg(Bw + static_cast<size_t>(rr) * Lk + j0 + lane) : 0.0f;
+        }
+        __syncthreads();
+        if (j0 >= jmax) continue;                    // nothing visible to this row in the tile (still joins the barriers)
+        float x[kTile];
+        float mt = -CUDART_INF_F;
+#pragma unroll
+        for (int t = 0; t < kTile; ++t) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int dd = 0; dd < D; ++dd) dot = fmaf(q[dd], ks[t * D + dd], dot);
+            x[t] = dot;
+        }
+        if (Bw) {
+#pragma unroll
+            for (int t4 = 0; t4 < kTile / 4; ++t4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(bs + threadIdx.x * kPitch + t4 * 4);
+                x[t4 * 4] += b4.x; x[t4 * 4 + 1] += b4.y; x[t4 * 4 + 2] += b4.z; x[t4 * 4 + 3] += b4.w;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kTile; ++t) {
+            if (j0 + t >= jmax) x[t] = -CUDART_INF_F;
+            mt = fmaxf(mt, x[t]);
+        }
+        const float m_new = fmaxf(m, mt);
+        if (m_new == -CUDART_INF_F) continue;        // every key so far is masked for this row
+        const float alpha = (m == -CUDART_INF_F) ? 0.0f : exp2f((m - m_new) * kLog2e);
+        const float ml2 = m_new * kLog2e;
+        float lt = 0.0f;
+#pragma unroll
+        for (int dd = 0; dd < D; ++dd) acc[dd] *= alpha;
+#pragma unroll
+        for (int t = 0; t < kTile; ++t) {
+            const float pj = exp2f(fmaf(x[t], kLog2e, -ml2));      // 2^-inf = 0 for masked keys
+            lt += pj;
+#pragma unroll
+            for (int dd = 0; dd < D; ++dd) acc[dd] = fmaf(pj, vs[t * D + dd], acc[dd]);
+        }
+        l = fmaf(l, alpha, lt);
+        m = m_new;
+    }
+    if (!row_ok) return;
+    float* o = O + (bh * L + i) * D;
+    float inv = 0.0f, lse = -CUDART_INF_F;
+    if (l > 0.0f) { inv = 1.0f / (l + eps); lse = m + logf(l + eps); }
+#pragma unroll
+    for (int dd = 0; dd < D; ++dd) o[dd] = acc[dd] * inv;
+    if (LSE) LSE[bh * L + i] = lse;
+}
+
+// Small head dims with few query rows (global column attention: one query over all keys): one warp per query row,
+// every lane keeps a private running maximum / sum / accumulator over the keys lane, lane + 32, ..., and the 32 partial
+// results are merged at the end (rescaled to the common maximum, then summed with shuffles).
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
+                     const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
+                     int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, long long rows_total) {
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int lane = threadIdx.x & 31;
+    const long long row = blockIdx.x * 4LL + (threadIdx.x >> 5);          // flattened (batch, head, query)
+    if (row >= rows_total) return;
+    const int i = static_cast<int>(row % L);
+    const long long bh = row / L;
+    const int hh = static_cast<int>(bh % H);
+    const long long b = bh / H;
+    float q[D];
+#pragma unroll
+    for (int dd = 0; dd < D; ++dd) q[dd] = attn_ld(Q + row * D + dd) * scale;
+    const T* Kb = K + bh * static_cast<long long>(Lk) * D;
+    const T* Vb = V + bh * static_cast<long long>(Lk) * D;
+    const float* Bb = bias ? bias + b * bias_batch_stride + (static_cast<long long>(hh) * L + i) * Lk : nullptr;
+    const int jmax = causal ? min(i + 1, Lk) : Lk;
+    float m = -CUDART_INF_F, l = 0.0f;
+    float acc[D];
+#pragma unroll
+    for (int dd = 0; dd < D; ++dd) acc[dd] = 0.0f;
+#pragma unroll 4
+    for (int j = lane; j < jmax; j += 32) {
+        float s = 0.0f;
+#pragma unroll
+        for (int dd = 0; dd < D; ++dd) s = fmaf(q[dd], attn_ld(Kb + static_cast<long long>(j) * D + dd), s);
+        if (Bb) s += Bb[j];
+        const float m_new = fmaxf(m, s);
+        if (m_new == -CUDART_INF_F) continue;                             // masked key, nothing visible before it
+        const float alpha = exp2f((m - m_new) * kLog2e);                  // m = -inf gives 0
+        const float pj = exp2f((s - m_new) * kLog2e);
+        l = fmaf(l, alpha, pj);
+#pragma unroll
+        for (int dd = 0; dd < D; ++dd) acc[dd] = fmaf(acc[dd], alpha, pj * attn_ld(Vb + static_cast<long long>(j) * D + dd));
+        m = m_new;
+    }
+    float mw = m;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, off));
+    const float f = (m == -CUDART_INF_F) ? 0.0f : exp2f((m - mw) * kLog2e);
+    l *= f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    float inv = 0.0f, lse = -CUDART_INF_F;
+    if (l > 0.0f) { inv = 1.0f / (l + eps); lse = mw + logf(l + eps); }
+#pragma unroll
+    for (int dd = 0; dd < D; ++dd) {
+        float a = acc[dd] * f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        if (lane == 0) O[row * D + dd] = a * inv;
+    }
+    if (LSE && lane == 0) LSE[row] = lse;
+}
+
+template <typename T>
+bool launch_attn_keylanes(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
+                          int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, cudaStream_t st) {
+    const long long rows = static_cast<long long>(B) * H * L;
+    const long long blocks = (rows + 3) / 4;
+    if (blocks > 0x7fffffffLL) return false;
+    const unsigned grid = static_cast<unsigned>(blocks);
+    if (d == 4) attn_keylanes_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows);
+    else if (d == 8) attn_keylanes_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows);
+    else if (d == 16) attn_keylanes_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows);
+    else return false;
+    return true;
+}
+
+template <typename T>
+bool launch_attn_rowthread(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
+                           int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, cudaStream_t st) {
+    dim3 grid((L + 127) / 128, H, B);
+    if (d == 4) attn_rowthread_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride);
+    else if (d == 8) attn_rowthread_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride);
+    else if (d == 16) attn_rowthread_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride);
+    else return false;
+    return true;
+}
+
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                         long long bias_batch_stride, cudaStream_t st) {
     if (d > 128 || H > 65535 || B > 65535 || elem < 0 || elem > 2) return ST_BAD_ARGS;
+    // small head dims with enough query rows to fill CTAs of one thread per row
+    if ((d == 4 || d == 8 || d == 16) && L < 32) {
+        bool done;
+        if (elem == 0) done = launch_attn_keylanes(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
+                                                   bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+        else if (elem == 1) done = launch_attn_keylanes(static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
+                                                        static_cast<const __nv_bfloat16*>(V), bias, O, LSE, B, H, L, Lk, d, causal, scale, eps,
+                                                        bias_batch_stride, st);
+        else done = launch_attn_keylanes(static_cast<const __half*>(Q), static_cast<const __half*>(K), static_cast<const __half*>(V),
+                                         bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+        if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+    }
+    if ((d == 4 || d == 8 || d == 16) && L >= 32) {
+        bool done;
+        if (elem == 0) done = launch_attn_rowthread(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
+                                                    bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+        else if (elem == 1) done = launch_attn_rowthread(static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
+                                                         static_cast<const __nv_bfloat16*>(V), bias, O, LSE, B, H, L, Lk, d, causal, scale, eps,
+                                                         bias_batch_stride, st);
+        else done = launch_attn_rowthread(static_cast<const __half*>(Q), static_cast<const __half*>(K), static_cast<const __half*>(V),
+                                          bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+        if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+    }
     dim3 grid((L + 3) / 4, H, B);
     const size_t smem = 4 * d * sizeof(float);
     if (elem == 0)

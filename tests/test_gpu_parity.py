@@ -274,6 +274,31 @@ def test_attention_shapes(oracle, B, h, L, d, Lk, bias, bcast):
     assert cases.rel_err(host(O), legacy) <= TOL_FP32
 
 
+@pytest.mark.parametrize("B,h,L,d,Lk,bias,bcast,causal", [
+    (2, 3, 200, 8, None, True, True, False),    # thread-per-row kernel: two row tiles, shared bias
+    (2, 2, 70, 16, 45, True, False, False),     # Lq != Lk, ragged key tile
+    (2, 2, 150, 4, None, False, False, True),   # causal: row tiles see different key ranges
+    (3, 2, 33, 8, 130, True, False, True),      # causal with Lk > L
+    (2, 3, 5, 4, 100, True, False, False),      # few query rows: keys over lanes, with bias
+    (4, 2, 1, 8, 1024, False, False, False),    # global column attention at full key count
+    (2, 2, 20, 16, None, False, False, True),   # few rows, causal (lanes without any visible key)
+])
+def test_attention_small_head_dims(oracle, B, h, L, d, Lk, bias, bcast, causal):
+    Q, K, V, bi = cases.attn_case(B, h, L, d, Lk=Lk, seed=9, bias=bias, bias_bcast=bcast)
+    if bi is not None:
+        bi[..., 1, :] = -np.inf                  # one fully masked query row per head
+        bi[..., 0, ::3] = -np.inf                # and a partly masked one
+    scale = 1 / np.sqrt(32.0)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None if bi is None else dev(bi), scale=scale, bias_bcast=bcast,
+                                         causal=causal)
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast, causal=causal)
+    O, LSE = host(O), host(LSE)
+    assert np.isfinite(O).all()
+    assert cases.rel_err(O, rO) <= TOL_FP32
+    fin = np.isfinite(rL)
+    assert np.array_equal(np.isfinite(LSE), fin) and np.abs(LSE[fin] - rL[fin]).max() <= 1e-5
+
+
 @pytest.mark.parametrize("B,h,L,Lk,bias,bcast,causal", [
     (4, 8, 256, None, True, True, False),       # full-size rows, one bias shared by the batch
     (3, 2, 256, None, True, False, False),      # full bias tensor
