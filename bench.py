@@ -259,13 +259,20 @@ def run_ours(args):
         d[0] += e0.elapsed_time(e1)
         d[1] += 1
     umma_launches = sum(1 for (_, taken, _, _) in events if taken == 1)
+    # kernels launched in the timed region: the product kernel of every shape, plus the activation quantizer of the
+    # shapes that take the two-pass form (the library reports which)
+    from proteinpredictmachinelearning_b200 import _lib
+    kernel_launches = sum((_lib.load().ppml_b200_q8_kernel_launches(s[2], s[0], s[1]) if (taken == 1 and args.kernel == "q8") else 1)
+                          for (s, taken, _, _) in events)
 
     # ---- timed region 2: end to end with host buffers ("e2e") ----------------------------------------
     if args.no_e2e:
         if rank == 0:
             print(json.dumps({"only": args.only, "ms_per_step": ms / args.steps, "kernel_ms_per_step": kernel_ms / args.steps,
                               "tflops": step_flops * args.steps / (kernel_ms * 1e-3) / 1e12,
-                              "gbs": step_bytes * args.steps / (kernel_ms * 1e-3) / 1e9}), flush=True)
+                              "gbs": step_bytes * args.steps / (kernel_ms * 1e-3) / 1e9,
+                              "per_shape_us": {"%dx%dx%d" % s: 1e3 * v[0] / v[1] for s, v in sorted(per_shape.items())}}),
+                  flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -364,7 +371,7 @@ def run_ours(args):
                      "kernel": "umma_q8_kernel, all launches of the timed region (sum of algorithmic bytes / sum of durations)"},
         "e2e": {"value": step_flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": len(events), "tensor_core_launches": umma_launches, "clocks": clocks,
+        "gpu_launches": kernel_launches, "tensor_core_launches": umma_launches, "clocks": clocks,
         "per_shape": [{"M": s[0], "K": s[1], "N": s[2], "us": 1e3 * v[0] / v[1],
                        "tflops": q8_flops(*s) / (v[0] / v[1] * 1e-3) / 1e12,
                        "gbs": q8_bytes(*s) / (v[0] / v[1] * 1e-3) / 1e9, "tensor_cores": v[2]} for s, v in sorted(per_shape.items())],
@@ -434,7 +441,13 @@ def main():
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs)")
     ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn"],
                     help="profiling runs with --no-e2e: time the fp32 (tf32 tensor-core) or bf16 mul_mat on the same shapes")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "block"],
+                    help="block: the hot-path op sequence of one main IterBlock at full size, sharded over --gpus ranks "
+                         "(proteinpredictmachinelearning_b200/block_bench.py); prints its own JSON line")
     args = ap.parse_args()
+    if args.workload == "block":
+        from proteinpredictmachinelearning_b200 import block_bench
+        return block_bench.run(args.gpus, args.steps, args.warmup)
     if args.kernel == "attn":
         return attn_profile(args)
     if args.impl == "reference":

@@ -77,6 +77,12 @@ int ppml_b200_cast_f32_to_bf16(const float* x, void* y, int64_t n, void* stream)
  * sumi_out (may be NULL) receives the exact int32 block sums as [N][M][K/32]. */
 int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, int K, int wtype, int c_trans,
                          const float* bias, int32_t* sumi_out, int path, int* path_out, void* stream);
+/* The tensor-core form either quantizes the activations inside the product kernel (one pass over X) or in a kernel
+ * of its own into a library-owned scratch buffer, as the reference's launcher does (src/cuda/MulMatQ8Kernel.cu:483-487);
+ * results are identical bit for bit.  mode < 0: chosen per shape (default), 0: always one pass, 1: always two. */
+void ppml_b200_set_q8_two_pass(int mode);
+/* Kernels one tensor-core call of this shape launches under the current mode (1 or 2); for launch accounting. */
+int ppml_b200_q8_kernel_launches(int M, int N, int K);
 
 /* Q8 mul_mat that never allocates device memory.  It has no counterpart in the reference (whose launcher
  * grows a cudaMalloc'ed scratch, src/cuda/MulMatQ8Kernel.cu:430-449).  For callers that cannot allocate
@@ -165,6 +171,12 @@ int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst,
 /* 16-bit operands (fp16 / bfloat16), fp32 accumulation and output; no counterpart in the reference. */
 int ppml_b200_outer_prod_mean_16(const void* left16, const void* right16, float* dst, int64_t D, int64_t L,
                                  int64_t N, int64_t B, float inv_N, int is_bf16, int path, void* stream);
+/* One rank's share of the op when `left` is split into contiguous d1 slabs across GPUs: D_left slabs of `left`
+ * ([D_left][L][N][B]) against all D slabs of `right`; dst [D_left * D][L][L][B] is that rank's contiguous part of
+ * the full result (src/backend/CPUKernels.cpp:1022-1028: output block (d1, d2) reads slab d1 of left and slab d2
+ * of right only). */
+int ppml_b200_outer_prod_mean_slabs(const float* left, const float* right, float* dst, int64_t D_left, int64_t D,
+                                    int64_t L, int64_t N, int64_t B, float inv_N, int path, void* stream);
 
 /* ---- per-shape statistics ----------------------------------------------------------------------------
  * Replace mulmat_stats_cuda_begin / mulmat_stats_cuda_end (src/backend/CUDAKernels.cpp:190-191;

@@ -45,6 +45,9 @@ SIGNATURES = {
     "ppml_b200_outer_prod_mean": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _f, _i, _vp]),
     "ppml_b200_tri_mul_16": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _i, _vp]),
     "ppml_b200_outer_prod_mean_16": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _f, _i, _i, _vp]),
+    "ppml_b200_set_q8_two_pass": (None, [_i]),
+    "ppml_b200_q8_kernel_launches": (_i, [_i, _i, _i]),
+    "ppml_b200_outer_prod_mean_slabs": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f, _i, _vp]),
     "ppml_b200_mulmat_stats_begin": (None, [_i, _i, _i]),
     "ppml_b200_mulmat_stats_end": (None, [C.c_char_p]),
     "ppml_b200_mulmat_stats_dump": (_i, [C.c_char_p, _i]),

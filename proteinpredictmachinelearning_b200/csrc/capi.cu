@@ -41,6 +41,20 @@ void* ensure_scratch(size_t bytes) {
     return p;
 }
 
+// Whether the tensor-core Q8 product quantizes its activations in a kernel of its own (into the shared scratch) instead
+// of inside the product kernel.  Measured on the sweep shapes: the one-pass form wins wherever there are more token
+// tiles than SMs (33 vs 44 us at 65536 x 128 x 128, 126 vs 197 us at 65536 x 1024 x 128: the extra pass over X costs
+// more than the quantizer warps do); with few token tiles and a long K the in-kernel quantizer is a serial chain of
+// K / 32 steps on two or four warps, and the two-pass form wins (33 vs 41 us at 408 x 1024 x N, 58 vs 68 us at
+// 2601 x 1024 x 1024).  PPML_B200_Q8_TWO_PASS=0 / 1 or ppml_b200_set_q8_two_pass() force the choice (measurements, tests).
+int g_q8_two_pass = [] { const char* e = std::getenv("PPML_B200_Q8_TWO_PASS"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
+bool q8_two_pass(int M, int N, int K) {
+    const int forced = g_q8_two_pass;
+    if (forced >= 0) return forced == 1;
+    (void)M;
+    return (N + 127) / 128 <= num_sms() && K >= 1024;
+}
+
 int mul_mat_any(const void* A, const void* B, float* C, int M, int K, int N, const float* bias, int path,
                 int elem, int tf32_mode, cudaStream_t st) {
     if (!A || !B || !C || M <= 0 || K <= 0 || N <= 0 || !path_ok(path)) return ST_BAD_ARGS;
@@ -117,6 +131,9 @@ int ppml_b200_cast_f32_to_bf16(const float* x, void* y, int64_t n, void* stream)
     return launch_cast(x, y, n, 1, as_stream(stream));
 }
 
+void ppml_b200_set_q8_two_pass(int mode) { g_q8_two_pass = mode < 0 ? -1 : (mode ? 1 : 0); }
+int ppml_b200_q8_kernel_launches(int M, int N, int K) { return q8_two_pass(M, N, K) ? 2 : 1; }
+
 int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, int K, int wtype, int c_trans,
                          const float* bias, int32_t* sumi_out, int path, int* path_out, void* stream) {
     if (path_out) *path_out = 0;
@@ -126,7 +143,16 @@ int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, 
     cudaStream_t st = as_stream(stream);
     if (path != PPML_B200_PATH_SIMT) {
         int rc = ST_UNSUPPORTED_PATH;
-        if (wtype == 2) rc = launch_umma_q8(W, X, C, M, N, K, c_trans, bias, sumi_out, st);
+        if (wtype == 2) {
+            // two-pass form (activations quantized by a kernel of their own into the shared scratch) or one-pass form
+            void* scratch = nullptr;
+            std::unique_lock<std::mutex> lock(g_scratch_mtx, std::defer_lock);
+            if (q8_two_pass(M, N, K)) {
+                lock.lock();
+                scratch = ensure_scratch(umma_q8_scratch_bytes(N, K));
+            }
+            rc = launch_umma_q8(W, X, C, M, N, K, c_trans, bias, sumi_out, st, scratch);
+        }
         if (rc == ST_OK && path_out) *path_out = 1;
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
     }
@@ -262,15 +288,16 @@ int ppml_b200_tri_mul_16(const void* left16, const void* right16, float* dst, in
     return tri_mul_any(left16, right16, dst, D, I, J, K, B, inv_L, outgoing, path, is_bf16 ? 2 : 1, as_stream(stream));
 }
 
-static int outer_prod_mean_any(const void* left, const void* right, float* dst, int64_t D, int64_t L,
+// D1 slabs of `left` against all D slabs of `right` (D1 == D for the whole op; D1 < D for one rank's d1 range)
+static int outer_prod_mean_any(const void* left, const void* right, float* dst, int64_t D1, int64_t D, int64_t L,
                                int64_t N, int64_t B, float inv_N, int path, int elem, cudaStream_t st) {
-    if (!left || !right || !dst || D <= 0 || L <= 0 || N <= 0 || B <= 0 || !path_ok(path)) return ST_BAD_ARGS;
+    if (!left || !right || !dst || D1 <= 0 || D <= 0 || L <= 0 || N <= 0 || B <= 0 || !path_ok(path)) return ST_BAD_ARGS;
     if (path != PPML_B200_PATH_SIMT) {
         int rc = ST_UNSUPPORTED_PATH;
-        if (B == 1 && D * L <= 0x7fffffff && N <= 0x7fffffff) {
+        if (B == 1 && D * L <= 0x7fffffff && D1 * L <= 0x7fffffff && N <= 0x7fffffff) {
             UmmaGemmArgs a{};
             a.A = left; a.B = right; a.C = dst;
-            a.M = static_cast<int>(D * L); a.N = static_cast<int>(D * L); a.K = static_cast<int>(N); a.batch = 1;
+            a.M = static_cast<int>(D1 * L); a.N = static_cast<int>(D * L); a.K = static_cast<int>(N); a.batch = 1;
             a.lda = N; a.ldb = N; a.ldc = D * L; a.alpha = inv_N;
             a.opm_D = static_cast<int>(D); a.opm_L = static_cast<int>(L); a.elem = elem; a.tf32_mode = PPML_B200_TF32_TMA;
             rc = launch_umma_gemm(a, st);
@@ -278,7 +305,7 @@ static int outer_prod_mean_any(const void* left, const void* right, float* dst, 
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
     }
     SimtContract p{};
-    p.M = D * L; p.N = D * L; p.K = N;
+    p.M = D1 * L; p.N = D * L; p.K = N;
     p.a_sm = N * B; p.a_sk = B; p.b_sn = N * B; p.b_sk = B;
     p.planes = B; p.ne2 = B;
     p.a_s2 = 1; p.a_div2 = 1; p.a_div3 = 1; p.b_s2 = 1; p.c_s2 = 1;
@@ -289,12 +316,17 @@ static int outer_prod_mean_any(const void* left, const void* right, float* dst, 
 
 int ppml_b200_outer_prod_mean(const float* left, const float* right, float* dst, int64_t D, int64_t L,
                               int64_t N, int64_t B, float inv_N, int path, void* stream) {
-    return outer_prod_mean_any(left, right, dst, D, L, N, B, inv_N, path, 0, as_stream(stream));
+    return outer_prod_mean_any(left, right, dst, D, D, L, N, B, inv_N, path, 0, as_stream(stream));
 }
 
 int ppml_b200_outer_prod_mean_16(const void* left16, const void* right16, float* dst, int64_t D, int64_t L,
                                  int64_t N, int64_t B, float inv_N, int is_bf16, int path, void* stream) {
-    return outer_prod_mean_any(left16, right16, dst, D, L, N, B, inv_N, path, is_bf16 ? 2 : 1, as_stream(stream));
+    return outer_prod_mean_any(left16, right16, dst, D, D, L, N, B, inv_N, path, is_bf16 ? 2 : 1, as_stream(stream));
+}
+
+int ppml_b200_outer_prod_mean_slabs(const float* left, const float* right, float* dst, int64_t D_left, int64_t D,
+                                    int64_t L, int64_t N, int64_t B, float inv_N, int path, void* stream) {
+    return outer_prod_mean_any(left, right, dst, D_left, D, L, N, B, inv_N, path, 0, as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

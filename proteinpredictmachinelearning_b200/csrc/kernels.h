@@ -55,7 +55,8 @@ struct UmmaGemmArgs {
 int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st);
 
 int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
-                   int* sumi_out, cudaStream_t st);
+                   int* sumi_out, cudaStream_t st, void* scratch = nullptr);
+size_t umma_q8_scratch_bytes(int N, int K);
 
 int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,

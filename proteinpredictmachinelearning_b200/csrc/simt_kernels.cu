@@ -404,8 +404,13 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
                       int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride) {
     constexpr int kTile = 32;
     constexpr float kLog2e = 1.4426950408889634f;
-    __shared__ __align__(16) float ks[kTile * D];
-    __shared__ __align__(16) float vs[kTile * D];
+    constexpr int kPer = (kTile * D + 127) / 128;               // K (and V) elements each thread moves per tile
+    constexpr int kPitch = 36;
+    // two stages of everything: the next tile's K / V travel through registers and its bias through cp.async while
+    // the current tile is consumed
+    __shared__ __align__(16) float ks_all[2][kTile * D];
+    __shared__ __align__(16) float vs_all[2][kTile * D];
+    __shared__ __align__(16) float bs_all[2][128 * kPitch];
     const int i = blockIdx.x * 128 + threadIdx.x;
     const int hh = blockIdx.y, b = blockIdx.z;
     const size_t bh = static_cast<size_t>(b) * H + hh;
@@ -416,10 +421,8 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
 #pragma unroll
     for (int dd = 0; dd < D; ++dd) q[dd] = row_ok ? attn_ld(Q + (bh * L + i) * D + dd) * scale : 0.0f;
     // bias: every warp brings the 32 x 32 tile of its own rows through shared memory (row by row, 128 contiguous bytes
-    // per load) and each thread then reads its row back with 16-byte loads; the pitch of 36 floats keeps both sides
+    // per request) and each thread then reads its row back with 16-byte loads; the pitch of 36 floats keeps both sides
     // free of bank conflicts
-    constexpr int kPitch = 36;
-    __shared__ __align__(16) float bs[128 * kPitch];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wrow0 = blockIdx.x * 128 + warp * 32;              // first query row of this warp
     const float* Bw = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
@@ -432,21 +435,48 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
     float acc[D];
 #pragma unroll
     for (int dd = 0; dd < D; ++dd) acc[dd] = 0.0f;
-    for (int j0 = 0; j0 < jend; j0 += kTile) {
-        __syncthreads();                             // the previous tile has been consumed
-        for (int e = threadIdx.x; e < kTile * D; e += 128) {
-            const int j = j0 + e / D;
-            ks[e] = (j < Lk) ? attn_ld(Kb + static_cast<size_t>(j0) * D + e) : 0.0f;
-            vs[e] = (j < Lk) ? attn_ld(Vb + static_cast<size_t>(j0) * D + e) : 0.0f;
+    float kreg[kPer], vreg[kPer];
+    auto fetch_kv = [&](int j0) {
+#pragma unroll
+        for (int c = 0; c < kPer; ++c) {
+            const int e = threadIdx.x + c * 128;
+            const bool ok = e < kTile * D && j0 + e / D < Lk;
+            kreg[c] = ok ? attn_ld(Kb + static_cast<size_t>(j0) * D + e) : 0.0f;
+            vreg[c] = ok ? attn_ld(Vb + static_cast<size_t>(j0) * D + e) : 0.0f;
         }
+    };
+    auto fetch_bias = [&](int j0, int buf) {
         if (Bw) {
             const bool col_ok = j0 + lane < Lk;
 #pragma unroll 8
-            for (int rr = 0; rr < 32; ++rr)
-                bs[(warp * 32 + rr) * kPitch + lane] =
-                    (col_ok && wrow0 + rr < L) ? __ldg(Bw + static_cast<size_t>(rr) * Lk + j0 + lane) : 0.0f;
+            for (int rr = 0; rr < 32; ++rr) {
+                float* dst = &bs_all[buf][(warp * 32 + rr) * kPitch + lane];
+                if (col_ok && wrow0 + rr < L) {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+                                 "l"(Bw + static_cast<size_t>(rr) * Lk + j0 + lane) : "memory");
+                } else {
+                    *dst = 0.0f;
+                }
+            }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_kv(0);
+    fetch_bias(0, 0);
+    for (int j0 = 0, tile = 0; j0 < jend; j0 += kTile, ++tile) {
+        const int buf = tile & 1;
+        float* ks = ks_all[buf];
+        float* vs = vs_all[buf];
+        const float* bs = bs_all[buf];
+        // this stage was last read two tiles ago, and every thread has passed the barrier of the tile in between
+#pragma unroll
+        for (int c = 0; c < kPer; ++c) {
+            const int e = threadIdx.x + c * 128;
+            if (e < kTile * D) { ks[e] = kreg[c]; vs[e] = vreg[c]; }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
+        if (j0 + kTile < jend) { fetch_kv(j0 + kTile); fetch_bias(j0 + kTile, buf ^ 1); }
         if (j0 >= jmax) continue;                    // nothing visible to this row in the tile (still joins the barriers)
         float x[kTile];
         float mt = -CUDART_INF_F;

@@ -66,6 +66,9 @@ struct Q8Params {
                                // and double-buffered across items, 3 = a short ring (items with a single column block)
     int dw_tabs;               // scale tables held in smem: n_blocks (all resident, filled once) or 1 (refilled per column block)
     int staged;                // 1: results leave through per-warp transposition buffers (row-contiguous stores)
+    int preq;                  // 1: the activations were quantized by a kernel of their own: int8 tiles and scale tables
+                               //    come in by TMA, the quantizer warps idle (tmX then maps the int8 matrix)
+    const __half* da_t;        // preq: activation scales [token tile][nblk][128]
     const __half* Wd;          // weight scales [Mout][nblk]
     float* C;
     const float* bias;
@@ -223,6 +226,53 @@ __device__ __forceinline__ void quantize_rows2(const uint8_t* raw, uint8_t* at, 
     d_out0 = d[0]; d_out1 = d[1];
 }
 
+// Activation quantizer as a kernel of its own (the two-pass form of the product): X fp32 [Ntok][K] -> int8 [Ntok][K]
+// plus the block scales as fp16 [token tile][nblk][128], the layout the product kernel's scale table has in shared
+// memory.  Eight threads per quant block, four elements each; same rule, bit for bit, as quantize_row above (the first
+// element of maximum magnitude gives d = vmax / -128; q = round-half-away(x * (1 / d)) saturated to [-128, 127]).
+// Rows past Ntok (the tail of the last token tile) only get a zero scale.
+__global__ void __launch_bounds__(256)
+quantize_q8_planar_kernel(const float* __restrict__ X, int8_t* __restrict__ Aq, __half* __restrict__ da_t,
+                          int Ntok, int K, int nblk, long long nthreads) {
+    const long long g = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (g >= nthreads) return;                    // nthreads is a multiple of 8: whole 8-thread groups leave together
+    const int sub = static_cast<int>(g & 7);
+    const long long ib = g >> 3;
+    const int row = static_cast<int>(ib / nblk), kb = static_cast<int>(ib - static_cast<long long>(row) * nblk);
+    const bool live = row < Ntok;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const size_t off = static_cast<size_t>(row) * K + kb * 32 + sub * 4;
+    if (live) v = *reinterpret_cast<const float4*>(X + off);
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    float amax = fabsf(x[0]), vmax = x[0];
+    int idx = sub * 4;
+#pragma unroll
+    for (int e = 1; e < 4; ++e) {
+        if (fabsf(x[e]) > amax) { amax = fabsf(x[e]); vmax = x[e]; idx = sub * 4 + e; }
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+        const float ov = __shfl_xor_sync(0xffffffffu, vmax, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oa > amax || (oa == amax && oi < idx)) { amax = oa; vmax = ov; idx = oi; }
+    }
+    const float d = (amax == 0.0f) ? 0.0f : vmax * -0.0078125f;
+    const float inv = (d == 0.0f) ? 0.0f : 1.0f / d;
+    if (live) {
+        int qi[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float y = x[e] * inv;
+            float t;
+            asm("add.rz.f32 %0, %1, %2;" : "=f"(t) : "f"(y), "f"(copysignf(0.5f, y)));
+            qi[e] = f2i_rz(t);
+        }
+        *reinterpret_cast<uint32_t*>(Aq + off) = pack_s8(qi[1], qi[0], pack_s8(qi[3], qi[2], 0u));
+    }
+    if (sub == 0) da_t[(static_cast<size_t>(row >> 7) * nblk + kb) * 128 + (row & 127)] = __float2half_rn(d);
+}
+
 template <bool SUMI, int QW>      // SUMI: also write the raw int32 block sums (tests); QW: quantizer warps
 __global__ void __launch_bounds__(Roles<QW>::kThreads, 1)
 umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Q8Params p) {
@@ -259,7 +309,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1);
         }
         for (int k = 0; k < 2 * kMaxKT; ++k) {
-            mbar_init(a_full(k), kQuantWarps * 4);       // four arrivals per quantizer warp and K step (a short last step pads)
+            // four arrivals per quantizer warp and K step (a short last step pads); one by the TMA thread when the
+            // activations arrive quantized
+            mbar_init(a_full(k), p.preq ? 1 : kQuantWarps * 4);
             mbar_init(a_empty(k), 1);
         }
         for (int s = 0; s < 4; ++s) { mbar_init(t_full(s), 1); mbar_init(t_empty(s), kEpiWarps); }
@@ -319,7 +371,27 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             long long t0 = 0; uint32_t idle = 0;
             while (!(x_done && w_done)) {
                 bool progress = false;
-                if (!x_done && mbar_test(raw_empty(x_s), x_ph ^ 1u)) {
+                if (p.preq) {
+                    // quantized activations: one int8 tile per K step straight into the A ring (x_kb counts K steps, x_s /
+                    // x_ph are the ring position); the first step of an item also brings the item's scale table, once the
+                    // epilogue has finished with the table of this parity (two items ago)
+                    bool can = !x_done && mbar_test(a_empty(x_s), x_ph ^ 1u);
+                    if (can && x_kb == 0 && x_it >= 2) can = mbar_test(epi_done(x_it & 1u), ((x_it >> 1) - 1u) & 1u);
+                    if (can) {
+                        const uint32_t tab = (x_kb == 0) ? static_cast<uint32_t>(p.nblk) * 256u : 0u;
+                        mbar_arrive_expect_tx(a_full(x_s), kTile + tab);
+                        tma_load_3d(smem_base + L.a_off + x_s * kTile, &tmX, a_full(x_s), x_kb * 128, x_row0, 0);
+                        if (tab != 0u)
+                            bulk_load(smem_base + L.da_off + (x_it & 1u) * tab, p.da_t + static_cast<size_t>(x_mt) * p.nblk * 128, tab,
+                                      a_full(x_s));
+                        if (++x_s == p.AR) { x_s = 0; x_ph ^= 1u; }
+                        if (++x_kb == p.KT) {
+                            x_kb = 0; x_done = !item_at(++x_it, x_mt, x_nb0, x_nb1);
+                            x_row0 = x_mt * 128;
+                        }
+                        progress = true;
+                    }
+                } else if (!x_done && mbar_test(raw_empty(x_s), x_ph ^ 1u)) {
                     mbar_arrive_expect_tx(raw_full(x_s), kTile);
                     tma_load_3d(smem_base + L.raw_off + x_s * kTile, &tmX, raw_full(x_s), x_kb * 32, x_row0, 0);
                     if (++x_s == p.RS) { x_s = 0; x_ph ^= 1u; }
@@ -426,8 +498,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         __syncwarp();
     } else if (warp >= kFirstQuantWarp && warp < kFirstQuantWarp + kQuantWarps) {
         // ---------------- quantizers: warp 2 owns token rows 0-63 of the tile, warp 3 rows 64-127 ------------
+        // (nothing to do when the activations arrive quantized)
         const int row0 = (warp - kFirstQuantWarp) * (128 / kQuantWarps) + lane;
-        uint32_t n_it = 0, x_ph = 0; int x_s = 0; bool ok = true;
+        uint32_t n_it = 0, x_ph = 0; int x_s = 0; bool ok = p.preq == 0;
         uint32_t a_slot = 0, a_par = 0;                 // ring position of the K step being quantized
         TR_DECL;
         int mt = 0, nb0 = 0, nb1 = 0;
@@ -684,8 +757,16 @@ extern "C" int ppml_b200_q8_trace_read(long long* out64) {
 
 // W: Q8_0R weights ([Mout*nblk*32] int8 plane followed by [Mout*nblk] half scales); X fp32 [Ntok][K];
 // M = weight rows (out features), N = tokens, as in the reference's launcher.
+// Bytes of scratch the two-pass form needs for N tokens of K elements: the int8 matrix, then the scale tables.
+size_t umma_q8_scratch_bytes(int N, int K) {
+    const size_t aq = (static_cast<size_t>(N) * K + 255) & ~static_cast<size_t>(255);
+    return aq + static_cast<size_t>((N + 127) / 128) * (K / 32) * 256;
+}
+
+// scratch: null = quantize inside the product kernel (one pass over X, nothing written but C); otherwise a device
+// buffer of umma_q8_scratch_bytes(N, K) that receives the quantized activations from a kernel of its own first.
 int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
-                   int* sumi_out, cudaStream_t st) {
+                   int* sumi_out, cudaStream_t st, void* scratch) {
     if (!W || !X || !C || M <= 0 || N <= 0 || K <= 0) return ST_BAD_ARGS;
     if (K % 32) return ST_BAD_K;
     if (K > 128 * kMaxKT) return ST_UNSUPPORTED_PATH;
@@ -715,9 +796,10 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     // more token tiles than SMs and enough work per token tile (column blocks x K steps; measured break-even at 8) that
     // quantizing the cut tiles twice pays off: cut the work into equal contiguous ranges instead
     p.flat = (p.groups == 1 && p.n_blocks * p.KT >= 8 && p.m_tiles > sms && p.m_tiles % sms != 0) ? 1 : 0;
-    int abuf = (p.KT <= 2 && total_items > sms) ? 2 : 1;
+    p.preq = scratch != nullptr ? 1 : 0;
+    int abuf = ((p.KT <= 2 || p.preq) && total_items > sms) ? 2 : 1;
     const bool ring = p.blocks_per_group == 1 && p.KT >= 3;    // every item has one column block: A is consumed once
-    p.AR = ring ? 3 : p.KT * abuf;
+    p.AR = ring ? (p.preq ? 4 : 3) : p.KT * abuf;
     p.dw_tabs = (p.n_blocks * p.nblk * 512 <= 32 * 1024) ? p.n_blocks : 1;
     p.staged = p.vec_ok ? 1 : 0;
     auto stages_for = [&]() {
@@ -729,7 +811,10 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     int stages = stages_for();
     if (stages < 3) return ST_UNSUPPORTED_PATH;
     if (stages > 2 * kMaxStages) stages = 2 * kMaxStages;
-    if (p.blocks_per_group == 1) {
+    if (p.preq) {
+        // no raw fp32 stages: everything goes to the weight ring
+        p.RS = 0; p.BS = stages > kMaxStages ? kMaxStages : stages;
+    } else if (p.blocks_per_group == 1) {
         // the weights of an item are one pass over K: two stages suffice, the activation ring carries the HBM stream
         p.BS = 2; p.RS = stages - 2;
     } else {
@@ -741,6 +826,18 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     p.Wd = Wd; p.C = C; p.bias = bias; p.sumi_out = sumi_out; p.c_trans = c_trans; p.err = err;
 
     CUtensorMap tmX, tmW;
+    if (p.preq) {
+        if (reinterpret_cast<uintptr_t>(scratch) & 255u) return ST_BAD_ARGS;
+        int8_t* aq = static_cast<int8_t*>(scratch);
+        __half* da_t = reinterpret_cast<__half*>(aq + ((static_cast<size_t>(N) * K + 255) & ~static_cast<size_t>(255)));
+        p.da_t = da_t;
+        const long long nthreads = static_cast<long long>(p.m_tiles) * 128 * p.nblk * 8;
+        const long long qgrid = nthreads / 256;
+        if (qgrid > 0x7fffffffLL) return ST_UNSUPPORTED_PATH;
+        quantize_q8_planar_kernel<<<static_cast<unsigned>(qgrid), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk, nthreads);
+        if (cudaGetLastError() != cudaSuccess) return ST_QUANT;
+        if (!make_tmap_3d(&tmX, TmaType::U8, aq, K, N, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
+    } else
     if (!make_tmap_3d(&tmX, TmaType::F32, X, K, N, 1, static_cast<uint64_t>(K) * 4, 0, 32, 128, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
 

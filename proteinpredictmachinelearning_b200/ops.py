@@ -222,3 +222,17 @@ def outer_prod_mean_cuda(left, right, path=PATH_AUTO):
         rc = _lib.load().ppml_b200_outer_prod_mean(_p(left), _p(right), _p(dst), D, L, N, B, 1.0 / float(N), path, _stream())
     _check(rc, "outer_prod_mean")
     return dst
+
+
+def outer_prod_mean_slabs_cuda(left_slabs, right, path=PATH_AUTO, out=None):
+    """One rank's share of the outer-product-mean: left_slabs [D_left,L,N,B] (a contiguous d1 range), right
+    [D,L,N,B] (all of it) -> [D_left*D, L, L, B], the rank's contiguous part of the full result."""
+    left_slabs, right = _f32c(left_slabs), _f32c(right)
+    D1, L, N, B = left_slabs.shape
+    D = right.shape[0]
+    assert right.shape[1:] == left_slabs.shape[1:]
+    dst = torch.empty((D1 * D, L, L, B), device=right.device, dtype=torch.float32) if out is None else out
+    rc = _lib.load().ppml_b200_outer_prod_mean_slabs(_p(left_slabs), _p(right), _p(dst), D1, D, L, N, B, 1.0 / float(N),
+                                                     path, _stream())
+    _check(rc, "outer_prod_mean_slabs")
+    return dst

@@ -192,6 +192,33 @@ def test_mul_mat_q8(oracle, Mout, Ntok, K, path):
     assert cases.rel_err(host(got), ref) <= TOL_FP32
 
 
+@pytest.mark.parametrize("Mout,Ntok,K", Q8_SHAPES + [(384, 1000, 1024), (128, 19000, 512)])
+def test_mul_mat_q8_one_and_two_pass_forms(oracle, Mout, Ntok, K):
+    """Quantizing inside the product kernel or in a kernel of its own gives the same int32 block sums and the same
+    fp32 results, bit for bit; both match the checker."""
+    from proteinpredictmachinelearning_b200 import _lib
+    w, x = cases.q8_case(Mout, Ntok, K, seed=12)
+    x = _q8_special(x)
+    W = oracle.repack_q8_0(oracle.quantize_q8_0(w))
+    bias = (np.random.default_rng(3).standard_normal(Mout) * 0.1).astype(np.float32)
+    ref, ref_sumi = oracle.mul_mat_q8(W, x, Mout, wtype=2, c_trans=1, bias=bias, want_sumi=True)
+    out = {}
+    try:
+        for mode in (0, 1):
+            _lib.load().ppml_b200_set_q8_two_pass(mode)
+            got, taken, sumi = ops.mul_mat_q8_cuda(dev(W), dev(x), Mout, wtype=2, c_trans=1, bias=dev(bias), path=PATH_UMMA,
+                                                   want_sumi=True)
+            fast, _ = ops.mul_mat_q8_cuda(dev(W), dev(x), Mout, wtype=2, c_trans=1, bias=dev(bias), path=PATH_UMMA)
+            assert taken == 1
+            out[mode] = (host(got), host(sumi), host(fast))
+    finally:
+        _lib.load().ppml_b200_set_q8_two_pass(-1)
+    assert np.array_equal(out[0][1], ref_sumi) and np.array_equal(out[1][1], ref_sumi)
+    assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][2], out[1][2])
+    assert np.array_equal(out[0][0], out[0][2])
+    assert cases.rel_err(out[1][0], ref) <= TOL_FP32
+
+
 @pytest.mark.parametrize("wtype", [0, 1, 2])
 @pytest.mark.parametrize("c_trans", [0, 1])
 def test_mul_mat_q8_weight_layouts(oracle, wtype, c_trans):
@@ -446,6 +473,17 @@ def test_outer_prod_mean_16bit(oracle, dtype):
 
 
 @pytest.mark.parametrize("path,tol", [(PATH_SIMT, TOL_FP32), (PATH_AUTO, TOL_TF32)])
+def test_outer_prod_mean_slabs(oracle, path, tol):
+    """A d1 range of `left` against all of `right` is the matching contiguous part of the whole result."""
+    for (D, L, N, lo, hi) in [(8, 64, 128, 2, 5), (16, 32, 64, 14, 16), (4, 51, 8, 0, 1)]:
+        l, r = cases.opm_case(D, L, N, seed=21 + D)
+        ref = oracle.outer_prod_mean(l, r)
+        got = host(ops.outer_prod_mean_slabs_cuda(dev(l[lo:hi]), dev(r), path=path))
+        assert got.shape[0] == (hi - lo) * D
+        assert cases.rel_err(got, ref[lo * D:hi * D]) <= tol, (D, L, N, path)
+
+
+@pytest.mark.parametrize("path,tol", [(PATH_SIMT, TOL_FP32), (PATH_AUTO, TOL_TF32)])
 def test_outer_prod_mean(oracle, path, tol):
     l, r = cases.opm_case(4, 12, 9)
     assert cases.rel_err(host(ops.outer_prod_mean_cuda(dev(l), dev(r), path=path)), GOLD["opm"]) <= tol
@@ -477,3 +515,13 @@ def test_out_prod(oracle):
     for i0 in range(4):
         for i1 in range(5):
             assert abs(got[i1, i0] - sum(float(a[i0 + k * 4]) * float(b[i1 + k * 5]) for k in range(3))) <= 1e-4
+
+
+def test_iter_block_sequence_runs(capsys):
+    """The full-size op sequence of one main IterBlock runs on one GPU and reports a time per op class."""
+    import json
+    from proteinpredictmachinelearning_b200 import block_bench
+    block_bench.run(1, 1, 3)
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["value"] > 0 and line["n_gpus"] == 1
+    assert {"attention", "linear_q8", "linear_tf32", "tri_mul", "outer_prod_mean"} <= set(line["split_ms_rank0"])
