@@ -50,3 +50,21 @@ def all_gather_rows(x_local, world, group=None):
     parts = [torch.empty_like(x_local) for _ in range(world)]
     dist.all_gather(parts, x_local.contiguous(), group=group)
     return torch.cat(parts, dim=0)
+
+
+def transpose_exchange(x_local, world, group=None):
+    """The (n, l) transpose of an activation [N, L, C] that is sharded by contiguous n ranges, as the reference's
+    `permute({0,2,1,3})` copies after MSA column attention and pair row attention do on one device
+    (src/ops/Attention.cpp:489, :744): x_local [N/world, L, C] -> this rank's rows [L/world, N, C] of the transposed
+    tensor.  One all-to-all in which every rank keeps 1/world of its data, plus local re-layouts."""
+    import torch.distributed as dist
+    n_loc, L, C = x_local.shape
+    if world == 1:
+        return x_local.permute(1, 0, 2).contiguous()
+    if L % world:
+        raise ValueError("L must be a multiple of the number of ranks")
+    l_loc = L // world
+    send = x_local.reshape(n_loc, world, l_loc, C).permute(1, 0, 2, 3).contiguous()      # [to rank][n][l][c]
+    recv = send.new_empty(send.shape)                                                    # [from rank][n][l][c]
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.permute(2, 0, 1, 3).reshape(l_loc, world * n_loc, C).contiguous()

@@ -517,6 +517,52 @@ def test_out_prod(oracle):
             assert abs(got[i1, i0] - sum(float(a[i0 + k * 4]) * float(b[i1 + k * 5]) for k in range(3))) <= 1e-4
 
 
+def test_attention_full_size_properties():
+    """BASELINE's attention sizes (MSA depth 256, L = 256, 8 heads x 32, shared pair bias): the tensor-core kernel
+    agrees with the CUDA-core kernel, a permutation of the batch permutes the output, and exp(LSE) equals the
+    softmax denominator recomputed from one batch's scores."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    B, h, L = 256, 8, 256
+    Q, K, V = (torch.randn(B, h, L, 32, device="cuda", generator=g) / 32 ** 0.5 for _ in range(3))
+    bias = torch.randn(h, L, L, device="cuda", generator=g)
+    scale = 1 / 32 ** 0.5
+    o_t, l_t = ops.flash_attn_forward_cuda(Q, K, V, bias, scale=scale, bias_bcast=True, path=PATH_UMMA)
+    o_s, l_s = ops.flash_attn_forward_cuda(Q, K, V, bias, scale=scale, bias_bcast=True, path=PATH_SIMT)
+    assert float((o_t - o_s).abs().max() / o_s.abs().max()) <= TOL_TF32
+    assert float((l_t - l_s).abs().max()) <= 2e-3
+    perm = torch.randperm(B, device="cuda", generator=g)
+    o_p, _ = ops.flash_attn_forward_cuda(Q[perm].contiguous(), K[perm].contiguous(), V[perm].contiguous(), bias, scale=scale,
+                                         bias_bcast=True, path=PATH_UMMA)
+    assert torch.equal(o_p, o_t[perm])
+    s = torch.einsum("hid,hjd->hij", Q[7], K[7]) * scale + bias
+    assert float((torch.logsumexp(s, dim=-1) - l_t[7]).abs().max()) <= 2e-3
+    o16, _ = ops.flash_attn_forward_cuda(Q.bfloat16(), K.bfloat16(), V.bfloat16(), bias, scale=scale, bias_bcast=True, path=PATH_UMMA)
+    assert float((o16 - o_s).abs().max() / o_s.abs().max()) <= TOL_16
+
+
+def test_pair_track_full_size_properties():
+    """BASELINE's pair-track sizes: triangle multiplication over 128 channel slabs at L = 384 and the outer-product-mean
+    at c = 32 (8192 x 8192 x 256): tensor cores against CUDA cores, and the slab structure (a slab of the result depends on
+    that slab of the operands only)."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    D, L = 128, 384
+    left, right = torch.randn(D, L, L, 1, device="cuda", generator=g), torch.randn(D, L, L, 1, device="cuda", generator=g)
+    for outgoing in (True, False):
+        t = ops.tri_mul_cuda(left, right, float(L), outgoing, path=PATH_UMMA)
+        s_ = ops.tri_mul_cuda(left, right, float(L), outgoing, path=PATH_SIMT)
+        assert float((t - s_).abs().max() / s_.abs().max()) <= TOL_TF32
+        part = ops.tri_mul_cuda(left[40:72].contiguous(), right[40:72].contiguous(), float(L), outgoing, path=PATH_UMMA)
+        assert torch.equal(part, t[40:72])
+    c, Lr, N = 32, 256, 256
+    a, b = torch.randn(c, Lr, N, 1, device="cuda", generator=g), torch.randn(c, Lr, N, 1, device="cuda", generator=g)
+    full = ops.outer_prod_mean_cuda(a, b, path=PATH_UMMA)
+    assert float((full - ops.outer_prod_mean_cuda(a, b, path=PATH_SIMT)).abs().max() / full.abs().max()) <= TOL_TF32
+    assert torch.equal(ops.outer_prod_mean_slabs_cuda(a[8:12].contiguous(), b, path=PATH_UMMA), full[8 * c:12 * c])
+    d1, d2, i, j = 5, 17, 100, 31                     # one entry against its definition
+    ref = float((a[d1, i, :, 0].double() * b[d2, j, :, 0].double()).sum() / N)
+    assert abs(float(full[d1 * c + d2, i, j, 0]) - ref) <= 1e-3 * max(1.0, abs(ref))
+
+
 def test_iter_block_sequence_runs(capsys):
     """The full-size op sequence of one main IterBlock runs on one GPU and reports a time per op class."""
     import json

@@ -73,6 +73,14 @@ def _worker(rank, world, port, q):
     full = shard.all_gather_rows(torch.from_numpy(mine), world).numpy()
     ok["opm"] = np.array_equal(full, ref)
 
+    # the (n, l) transpose that closes MSA column attention and pair row attention: one all-to-all plus local re-layouts
+    Nn, Ll, Cc = 6, 8, 3
+    x = np.arange(Nn * Ll * Cc, dtype=np.float32).reshape(Nn, Ll, Cc)
+    lo, hi = shard.split(Nn, world, rank)
+    mine = shard.transpose_exchange(torch.from_numpy(x[lo:hi].copy()), world)
+    full = shard.all_gather_rows(mine, world).numpy()
+    ok["transpose"] = np.array_equal(full, x.transpose(1, 0, 2))
+
     if rank == 0:
         q.put(ok)
     dist.barrier()
