@@ -52,6 +52,19 @@ def test_bad_arguments_are_rejected_on_the_host(lib):
     assert lib.ppml_b200_out_prod(p, p, p, 4, 3, 1, 1, 5, 2, 1, 1, 4, 5, 1, 1, 0, None) == 1             # K mismatch
     assert lib.ppml_b200_quantize_rows_q8_1(p, p, 33, None) == 1
     assert lib.ppml_b200_q8_0r_bytes(64) == 68
+    # entries without a counterpart in the reference follow the same conventions
+    assert lib.ppml_b200_flash_attn_forward_16(None, 8, 0, p, p, p, None, p, None, 1, 0, None) == 1
+    assert lib.ppml_b200_outer_prod_mean_slabs(p, p, p, 0, 4, 4, 4, 1, 1.0, 0, None) == 1
+    assert lib.ppml_b200_outer_prod_mean_slabs(p, None, p, 2, 4, 4, 4, 1, 1.0, 0, None) == 1
+    assert lib.ppml_b200_tri_mul_16(p, p, None, 1, 1, 1, 1, 1, 1.0, 1, 1, 0, None) == 1
+    # the form of the tensor-core Q8 product: forced one-pass, forced two-pass, per shape (long K, few token tiles)
+    try:
+        lib.ppml_b200_set_q8_two_pass(0)
+        assert lib.ppml_b200_q8_kernel_launches(256, 408, 1024) == 1
+        lib.ppml_b200_set_q8_two_pass(1)
+        assert lib.ppml_b200_q8_kernel_launches(256, 65536, 128) == 2
+    finally:
+        lib.ppml_b200_set_q8_two_pass(-1)
 
 
 def test_host_weight_quantizer_bit_exact(oracle, lib):
