@@ -246,7 +246,30 @@ def run_ours(args):
         one_pass(events)
     t1.record()
     barrier()
-    ms = t0.elapsed_time(t1)
+    eager_ms = t0.elapsed_time(t1)
+    # The same K passes replayed from one captured CUDA graph: with 24 of the 36 launches lasting 10-20 us, launching
+    # them one by one from Python leaves the GPU waiting for the host between kernels.  The per-launch events above
+    # (roofline, per-shape times) come from the eager passes; `value` from the replay when capture is possible.
+    ms, launch_mode, graph = eager_ms, "eager, one call per launch", None
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                one_pass()
+        except Exception as exc:           # capture not possible: the eager figure stands
+            graph, launch_mode = None, f"eager (graph capture failed: {type(exc).__name__})"
+        # every rank takes the same barriers whether or not its capture worked
+        run = graph.replay if graph is not None else one_pass
+        for _ in range(2):
+            run()
+        barrier()
+        t0.record()
+        for _ in range(args.steps):
+            run()
+        t1.record()
+        barrier()
+        if graph is not None:
+            ms, launch_mode = t0.elapsed_time(t1), "one CUDA graph per pass (36 launches), replayed"
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         tt = torch.tensor([ms], device=dev)
@@ -364,7 +387,8 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "q8 (int8 x int8 -> int32, fp32 rescale)", "data": "synthetic",
         "config": {"workload": "configs[1] Q8 block-quantized mul_mat sweep, 36 shapes per step", "K": list(KS),
                    "N": list(NS), "M": list(MS), "seed": SEED, "sharding": f"token rows, {world} shard(s)",
-                   "l2": "working set per step (~0.9 GB) exceeds L2, no explicit flush"},
+                   "l2": "working set per step (~0.9 GB) exceeds L2, no explicit flush", "launch": launch_mode,
+                   "eager_ms_per_step": eager_ms / args.steps},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": Q8_SWEEP_DRAM_BYTES_PER_LAUNCH if not args.only else None,
                      "algorithmic_bytes_per_launch": step_bytes / max(len(sh), 1), "peak_kind": peak_kind,
@@ -438,6 +462,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="stop after the device-resident region (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="time the device-resident region with eager launches only")
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs)")
     ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn"],
                     help="profiling runs with --no-e2e: time the fp32 (tf32 tensor-core) or bf16 mul_mat on the same shapes")
