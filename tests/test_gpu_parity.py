@@ -518,7 +518,7 @@ def test_out_prod(oracle):
 
 
 def test_attention_full_size_properties():
-    """BASELINE's attention sizes (MSA depth 256, L = 256, 8 heads x 32, shared pair bias): the tensor-core kernel
+    """The full-size attention case (MSA depth 256, L = 256, 8 heads x 32, shared pair bias): the tensor-core kernel
     agrees with the CUDA-core kernel, a permutation of the batch permutes the output, and exp(LSE) equals the
     softmax denominator recomputed from one batch's scores."""
     g = torch.Generator(device="cuda").manual_seed(3)
@@ -541,7 +541,7 @@ def test_attention_full_size_properties():
 
 
 def test_pair_track_full_size_properties():
-    """BASELINE's pair-track sizes: triangle multiplication over 128 channel slabs at L = 384 and the outer-product-mean
+    """The full-size pair-track cases: triangle multiplication over 128 channel slabs at L = 384 and the outer-product-mean
     at c = 32 (8192 x 8192 x 256): tensor cores against CUDA cores, and the slab structure (a slab of the result depends on
     that slab of the operands only)."""
     g = torch.Generator(device="cuda").manual_seed(4)
