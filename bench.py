@@ -437,6 +437,9 @@ def attn_profile(args):
     g = torch.Generator(device=dev).manual_seed(3)
     Q, K, V = (torch.randn(B, h, L, 32, device=dev, generator=g) / 32 ** 0.5 for _ in range(3))
     bias = torch.randn(h, L, L, device=dev, generator=g)
+    half = args.kernel == "attn_bf16"                       # bf16 Q/K/V (kind::f16 products), fp32 bias / softmax / output
+    if half:
+        Q, K, V = Q.bfloat16(), K.bfloat16(), V.bfloat16()
     f = lambda: ops.flash_attn_forward_cuda(Q, K, V, bias, scale=1 / 32 ** 0.5, bias_bcast=True, path=PATH_UMMA)
     for _ in range(max(args.warmup, 3)):
         f()
@@ -449,8 +452,8 @@ def attn_profile(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) / args.steps * 1e3
     flops = 4.0 * B * h * L * L * 32
-    nbytes = 16.0 * B * h * L * 32 + 4.0 * h * L * L + 4.0 * B * h * L
-    print(json.dumps({"kernel": "umma_attn_kernel", "B": B, "h": h, "L": L, "us": us, "tflops": flops / us / 1e6,
+    nbytes = (10.0 if half else 16.0) * B * h * L * 32 + 4.0 * h * L * L + 4.0 * B * h * L
+    print(json.dumps({"kernel": "umma_attn_kernel<bf16>" if half else "umma_attn_kernel", "B": B, "h": h, "L": L, "us": us, "tflops": flops / us / 1e6,
                       "gbs": nbytes / us / 1e3}), flush=True)
 
 
@@ -464,7 +467,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="stop after the device-resident region (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="time the device-resident region with eager launches only")
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs)")
-    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn"],
+    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn", "attn_bf16"],
                     help="profiling runs with --no-e2e: time the fp32 (tf32 tensor-core) or bf16 mul_mat on the same shapes")
     ap.add_argument("--workload", default="sweep", choices=["sweep", "block"],
                     help="block: the hot-path op sequence of one main IterBlock at full size, sharded over --gpus ranks "
@@ -473,7 +476,7 @@ def main():
     if args.workload == "block":
         from proteinpredictmachinelearning_b200 import block_bench
         return block_bench.run(args.gpus, args.steps, args.warmup)
-    if args.kernel == "attn":
+    if args.kernel in ("attn", "attn_bf16"):
         return attn_profile(args)
     if args.impl == "reference":
         run_reference(args)
