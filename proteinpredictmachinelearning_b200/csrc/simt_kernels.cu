@@ -397,6 +397,11 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
 // accumulator are per-thread scalars: no shuffles and no cross-lane reductions.  Same arithmetic contract as the
 // kernel above; exp is 2^((s - m) log2 e) on the transcendental unit.
 // =============================================================================================
+// 2^x on the transcendental unit (about 2 ulp); results below the normal range flush to 0, 2^-inf = 0
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(128)
 attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
@@ -501,14 +506,14 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
         }
         const float m_new = fmaxf(m, mt);
         if (m_new == -CUDART_INF_F) continue;        // every key so far is masked for this row
-        const float alpha = (m == -CUDART_INF_F) ? 0.0f : exp2f((m - m_new) * kLog2e);
+        const float alpha = (m == -CUDART_INF_F) ? 0.0f : ex2_fast((m - m_new) * kLog2e);
         const float ml2 = m_new * kLog2e;
         float lt = 0.0f;
 #pragma unroll
         for (int dd = 0; dd < D; ++dd) acc[dd] *= alpha;
 #pragma unroll
         for (int t = 0; t < kTile; ++t) {
-            const float pj = exp2f(fmaf(x[t], kLog2e, -ml2));      // 2^-inf = 0 for masked keys
+            const float pj = ex2_fast(fmaf(x[t], kLog2e, -ml2));      // 2^-inf = 0 for masked keys
             lt += pj;
 #pragma unroll
             for (int dd = 0; dd < D; ++dd) acc[dd] = fmaf(pj, vs[t * D + dd], acc[dd]);
