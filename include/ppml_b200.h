@@ -63,6 +63,16 @@ int ppml_b200_mul_mat_f16(const void* A16, const void* B16, float* C, int M, int
 int ppml_b200_mul_mat_bf16(const void* A16, const void* B16, float* C, int M, int K, int N, const float* bias,
                            int path, void* stream);
 
+/* bf16 products behind fp32 tensors (no counterpart in the reference, whose type enum has no bf16,
+ * include/ppml/Tensor.h:35-64): A (activations) and B (weights) are fp32 in device memory; A is cast to bf16 into
+ * library-owned scratch on the stream, B into a cached bf16 copy keyed by (device, B, N, K) that is made on the first
+ * call and reused afterwards -- call ppml_b200_bf16_shadow_invalidate(B) (NULL: every cached copy) after the weights
+ * change.  Creating a cached copy or growing the scratch allocates, which is refused (status 3) during stream
+ * capture: make the first call with each weight before capturing.  Tolerance against the fp32 product: 1e-2. */
+int ppml_b200_mul_mat_f32_as_bf16(const float* A, const float* B, float* C, int M, int K, int N, const float* bias,
+                                  int path, void* stream);
+void ppml_b200_bf16_shadow_invalidate(const void* B);
+
 /* fp32 -> fp16 / bf16 (round to nearest even); no counterpart in the reference (it has no cast op). */
 int ppml_b200_cast_f32_to_f16(const float* x, void* y, int64_t n, void* stream);
 int ppml_b200_cast_f32_to_bf16(const float* x, void* y, int64_t n, void* stream);
@@ -92,7 +102,9 @@ int ppml_b200_q8_kernel_launches(int M, int N, int K);
  * a fixed 4 MiB array inside the library image (held by every GPU that loads the library), so
  * N * (K / 32) * 36 bytes must fit: otherwise status 9 and a message on stderr.  All calls share that
  * array: issue them on one stream, overlapping calls race.  The first call on a device looks up the
- * array's address and should be made before any stream capture on that device. */
+ * array's address and should be made before any stream capture on that device; the CUDA runtime may
+ * load the library's device code and back the array during that first call (free memory can drop once,
+ * then never again), so make it before the memory is capped or given away. */
 #define PPML_B200_NOALLOC_SCRATCH_BYTES (4u << 20)
 int ppml_b200_mul_mat_q8_noalloc(const void* W, const float* X, float* C, int M, int N, int K, int wtype,
                                  int c_trans, const float* bias, void* stream);
@@ -121,7 +133,12 @@ typedef struct ppml_b200_flash_cfg {
     int causal;
     float scale;
     float softmax_eps;
-    int Br, Bc;               /* accepted for compatibility; the kernels pick their own tiles */
+    int Br, Bc;               /* the kernels pick their own tiles.  Bc (0 = 64, as in the reference) still decides one
+                                 thing: a query row whose first Bc scores are all -inf comes out as O = 0, LSE = -inf
+                                 even when later keys are visible, because the reference's CPU kernel turns such a row
+                                 into NaN and then into zeros (src/ops/FlashAttn.cpp:94-121).  Bc < 0 switches this
+                                 off: the ordinary softmax over the visible keys (no counterpart in the reference).
+                                 The tensor-core kernel takes Bc that are multiples of 64. */
 } ppml_b200_flash_cfg;
 
 int ppml_b200_flash_attn_forward(const ppml_b200_flash_cfg* cfg, const float* Q, const float* K, const float* V,
@@ -182,7 +199,9 @@ int ppml_b200_outer_prod_mean_slabs(const float* left, const float* right, float
  * Replace mulmat_stats_cuda_begin / mulmat_stats_cuda_end (src/backend/CUDAKernels.cpp:190-191;
  * src/cuda/CUDAKernels.cu:1693-1732): event pair around one launch, totals per (path, M, K, N).
  * Active only when the environment has PPML_MULMAT_STATS=1.  ppml_b200_mulmat_stats_dump writes
- * the table (one line per shape) into buf and returns the number of bytes written. */
+ * the table (one line per shape) into buf, clears it and returns the number of bytes written; what is
+ * left at process exit is printed to stderr, as the reference prints its table
+ * (include/ppml/MulMatStats.h:137-145).  At most 4096 event pairs are kept open at a time. */
 void ppml_b200_mulmat_stats_begin(int M, int K, int N);
 void ppml_b200_mulmat_stats_end(const char* path);
 int ppml_b200_mulmat_stats_dump(char* buf, int cap);

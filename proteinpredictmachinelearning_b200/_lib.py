@@ -26,6 +26,8 @@ SIGNATURES = {
     "ppml_b200_mul_mat_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp]),
     "ppml_b200_mul_mat_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "ppml_b200_mul_mat_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "ppml_b200_mul_mat_f32_as_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "ppml_b200_bf16_shadow_invalidate": (None, [_vp]),
     "ppml_b200_cast_f32_to_f16": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_cast_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_mul_mat_q8": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, C.POINTER(_i), _vp]),

@@ -1,7 +1,7 @@
 """Hot-path op sequence of one main IterBlock of the reference model at full size, on 1..8 GPUs of one box.
 
 The block's dense contractions and attention calls (src/model/PPML.cpp:2164-2273 for the layer shapes,
-src/model/PPML.cpp:908-994 for the op order, src/ops/Attention.cpp:223-284, :361-392, :468-489, :717-744 for the
+src/model/PPML.cpp:908-994 for the op order, src/modules/Attention.cpp:223-284, :361-392, :468-489, :717-744 for the
 attention call sites) at L = 256 residues, MSA depth N = 256, d_msa = 256, d_pair = 128, 8 heads x 32:
 
   MSA row attention   5 Linears 256->256 on N*L tokens, pair bias Linear 128->8 on L*L tokens, attention
@@ -24,7 +24,7 @@ flat chunks (token rows; attention batches; tri_mul channel slabs; outer-product
 block, all through NCCL into local memory before any kernel reads them: all-gather of each pair bias ([L*L, 8],
 2 MiB, three times), all-gather of the outer-product-mean's `right` operand (4 MiB), and two all-to-alls of 64 MiB in
 total that stand for the (n, l) transposes closing MSA column attention and pair row attention
-(src/ops/Attention.cpp:489, :744).  With G = 1 there is no exchange.  Total work is fixed as G grows ("strong").
+(src/modules/Attention.cpp:489, :744).  With G = 1 there is no exchange.  Total work is fixed as G grows ("strong").
 The exchanges run in stream order between the kernels.  Running them asynchronously behind independent products
 (bias gathered during the projections, the Linear before a transpose cut into row chunks whose all-to-alls follow
 the next chunk's product) was measured slower on two GPUs (2.43 against 1.78 ms per block): the collectives' CTAs

@@ -23,21 +23,45 @@ inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
 inline bool path_ok(int path) { return path >= PPML_B200_PATH_AUTO && path <= PPML_B200_PATH_UMMA; }
 
-// Grow-only device scratch for the dp4a Q8 path (Q8_1 activation blocks), one per device, guarded
-// by a mutex as the reference's launcher does (src/cuda/MulMatQ8Kernel.cu:430-449).
+// Library-owned device scratch, one set per device, guarded by a mutex as the reference's launcher guards its own
+// (src/cuda/MulMatQ8Kernel.cu:430-449).  Three independent buffers, so that a launch recorded in a CUDA graph never
+// sees its buffer move:
+//   kScratchDp4a   Q8_1 activation blocks of the dp4a path                      (grows)
+//   kScratchTwoPass int8 activations + scale tables of the two-pass tensor-core form: that form is only chosen for
+//                  at most num_sms token tiles and K <= 1024, so the buffer is allocated once at its maximum size
+//                  (about 20 MB) and its address never changes
+//   kScratchCast   bf16 copy of fp32 activations (ppml_b200_mul_mat_f32_as_bf16) (grows)
+// A buffer that has to grow is replaced, never freed: the old one stays allocated until the process exits, because a
+// captured graph may still hold its address (sizes at least double, so the retired ones add up to less than the live
+// one).  Growing is refused (null) while the stream is being captured: allocation is not a stream operation.
+enum { kScratchDp4a = 0, kScratchTwoPass = 1, kScratchCast = 2, kScratchKinds = 3 };
 struct Scratch { void* ptr = nullptr; size_t bytes = 0; };
-Scratch g_scratch[64];
+Scratch g_scratch[64][kScratchKinds];
+std::vector<void*>* g_retired = nullptr;     // leaked on purpose
 std::mutex g_scratch_mtx;
 
-void* ensure_scratch(size_t bytes) {
+bool stream_is_capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) { cudaGetLastError(); return false; }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+// Caller holds g_scratch_mtx.
+void* ensure_scratch(int kind, size_t bytes, cudaStream_t st) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    Scratch& s = g_scratch[dev];
+    Scratch& s = g_scratch[dev][kind];
     if (bytes <= s.bytes) return s.ptr;
-    if (s.ptr) { cudaFree(s.ptr); s.ptr = nullptr; s.bytes = 0; }
+    if (stream_is_capturing(st)) return nullptr;
+    size_t want = bytes;
+    if (kind != kScratchTwoPass && want < 2 * s.bytes) want = 2 * s.bytes;
     void* p = nullptr;
-    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    s.ptr = p; s.bytes = bytes;
+    if (cudaMalloc(&p, want) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (s.ptr) {
+        if (!g_retired) g_retired = new std::vector<void*>();
+        g_retired->push_back(s.ptr);
+    }
+    s.ptr = p; s.bytes = want;
     return p;
 }
 
@@ -124,6 +148,46 @@ int ppml_b200_mul_mat_bf16(const void* A16, const void* B16, float* C, int M, in
     return mul_mat_any(A16, B16, C, M, K, N, bias, path, 2, 0, as_stream(stream));
 }
 
+// fp32 tensors, bf16 products: the activations are cast into library scratch on the stream, the weights into a
+// cached bf16 copy keyed by (device, pointer, N, K) that is made on first use and lives until it is invalidated.
+namespace {
+std::map<std::tuple<int, const void*, int, int>, void*>* g_shadow = nullptr;     // leaked on purpose
+}
+int ppml_b200_mul_mat_f32_as_bf16(const float* A, const float* B, float* C, int M, int K, int N, const float* bias,
+                                  int path, void* stream) {
+    if (!A || !B || !C || M <= 0 || K <= 0 || N <= 0 || !path_ok(path)) return ST_BAD_ARGS;
+    cudaStream_t st = as_stream(stream);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return ST_LAUNCH; }
+    std::lock_guard<std::mutex> lock(g_scratch_mtx);
+    if (!g_shadow) g_shadow = new std::map<std::tuple<int, const void*, int, int>, void*>();
+    const auto key = std::make_tuple(dev, static_cast<const void*>(B), N, K);
+    void* b16 = nullptr;
+    auto it = g_shadow->find(key);
+    if (it != g_shadow->end()) {
+        b16 = it->second;
+    } else {
+        if (stream_is_capturing(st)) return ST_SCRATCH;
+        if (cudaMalloc(&b16, static_cast<size_t>(N) * K * 2) != cudaSuccess) { cudaGetLastError(); return ST_SCRATCH; }
+        if (launch_cast(B, b16, static_cast<long long>(N) * K, 1, st) != ST_OK) { cudaFree(b16); return ST_LAUNCH; }
+        (*g_shadow)[key] = b16;
+    }
+    void* a16 = ensure_scratch(kScratchCast, static_cast<size_t>(M) * K * 2, st);
+    if (!a16) return ST_SCRATCH;
+    const int rc = launch_cast(A, a16, static_cast<long long>(M) * K, 1, st);
+    if (rc != ST_OK) return rc;
+    return mul_mat_any(a16, b16, C, M, K, N, bias, path, 2, 0, st);
+}
+void ppml_b200_bf16_shadow_invalidate(const void* B) {
+    std::lock_guard<std::mutex> lock(g_scratch_mtx);
+    if (!g_shadow) return;
+    cudaDeviceSynchronize();
+    for (auto it = g_shadow->begin(); it != g_shadow->end();) {
+        if (B == nullptr || std::get<1>(it->first) == B) { cudaFree(it->second); it = g_shadow->erase(it); }
+        else ++it;
+    }
+}
+
 int ppml_b200_cast_f32_to_f16(const float* x, void* y, int64_t n, void* stream) {
     return launch_cast(x, y, n, 0, as_stream(stream));
 }
@@ -149,7 +213,12 @@ int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, 
             std::unique_lock<std::mutex> lock(g_scratch_mtx, std::defer_lock);
             if (q8_two_pass(M, N, K)) {
                 lock.lock();
-                scratch = ensure_scratch(umma_q8_scratch_bytes(N, K));
+                // the largest problem this form is chosen for (forced mode aside): one token tile per SM, K = 1024
+                size_t need = umma_q8_scratch_bytes(N, K);
+                const size_t fixed = umma_q8_scratch_bytes(num_sms() * 128, 1024);
+                if (need < fixed) need = fixed;
+                scratch = ensure_scratch(kScratchTwoPass, need, st);
+                if (!scratch) return ST_SCRATCH;
             }
             rc = launch_umma_q8(W, X, C, M, N, K, c_trans, bias, sumi_out, st, scratch);
         }
@@ -158,7 +227,7 @@ int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, 
     }
     const int nblk = K / 32;
     std::lock_guard<std::mutex> lock(g_scratch_mtx);
-    void* qa = ensure_scratch(static_cast<size_t>(nblk) * static_cast<size_t>(N) * 36);
+    void* qa = ensure_scratch(kScratchDp4a, static_cast<size_t>(nblk) * static_cast<size_t>(N) * 36, st);
     if (!qa) return ST_SCRATCH;
     if (launch_quantize_q8_1(X, qa, static_cast<long long>(K) * N, st) != ST_OK) return ST_QUANT;
     return launch_q8_dp4a(W, qa, C, M, N, nblk, wtype, c_trans, bias, sumi_out, st);
@@ -185,13 +254,17 @@ int flash_attn_any(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_st
     if (!cfg || !Q || !K || !V || !O || !path_ok(path)) return ST_BAD_ARGS;
     if (cfg->B <= 0 || cfg->h <= 0 || cfg->L <= 0 || cfg->d <= 0 || Lk <= 0) return ST_BAD_ARGS;
     const float scale = (cfg->scale > 0.f) ? cfg->scale : 1.0f / std::sqrt(static_cast<float>(cfg->d));
+    // Bc is the key tile of the reference's CPU kernel (<= 0 there means 64, src/ops/FlashAttn.cpp:58); it only matters
+    // for rows whose first Bc scores are all -inf, which that kernel turns into O = 0, LSE = -inf.  Bc < 0 here switches
+    // that rule off (ordinary softmax over the visible keys).
+    const int ft = cfg->Bc < 0 ? 0 : (cfg->Bc == 0 ? 64 : cfg->Bc);
     if (path != PPML_B200_PATH_SIMT) {
         const int rc = launch_umma_attn(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0,
-                                        scale, cfg->softmax_eps, bias_batch_stride, as_stream(stream));
+                                        scale, cfg->softmax_eps, bias_batch_stride, ft, as_stream(stream));
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
     }
     return launch_attn_rowwarp(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
-                               cfg->softmax_eps, bias_batch_stride, as_stream(stream));
+                               cfg->softmax_eps, bias_batch_stride, ft, as_stream(stream));
 }
 }  // namespace
 
@@ -334,55 +407,83 @@ int ppml_b200_outer_prod_mean_slabs(const float* left, const float* right, float
 // ---------------------------------------------------------------------------------------------
 namespace {
 struct StatRec { int M, K, N; cudaEvent_t e0, e1; std::string path; bool closed; };
-std::vector<StatRec> g_stat_open;
+struct StatAgg { long long calls = 0; double ms = 0.0; };
+std::vector<StatRec>* g_stat_open = nullptr;                                       // leaked on purpose: used at exit
+std::map<std::tuple<std::string, int, int, int>, StatAgg>* g_stat_agg = nullptr;
 std::mutex g_stat_mtx;
+constexpr size_t kStatOpenCap = 4096;      // event pairs kept before they are folded into the table
 bool stats_enabled() {
     static const bool on = [] { const char* e = std::getenv("PPML_MULMAT_STATS"); return e && e[0] == '1'; }();
     return on;
+}
+// Folds every closed record into the table (waits for its end event) and destroys its events.  Caller holds the mutex.
+void stats_fold() {
+    if (!g_stat_open) return;
+    if (!g_stat_agg) g_stat_agg = new std::map<std::tuple<std::string, int, int, int>, StatAgg>();
+    std::vector<StatRec> keep;
+    for (auto& r : *g_stat_open) {
+        if (!r.closed) { keep.push_back(r); continue; }
+        float ms = 0.f;
+        if (cudaEventSynchronize(r.e1) != cudaSuccess || cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) {
+            cudaGetLastError(); ms = 0.f;
+        }
+        StatAgg& a = (*g_stat_agg)[std::make_tuple(r.path, r.M, r.K, r.N)];
+        a.calls += 1; a.ms += ms;
+        cudaEventDestroy(r.e0); cudaEventDestroy(r.e1);
+    }
+    g_stat_open->swap(keep);
+}
+int stats_format(char* buf, int cap) {
+    int off = 0;
+    if (!g_stat_agg) return 0;
+    for (auto& kv : *g_stat_agg) {
+        const int n = std::snprintf(buf + off, static_cast<size_t>(cap - off), "%s M=%d K=%d N=%d calls=%lld ms=%.4f\n",
+                                    std::get<0>(kv.first).c_str(), std::get<1>(kv.first), std::get<2>(kv.first),
+                                    std::get<3>(kv.first), kv.second.calls, kv.second.ms);
+        if (n < 0 || n >= cap - off) break;
+        off += n;
+    }
+    return off;
+}
+// At process exit the table goes to stderr, the way the reference prints its own at exit
+// (include/ppml/MulMatStats.h:137-145).  The reference's table lives in its own binary and cannot be fed from here.
+void stats_at_exit() {
+    std::lock_guard<std::mutex> lock(g_stat_mtx);
+    stats_fold();
+    static char buf[1 << 16];
+    if (stats_format(buf, sizeof(buf)) > 0) std::fprintf(stderr, "[ppml_b200 MULMAT-STATS] per shape (CUDA events)\n%s", buf);
 }
 }  // namespace
 
 void ppml_b200_mulmat_stats_begin(int M, int K, int N) {
     if (!stats_enabled()) return;
     std::lock_guard<std::mutex> lock(g_stat_mtx);
+    if (!g_stat_open) { g_stat_open = new std::vector<StatRec>(); std::atexit(stats_at_exit); }
+    if (g_stat_open->size() >= kStatOpenCap) stats_fold();
     StatRec r{M, K, N, nullptr, nullptr, "", false};
     if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) { cudaGetLastError(); return; }
     cudaEventRecord(r.e0, 0);
-    g_stat_open.push_back(r);
+    g_stat_open->push_back(r);
 }
 
 void ppml_b200_mulmat_stats_end(const char* path) {
     if (!stats_enabled()) return;
     std::lock_guard<std::mutex> lock(g_stat_mtx);
-    for (auto it = g_stat_open.rbegin(); it != g_stat_open.rend(); ++it) {
+    if (!g_stat_open) return;
+    for (auto it = g_stat_open->rbegin(); it != g_stat_open->rend(); ++it) {
         if (!it->closed) { cudaEventRecord(it->e1, 0); it->path = path ? path : "?"; it->closed = true; break; }
     }
 }
 
+// Writes the table accumulated so far into buf and clears it.
 int ppml_b200_mulmat_stats_dump(char* buf, int cap) {
     if (!buf || cap <= 0) return 0;
     buf[0] = 0;
     if (!stats_enabled()) return 0;
     std::lock_guard<std::mutex> lock(g_stat_mtx);
-    cudaDeviceSynchronize();
-    std::map<std::tuple<std::string, int, int, int>, std::pair<long long, double>> agg;
-    for (auto& r : g_stat_open) {
-        if (!r.closed) continue;
-        float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) { cudaGetLastError(); ms = 0.f; }
-        auto& a = agg[std::make_tuple(r.path, r.M, r.K, r.N)];
-        a.first += 1; a.second += ms;
-        cudaEventDestroy(r.e0); cudaEventDestroy(r.e1);
-    }
-    g_stat_open.clear();
-    int off = 0;
-    for (auto& kv : agg) {
-        const int n = std::snprintf(buf + off, static_cast<size_t>(cap - off), "%s M=%d K=%d N=%d calls=%lld ms=%.4f\n",
-                                    std::get<0>(kv.first).c_str(), std::get<1>(kv.first), std::get<2>(kv.first),
-                                    std::get<3>(kv.first), kv.second.first, kv.second.second);
-        if (n < 0 || n >= cap - off) break;
-        off += n;
-    }
+    stats_fold();
+    const int off = stats_format(buf, cap);
+    if (g_stat_agg) g_stat_agg->clear();
     return off;
 }
 

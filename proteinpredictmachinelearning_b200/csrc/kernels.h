@@ -34,9 +34,11 @@ int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaSt
 int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
                    const float* bias, int* sumi_out, cudaStream_t st);
 // elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16; bias, O and LSE are fp32
+// ft: keys of the reference's first softmax tile (its Bc); a row whose first ft scores are all -inf gives O = 0, LSE = -inf
+// as the reference's CPU kernel does; 0 switches that off
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                        long long bias_batch_stride, cudaStream_t st);
+                        long long bias_batch_stride, int ft, cudaStream_t st);
 
 // tcgen05 paths (umma_gemm.cu / umma_q8.cu / umma_attn.cu).  Each returns ST_UNSUPPORTED_PATH when the
 // shape or the alignment rules it out, so that the caller can take the CUDA-core kernel.
@@ -60,7 +62,7 @@ size_t umma_q8_scratch_bytes(int N, int K);
 
 int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                     long long bias_batch_stride, cudaStream_t st);
+                     long long bias_batch_stride, int ft, cudaStream_t st);
 
 int num_sms();
 

@@ -16,9 +16,14 @@
 //
 // The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with
 // that device current).  That lookup is not a stream operation; make the first call on a device
-// before starting any stream capture on it.
+// before starting any stream capture on it.  It is also the moment at which the CUDA runtime may load
+// this library's device code onto that device and back the array with memory (module loading is lazy
+// by default), so the free-memory figure can drop once, by about the size of the array and the code,
+// during that first call and never afterwards: make it before the memory is capped or handed to
+// another allocator.  Later calls change nothing on the device but the caller's C.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/ppml_b200.h"
@@ -32,13 +37,14 @@ constexpr size_t kNoAllocScratchBytes = PPML_B200_NOALLOC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {nullptr};
+std::atomic<void*> g_scratch_addr[kMaxDevices];      // zero-initialised; two threads may both look up, same answer
 
 // Device address of the scratch array on the current device (looked up once per device).
 void* scratch_for_current_device() {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return nullptr; }
-    if (g_scratch_addr[dev] == nullptr) {
+    void* known = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (known == nullptr) {
         void* ptr = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
         if (e != cudaSuccess || ptr == nullptr) {
@@ -47,9 +53,10 @@ void* scratch_for_current_device() {
             cudaGetLastError();
             return nullptr;
         }
-        g_scratch_addr[dev] = ptr;
+        g_scratch_addr[dev].store(ptr, std::memory_order_release);
+        known = ptr;
     }
-    return g_scratch_addr[dev];
+    return known;
 }
 
 }  // namespace

@@ -316,6 +316,10 @@ int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int 
 // General attention forward (any L, Lk, head dim <= 128): one warp per query row, lanes over keys.
 // O = softmax(scale * Q K^T + bias) V with denominator (l + eps); LSE = m + log(l + eps);
 // a row with no unmasked key gives O = 0, LSE = -inf.
+// `ft` > 0 reproduces a property of the reference's CPU kernel (src/ops/FlashAttn.cpp:82-121), which walks the keys in
+// tiles of Bc: when every score of the first tile (the first min(ft, visible keys) keys) is -inf, exp(-inf - -inf) turns
+// its running sum into NaN, the final test `l > 0` fails and the row comes out as O = 0, LSE = -inf even if later keys are
+// finite.  All attention kernels here take the same parameter; 0 gives the ordinary softmax over the visible keys.
 // =============================================================================================
 __device__ __forceinline__ float attn_ld(const float* p) { return *p; }
 __device__ __forceinline__ float attn_ld(const __half* p) { return __half2float(*p); }
@@ -325,7 +329,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                     const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
-                    int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride) {
+                    int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft) {
     extern __shared__ float qs[];                    // [4][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int i = blockIdx.x * 4 + warp;
@@ -342,6 +346,7 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
                                  (static_cast<size_t>(hh) * L + i) * static_cast<size_t>(Lk) : nullptr;
     const int jmax = causal ? ((i + 1 < Lk) ? i + 1 : Lk) : Lk;
     float m = -CUDART_INF_F, l = 0.0f;
+    float mfirst = -CUDART_INF_F;                    // maximum over the first `ft` keys (see launch_attn_rowwarp)
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int j0 = 0; j0 < jmax; j0 += 32) {
         const int j = j0 + lane;
@@ -353,6 +358,7 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
             s = dot * scale;
             if (Bb) s += Bb[j];
         }
+        if (j < ft) mfirst = fmaxf(mfirst, s);
         float mt = s;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off));
@@ -376,6 +382,11 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
                 if (dd < d) acc[t] = fmaf(p, attn_ld(v + dd), acc[t]);
             }
         }
+    }
+    if (ft > 0) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mfirst = fmaxf(mfirst, __shfl_xor_sync(0xffffffffu, mfirst, off));
+        if (mfirst == -CUDART_INF_F) l = 0.0f;       // the reference's first key tile is fully masked: O = 0, LSE = -inf
     }
     float* o = O + bh * static_cast<size_t>(L) * d + static_cast<size_t>(i) * d;
     if (l > 0.0f) {
@@ -406,7 +417,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(128)
 attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                       const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
-                      int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride) {
+                      int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft) {
     constexpr int kTile = 32;
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr int kPer = (kTile * D + 127) / 128;               // K (and V) elements each thread moves per tile
@@ -437,6 +448,7 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
     const int last_row = min(blockIdx.x * 128 + 127, L - 1);
     const int jend = causal ? min(last_row + 1, Lk) : Lk;
     float m = -CUDART_INF_F, l = 0.0f;
+    float mfirst = -CUDART_INF_F;                    // maximum over the first `ft` keys
     float acc[D];
 #pragma unroll
     for (int dd = 0; dd < D; ++dd) acc[dd] = 0.0f;
@@ -504,6 +516,13 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
             if (j0 + t >= jmax) x[t] = -CUDART_INF_F;
             mt = fmaxf(mt, x[t]);
         }
+        if (j0 < ft) {
+            if (j0 + kTile <= ft) mfirst = fmaxf(mfirst, mt);
+            else {
+#pragma unroll
+                for (int t = 0; t < kTile; ++t) if (j0 + t < ft) mfirst = fmaxf(mfirst, x[t]);
+            }
+        }
         const float m_new = fmaxf(m, mt);
         if (m_new == -CUDART_INF_F) continue;        // every key so far is masked for this row
         const float alpha = (m == -CUDART_INF_F) ? 0.0f : ex2_fast((m - m_new) * kLog2e);
@@ -522,6 +541,7 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
         m = m_new;
     }
     if (!row_ok) return;
+    if (ft > 0 && mfirst == -CUDART_INF_F) l = 0.0f; // the reference's first key tile is fully masked: O = 0, LSE = -inf
     float* o = O + (bh * L + i) * D;
     float inv = 0.0f, lse = -CUDART_INF_F;
     if (l > 0.0f) { inv = 1.0f / (l + eps); lse = m + logf(l + eps); }
@@ -537,7 +557,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(128)
 attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                      const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
-                     int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, long long rows_total) {
+                     int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, long long rows_total,
+                     int ft) {
     constexpr float kLog2e = 1.4426950408889634f;
     const int lane = threadIdx.x & 31;
     const long long row = blockIdx.x * 4LL + (threadIdx.x >> 5);          // flattened (batch, head, query)
@@ -554,6 +575,7 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
     const float* Bb = bias ? bias + b * bias_batch_stride + (static_cast<long long>(hh) * L + i) * Lk : nullptr;
     const int jmax = causal ? min(i + 1, Lk) : Lk;
     float m = -CUDART_INF_F, l = 0.0f;
+    float mfirst = -CUDART_INF_F;                    // maximum over the first `ft` keys
     float acc[D];
 #pragma unroll
     for (int dd = 0; dd < D; ++dd) acc[dd] = 0.0f;
@@ -563,6 +585,7 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
 #pragma unroll
         for (int dd = 0; dd < D; ++dd) s = fmaf(q[dd], attn_ld(Kb + static_cast<long long>(j) * D + dd), s);
         if (Bb) s += Bb[j];
+        if (j < ft) mfirst = fmaxf(mfirst, s);
         const float m_new = fmaxf(m, s);
         if (m_new == -CUDART_INF_F) continue;                             // masked key, nothing visible before it
         const float alpha = exp2f((m - m_new) * kLog2e);                  // m = -inf gives 0
@@ -579,6 +602,11 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
     l *= f;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    if (ft > 0) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mfirst = fmaxf(mfirst, __shfl_xor_sync(0xffffffffu, mfirst, off));
+        if (mfirst == -CUDART_INF_F) l = 0.0f;       // the reference's first key tile is fully masked: O = 0, LSE = -inf
+    }
     float inv = 0.0f, lse = -CUDART_INF_F;
     if (l > 0.0f) { inv = 1.0f / (l + eps); lse = mw + logf(l + eps); }
 #pragma unroll
@@ -593,68 +621,68 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
 
 template <typename T>
 bool launch_attn_keylanes(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
-                          int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, cudaStream_t st) {
+                          int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, cudaStream_t st) {
     const long long rows = static_cast<long long>(B) * H * L;
     const long long blocks = (rows + 3) / 4;
     if (blocks > 0x7fffffffLL) return false;
     const unsigned grid = static_cast<unsigned>(blocks);
-    if (d == 4) attn_keylanes_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows);
-    else if (d == 8) attn_keylanes_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows);
-    else if (d == 16) attn_keylanes_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows);
+    if (d == 4) attn_keylanes_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft);
+    else if (d == 8) attn_keylanes_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft);
+    else if (d == 16) attn_keylanes_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft);
     else return false;
     return true;
 }
 
 template <typename T>
 bool launch_attn_rowthread(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
-                           int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, cudaStream_t st) {
+                           int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, cudaStream_t st) {
     dim3 grid((L + 127) / 128, H, B);
-    if (d == 4) attn_rowthread_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride);
-    else if (d == 8) attn_rowthread_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride);
-    else if (d == 16) attn_rowthread_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride);
+    if (d == 4) attn_rowthread_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft);
+    else if (d == 8) attn_rowthread_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft);
+    else if (d == 16) attn_rowthread_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft);
     else return false;
     return true;
 }
 
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                        long long bias_batch_stride, cudaStream_t st) {
+                        long long bias_batch_stride, int ft, cudaStream_t st) {
     if (d > 128 || H > 65535 || B > 65535 || elem < 0 || elem > 2) return ST_BAD_ARGS;
     // small head dims with enough query rows to fill CTAs of one thread per row
     if ((d == 4 || d == 8 || d == 16) && L < 32) {
         bool done;
         if (elem == 0) done = launch_attn_keylanes(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
-                                                   bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+                                                   bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
         else if (elem == 1) done = launch_attn_keylanes(static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
                                                         static_cast<const __nv_bfloat16*>(V), bias, O, LSE, B, H, L, Lk, d, causal, scale, eps,
-                                                        bias_batch_stride, st);
+                                                        bias_batch_stride, ft, st);
         else done = launch_attn_keylanes(static_cast<const __half*>(Q), static_cast<const __half*>(K), static_cast<const __half*>(V),
-                                         bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+                                         bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
         if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
     }
     if ((d == 4 || d == 8 || d == 16) && L >= 32) {
         bool done;
         if (elem == 0) done = launch_attn_rowthread(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
-                                                    bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+                                                    bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
         else if (elem == 1) done = launch_attn_rowthread(static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
                                                          static_cast<const __nv_bfloat16*>(V), bias, O, LSE, B, H, L, Lk, d, causal, scale, eps,
-                                                         bias_batch_stride, st);
+                                                         bias_batch_stride, ft, st);
         else done = launch_attn_rowthread(static_cast<const __half*>(Q), static_cast<const __half*>(K), static_cast<const __half*>(V),
-                                          bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, st);
+                                          bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
         if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
     }
     dim3 grid((L + 3) / 4, H, B);
     const size_t smem = 4 * d * sizeof(float);
     if (elem == 0)
         attn_rowwarp_kernel<float><<<grid, 128, smem, st>>>(static_cast<const float*>(Q), static_cast<const float*>(K),
-            static_cast<const float*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride);
+            static_cast<const float*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft);
     else if (elem == 1)
         attn_rowwarp_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(Q),
             static_cast<const __nv_bfloat16*>(K), static_cast<const __nv_bfloat16*>(V), bias, O, LSE, H, L, Lk, d, causal,
-            scale, eps, bias_batch_stride);
+            scale, eps, bias_batch_stride, ft);
     else
         attn_rowwarp_kernel<__half><<<grid, 128, smem, st>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
-            static_cast<const __half*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride);
+            static_cast<const __half*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 

@@ -88,6 +88,8 @@ struct AttnParams {
     int q_tiles, k_tiles;
     int total_items;             // B * H * q_tiles
     int o_align32;               // O is 32-byte aligned: rows can be written with 256-bit stores
+    int ft_tiles;                // > 0: a row whose first ft_tiles key tiles hold only -inf scores gives O = 0, LSE = -inf,
+                                 //      as the reference's CPU kernel does for its first key tile (src/ops/FlashAttn.cpp:94-121)
     int* err;
 };
 
@@ -288,8 +290,9 @@ int launch_attn_elem(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUten
 // elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16 (bias, O and LSE are fp32 in every case)
 int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                     long long bias_batch_stride, cudaStream_t st) {
+                     long long bias_batch_stride, int ft, cudaStream_t st) {
     if (d != kD) return ST_UNSUPPORTED_PATH;
+    if (ft < 0 || ft % kBN) return ST_UNSUPPORTED_PATH;       // the first-tile rule is checked per key tile of this kernel
     if (elem < 0 || elem > 2) return ST_BAD_ARGS;
     if ((reinterpret_cast<uintptr_t>(Q) & 15u) || (reinterpret_cast<uintptr_t>(K) & 15u) ||
         (reinterpret_cast<uintptr_t>(V) & 15u) || (reinterpret_cast<uintptr_t>(O) & 15u)) return ST_UNSUPPORTED_PATH;
@@ -305,6 +308,7 @@ int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, cons
     if (items <= 0 || items > 0x7fffffffLL || Lk <= 0) return ST_BAD_ARGS;
     p.total_items = static_cast<int>(items);
     p.o_align32 = (reinterpret_cast<uintptr_t>(O) & 31u) == 0 ? 1 : 0;
+    p.ft_tiles = ft / kBN;
     const long long resident = static_cast<long long>(kCtasPerSm) * num_sms();     // persistent CTAs
     const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
     CUtensorMap tmQ, tmK, tmV, tmB;

@@ -23,24 +23,6 @@ namespace ppml_b200 {
 
 namespace {
 
-#ifndef PPML_Q8_ABL
-#define PPML_Q8_ABL 0      // timing experiments only: 1 no rescale math, 2 no quantizer math, 4 no result stores
-#endif
-
-// Optional wait profiling (build with -DPPML_Q8_TRACE): one thread of each role of CTA 0 adds up the cycles it
-// spends in each wait / work section and writes them to a global table at the end; off in normal builds.
-#ifdef PPML_Q8_TRACE
-__device__ long long g_q8_trace[64];
-#define TR_DECL long long tr_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tr_t_ = clock64(); const long long tr_start_ = tr_t_
-#define TR(i) do { const long long n_ = clock64(); tr_[i] += n_ - tr_t_; tr_t_ = n_; } while (0)
-#define TR_FLUSH(base, cond) do { if (blockIdx.x == 0 && (cond)) { for (int i_ = 0; i_ < 7; ++i_) g_q8_trace[(base) + i_] = tr_[i_]; \
-        g_q8_trace[(base) + 7] = clock64() - tr_start_; } } while (0)
-#else
-#define TR_DECL do {} while (0)
-#define TR(i) do {} while (0)
-#define TR_FLUSH(base, cond) do {} while (0)
-#endif
-
 constexpr int kTile = 128 * 128;          // bytes: one int8 A tile (128 rows x 128 K) == one weight stage == one raw fp32 stage
 constexpr int kMaxKT = 8;                 // K <= 1024
 constexpr int kMaxStages = 6;
@@ -436,20 +418,16 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const uint64_t dc = make_smem_desc(smem_base + L.c_off, 128, 256, 0);
             uint32_t bcnt = 0, n_it = 0, w_ph = 0; int w_s = 0; bool ok = true;
             uint32_t a_slot0 = 0, a_par0 = 0;           // slot and parity of K step 0 of the current item
-            TR_DECL;
             int mt = 0, nb0 = 0, nb1 = 0;
             for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
                 for (int nb = nb0; nb < nb1 && ok; ++nb) {
                     uint32_t a_slot = a_slot0, a_par = a_par0;              // A slots form a ring over (item, K step)
                     for (int ks = 0; ks < p.KT; ++ks, a_slot = (a_slot + 1 == static_cast<uint32_t>(p.AR)) ? 0u : a_slot + 1u,
                                                     a_par ^= (a_slot == 0u) ? 1u : 0u) {
-                        TR(0);
                         if (nb == nb0) {
                             if (!mbar_wait(a_full(a_slot), a_par, cta_abort, p.err, 0x1301)) { ok = false; break; }
                         }
-                        TR(1);
                         if (!mbar_wait(w_full(w_s), w_ph, cta_abort, p.err, 0x1302)) { ok = false; break; }
-                        TR(2);
                         tc_fence_after();
                         const uint64_t da = da0 + static_cast<uint64_t>(a_slot * (kTile >> 4));
                         const uint64_t db = db0 + static_cast<uint64_t>(w_s * (kTile >> 4));
@@ -461,9 +439,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             const uint32_t par = ((bcnt >> 2) & 1u) ^ 1u;
 #pragma unroll
                             for (int g = 0; g < 2; ++g) {
-                                TR(0);
                                 if (!mbar_wait(t_empty(2 * g), par, cta_abort, p.err, 0x1303)) { ok = false; break; }
-                                TR(3);
                                 tc_fence_after();
 #pragma unroll
                                 for (int j = 2 * g; j < 2 * g + 2; ++j) {
@@ -476,9 +452,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                         } else
                         for (int j = 0; j < nstep; ++j, ++bcnt) {
                             const uint32_t slot = bcnt & 3u;
-                            TR(0);
                             if (!mbar_wait(t_empty(slot), ((bcnt >> 2) & 1u) ^ 1u, cta_abort, p.err, 0x1303)) { ok = false; break; }
-                            TR(3);
                             tc_fence_after();
                             umma<MmaKind::I8>(tmem_base + slot * 128u, da + 2u * j, db + 2u * j, idesc, 0u);
                             umma<MmaKind::I8>(tmem_base + slot * 128u, dc, dc, idesc_off, 1u);
@@ -492,8 +466,6 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 }
                 for (int ks = 0; ks < p.KT; ++ks) { if (++a_slot0 == static_cast<uint32_t>(p.AR)) { a_slot0 = 0; a_par0 ^= 1u; } }
             }
-            TR(0);
-            TR_FLUSH(0, true);
         }
         __syncwarp();
     } else if (warp >= kFirstQuantWarp && warp < kFirstQuantWarp + kQuantWarps) {
@@ -502,31 +474,23 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const int row0 = (warp - kFirstQuantWarp) * (128 / kQuantWarps) + lane;
         uint32_t n_it = 0, x_ph = 0; int x_s = 0; bool ok = p.preq == 0;
         uint32_t a_slot = 0, a_par = 0;                 // ring position of the K step being quantized
-        TR_DECL;
         int mt = 0, nb0 = 0, nb1 = 0;
         for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
-            TR(0);
             if (n_it >= 2) {    // the scale table of this parity was last read by the epilogue two items ago
                 if (!mbar_wait(epi_done(n_it & 1u), ((n_it >> 1) - 1u) & 1u, cta_abort, p.err, 0x1501)) { ok = false; break; }
             }
             __half* da_w = da_s + (n_it & 1u) * p.nblk * 128;
-            TR(1);
             for (int kb = 0; kb < p.nblk; ++kb) {
-                TR(0);
                 if ((kb & 3) == 0) {     // the tensor core must have finished with the previous user of this slot
                     if (!mbar_wait(a_empty(a_slot), a_par ^ 1u, cta_abort, p.err, 0x1502)) { ok = false; break; }
                 }
-                TR(2);
                 if (!mbar_wait(raw_full(x_s), x_ph, cta_abort, p.err, 0x1503)) { ok = false; break; }
-                TR(3);
                 const uint8_t* raw = sg + L.raw_off + x_s * kTile;
                 uint8_t* at = sg + L.a_off + a_slot * kTile;
                 const int c0 = (kb & 3) * 2;
                 float d0 = 1.0f, d1 = 1.0f;
-                if (!(PPML_Q8_ABL & 2)) {
-                    if (kQuantWarps == 4) d0 = quantize_row(raw, at, row0, c0);
-                    else quantize_rows2(raw, at, row0, c0, d0, d1);
-                }
+                if (kQuantWarps == 4) d0 = quantize_row(raw, at, row0, c0);
+                else quantize_rows2(raw, at, row0, c0, d0, d1);
                 da_w[kb * 128 + row0] = __float2half_rn(d0);
                 if (kQuantWarps == 2) da_w[kb * 128 + row0 + 32] = __float2half_rn(d1);
                 fence_proxy_async_smem();
@@ -538,10 +502,8 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 }
                 if (++x_s == p.RS) { x_s = 0; x_ph ^= 1u; }
                 if ((kb & 3) == 3 || kb == p.nblk - 1) { if (++a_slot == static_cast<uint32_t>(p.AR)) { a_slot = 0; a_par ^= 1u; } }
-                TR(4);
             }
         }
-        TR_FLUSH(8, warp == kFirstQuantWarp && lane == 0);
     } else {
         // ---------------- epilogue: per-block rescale, fp32 accumulation in registers ----------------------
         const int q = warp & 3;                            // TMEM lane quarter
@@ -563,7 +525,6 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (lane == 0) mbar_arrive(dw_full);
             if (!mbar_wait(dw_full, 0u, cta_abort, p.err, 0x1404)) ok = false;
         }
-        TR_DECL;
         int mt = 0, nb0 = 0, nb1 = 0;
         for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
             const int tok = mt * 128 + row;
@@ -603,11 +564,6 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                                 p.sumi_out[(static_cast<size_t>(tok) * p.Mout + mo) * p.nblk + kb] = static_cast<int>(v[j]) - (1 << 19);
                         }
                     }
-                    if (PPML_Q8_ABL & 1) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) acc[h * 16 + j] += __uint_as_float(v[j]);
-                        return;
-                    }
 #pragma unroll
                     for (int j4 = 0; j4 < 4; ++j4) {
                         const float4 w4 = lds_f4(dwp + j4 * 16);
@@ -620,9 +576,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 // Two 16-column halves per block, software-pipelined: while one half is rescaled the TMEM load of
                 // the next half (of this block or of the next one) is in flight.
                 uint32_t va[16], vb[16];
-                TR(0);
                 if (!mbar_wait(t_full(bcnt & 3u), (bcnt >> 2) & 1u, cta_abort, p.err, 0x1401)) { ok = false; break; }
-                TR(1);
                 tc_fence_after();
                 tmem_ld16(taddr0 + (bcnt & 3u) * 128u, va);
                 uint16_t da_raw = lds_u16(da_a0);                     // d_a of block 0 of this row
@@ -631,39 +585,29 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 // with parity `acq_par` before the next block is touched.
                 auto one_block = [&](int kb, uint32_t slot, uint32_t nslot, bool has_next, uint32_t rel_bar, uint32_t acq_bar,
                                      uint32_t acq_par) -> bool {
-                    TR(0);
                     const float da = __half2float(__ushort_as_half(da_raw)) * kTwo100;
                     const float dc = da * __uint_as_float(0x80080000u);      // -2^-130 * (d_a * 2^100)
-                    TR(5);
                     tmem_ld_wait();
-                    TR(2);
                     tmem_ld16(taddr0 + slot * 128u + 16u, vb);
                     // the next block's scale, in flight during the math; only when that block is already known to be
                     // complete (same pair): its scale is written by the quantizer just before its MMA can be issued
                     if (has_next && acq_bar == 0u) da_raw = lds_u16(da_a0 + (kb + 1) * 256);
-                    TR(5);
                     rescale(va, 0, kb, da, dc);
-                    TR(3);
                     tmem_ld_wait();
-                    TR(2);
                     if (rel_bar != 0u) {
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(rel_bar);         // the slot(s) may take their next blocks already
                     }
-                    TR(6);
                     if (has_next) {
                         if (acq_bar != 0u) {
                             if (!mbar_wait(acq_bar, acq_par, cta_abort, p.err, 0x1401)) return false;
-                            TR(1);
                             tc_fence_after();
                             da_raw = lds_u16(da_a0 + (kb + 1) * 256);
                         }
                         tmem_ld16(taddr0 + nslot * 128u, va);
-                        TR(5);
                     }
                     rescale(vb, 1, kb, da, dc);
-                    TR(3);
                     return true;
                 };
                 if ((p.nblk & 3) == 0) {
@@ -684,7 +628,6 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     }
                 }
                 if (!ok) break;
-                TR(0);
                 if (!dw_resident) { __syncwarp(); if (lane == 0) mbar_arrive(dw_free); ++dwcnt; }
                 const int mo0 = nb * 128 + cg * 32;
                 if (p.bias != nullptr) {
@@ -710,13 +653,12 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             const int rr = (lane >> 2) + 8 * i;
                             const int trow = mt * 128 + q * 32 + rr;
                             const float4 val = *reinterpret_cast<const float4*>(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) << 4));
-                            if ((PPML_Q8_ABL & 4) && val.x != 123.456f) continue;
                             if (trow < p.Ntok && col < p.Mout)      // staged mode requires Mout % 4 == 0
                                 *reinterpret_cast<float4*>(p.C + static_cast<size_t>(trow) * p.Mout + col) = val;
                         }
                         __syncwarp();
                     }
-                } else if (tok < p.Ntok && (!(PPML_Q8_ABL & 4) || acc[lane] == 123.456f)) {
+                } else if (tok < p.Ntok) {
                     if (p.c_trans) {
                         float* dst = p.C + static_cast<size_t>(tok) * p.Mout + mo0;
                         if (p.vec_ok && mo0 + 32 <= p.Mout) {
@@ -734,11 +676,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     }
                 }
             }
-            TR(4);
             __syncwarp();
             if (lane == 0) mbar_arrive(epi_done(n_it & 1u));
         }
-        TR_FLUSH(16, warp == kFirstEpiWarp + 5 && lane == 0);
     }
 
     tc_fence_before();
@@ -748,12 +688,6 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
 }  // namespace
 
-#ifdef PPML_Q8_TRACE
-extern "C" int ppml_b200_q8_trace_read(long long* out64) {
-    cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out64, g_q8_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 // W: Q8_0R weights ([Mout*nblk*32] int8 plane followed by [Mout*nblk] half scales); X fp32 [Ntok][K];
 // M = weight rows (out features), N = tokens, as in the reference's launcher.

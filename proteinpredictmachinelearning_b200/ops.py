@@ -8,7 +8,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import PATH_AUTO, PATH_SIMT, PATH_UMMA, TF32_ROUND, FlashCfg
+from ._lib import PATH_AUTO, PATH_SIMT, PATH_UMMA, TF32_ROUND, TF32_TMA, FlashCfg
 
 
 def _p(t):
@@ -37,8 +37,9 @@ def device_status():
     return rc, where.value
 
 
-def mul_mat_cuda(A, B, bias=None, path=PATH_AUTO, tf32_mode=TF32_ROUND, out=None):
-    """C[M,N] = A[M,K] @ B[N,K]^T (+ bias[N]); replaces mul_mat_cuda / mul_mat_mma_tf32_smem."""
+def mul_mat_cuda(A, B, bias=None, path=PATH_AUTO, tf32_mode=TF32_TMA, out=None):
+    """C[M,N] = A[M,K] @ B[N,K]^T (+ bias[N]); replaces mul_mat_cuda / mul_mat_mma_tf32_smem.  The default
+    tf32_mode is the one the C++ forwarders under the reference's names use (the TMA unit delivers tf32)."""
     A, B = _f32c(A), _f32c(B)
     M, K = A.shape
     N = B.shape[0]
@@ -59,6 +60,21 @@ def mul_mat_16(A16, B16, bias=None, path=PATH_AUTO, out=None):
     fn = _lib.load().ppml_b200_mul_mat_f16 if A16.dtype == torch.float16 else _lib.load().ppml_b200_mul_mat_bf16
     _check(fn(_p(A16), _p(B16), _p(Cout), M, K, N, _p(bias), path, _stream()), "mul_mat_16")
     return Cout
+
+
+def mul_mat_f32_as_bf16(A, B, bias=None, path=PATH_AUTO, out=None):
+    """fp32 tensors, bf16 products (activations cast into library scratch, weights into a cached bf16 copy)."""
+    A, B = _f32c(A), _f32c(B)
+    M, K = A.shape
+    N = B.shape[0]
+    Cout = out if out is not None else torch.empty((M, N), device=A.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_mul_mat_f32_as_bf16(_p(A), _p(B), _p(Cout), M, K, N, _p(bias), path, _stream())
+    _check(rc, "mul_mat_f32_as_bf16")
+    return Cout
+
+
+def bf16_shadow_invalidate(B=None):
+    _lib.load().ppml_b200_bf16_shadow_invalidate(_p(B))
 
 
 def cast(x, dtype):
@@ -134,10 +150,12 @@ def mul_mat_q8_noalloc(W, X, M, wtype=2, c_trans=1, bias=None, out=None):
     return Cout
 
 
-def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-9, bias_bcast=False, path=PATH_AUTO, out=None):
+def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-9, bias_bcast=False, path=PATH_AUTO, out=None,
+                            Bc=64):
     """Q [B,h,L,d], K/V [B,h,Lk,d], bias [B,h,L,Lk] (or [h,L,Lk] shared over B with bias_bcast).
     Returns (O, LSE).  Lk != L and bias_bcast go through the extended entry.  `out` is an optional contiguous
-    fp32 destination of Q's shape (any 16-byte-aligned address)."""
+    fp32 destination of Q's shape (any 16-byte-aligned address).  Bc: the reference's key tile (a row whose first
+    Bc scores are all -inf gives zeros, as in the reference); Bc < 0 switches that rule off."""
     half = Q.dtype in (torch.float16, torch.bfloat16)         # 16-bit Q/K/V: fp32 softmax, bias, output
     if half:
         assert K.dtype == Q.dtype and V.dtype == Q.dtype
@@ -149,7 +167,7 @@ def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-
     O = torch.empty(Q.shape, device=Q.device, dtype=torch.float32) if out is None else out
     assert O.is_contiguous() and O.dtype == torch.float32 and O.shape == Q.shape
     LSE = torch.empty((B, h, L), device=Q.device, dtype=torch.float32)
-    cfg = FlashCfg(B, h, L, d, int(causal), float(scale), float(eps), 64, 64)
+    cfg = FlashCfg(B, h, L, d, int(causal), float(scale), float(eps), 64, int(Bc))
     lib = _lib.load()
     if bias is not None:
         bias = _f32c(bias)

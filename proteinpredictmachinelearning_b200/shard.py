@@ -41,12 +41,31 @@ def opm_slabs(D, world, rank):
     return split(D, world, rank)
 
 
+def _require_equal_shards(n_local, world, group, what):
+    """Every rank must bring the same number of leading rows: a collective entered with different sizes hangs or
+    overwrites memory.  The sizes are exchanged first (one small all-gather) and a mismatch raises on every rank."""
+    import torch
+    import torch.distributed as dist
+    mine = torch.tensor([int(n_local)], dtype=torch.int64)
+    backend = dist.get_backend(group)
+    if backend == "nccl":
+        mine = mine.cuda()
+    sizes = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(sizes, mine, group=group)
+    sizes = [int(t.item()) for t in sizes]
+    if any(n != sizes[0] for n in sizes):
+        raise ValueError(f"{what}: ranks hold different shard sizes {sizes}; split a total that is a multiple of the "
+                         "number of ranks (split(total, world, rank) gives the last rank the remainder otherwise)")
+
+
 def all_gather_rows(x_local, world, group=None):
-    """All-gather along dim 0 of equally sized shards (NCCL on GPUs, gloo in the CPU tests)."""
+    """All-gather along dim 0 of equally sized shards (NCCL on GPUs, gloo in the CPU tests).  Raises ValueError on
+    every rank when the shards differ in size."""
     import torch
     import torch.distributed as dist
     if world == 1:
         return x_local
+    _require_equal_shards(x_local.shape[0], world, group, "all_gather_rows")
     parts = [torch.empty_like(x_local) for _ in range(world)]
     dist.all_gather(parts, x_local.contiguous(), group=group)
     return torch.cat(parts, dim=0)
@@ -55,7 +74,7 @@ def all_gather_rows(x_local, world, group=None):
 def transpose_exchange(x_local, world, group=None):
     """The (n, l) transpose of an activation [N, L, C] that is sharded by contiguous n ranges, as the reference's
     `permute({0,2,1,3})` copies after MSA column attention and pair row attention do on one device
-    (src/ops/Attention.cpp:489, :744): x_local [N/world, L, C] -> this rank's rows [L/world, N, C] of the transposed
+    (src/modules/Attention.cpp:489, :744): x_local [N/world, L, C] -> this rank's rows [L/world, N, C] of the transposed
     tensor.  One all-to-all in which every rank keeps 1/world of its data, plus local re-layouts."""
     import torch.distributed as dist
     n_loc, L, C = x_local.shape
@@ -63,6 +82,7 @@ def transpose_exchange(x_local, world, group=None):
         return x_local.permute(1, 0, 2).contiguous()
     if L % world:
         raise ValueError("L must be a multiple of the number of ranks")
+    _require_equal_shards(n_loc, world, group, "transpose_exchange")
     l_loc = L // world
     send = x_local.reshape(n_loc, world, l_loc, C).permute(1, 0, 2, 3).contiguous()      # [to rank][n][l][c]
     recv = send.new_empty(send.shape)                                                    # [from rank][n][l][c]

@@ -38,6 +38,16 @@ def attn_case(B, h, L, d, Lk=None, seed=3, bias=True, bias_bcast=False):
     return Q, K, V, bi
 
 
+def attn_masked_first_tile_case(d=8, L=100, Lk=200, seed=13):
+    """Rows whose leading scores are -inf: row 3 has the reference's whole first key tile (64 keys) masked and later
+    keys visible, row 4 has 63 of them masked, row 2 two whole tiles."""
+    Q, K, V, bi = attn_case(2, 2, L, d, Lk=Lk, seed=seed)
+    bi[:, :, 3, :64] = -np.inf
+    bi[:, :, 4, :63] = -np.inf
+    bi[:, :, 2, :130] = -np.inf
+    return Q, K, V, bi
+
+
 def tri_case(D, I, J, K, B=1, outgoing=True, seed=4):
     r = rng(seed)
     if outgoing:

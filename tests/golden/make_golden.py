@@ -24,11 +24,17 @@ HOT_LAUNCHERS = ("mul_mat_cuda", "mul_mat_mma_tf32_smem", "mul_mat_mma_f16", "mu
                  "tri_mul_cuda", "outer_prod_mean_cuda", "mulmat_stats_cuda", "cutlass_hw_supported")
 
 
-def launcher_symbols(reference="/root/reference"):
+def reference_dir():
+    """The reference checkout: $PPML_REFERENCE_DIR, else the directory `reference` beside this repository."""
+    return os.environ.get("PPML_REFERENCE_DIR") or os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference"))
+
+
+def launcher_symbols(reference=None):
     """The mangled names the reference's dispatcher (src/backend/CUDAKernels.cpp) leaves undefined for the
     hot-path launchers: exactly what a drop-in library has to export."""
     import subprocess
     import tempfile
+    reference = reference or reference_dir()
     with tempfile.TemporaryDirectory() as tmp:
         obj = os.path.join(tmp, "CUDAKernels.o")
         subprocess.check_call(["g++", "-std=c++17", "-O0", "-w", "-fPIC", f"-I{reference}/include",
@@ -73,6 +79,14 @@ def main():
     out["fa_legacy_O"] = ref.attention_legacy(Q, K, V, bi, 1 / np.sqrt(32.0))
     Q, K, V, bi = cases.attn_case(3, 2, 1, 8, Lk=40, seed=33)
     out["fa_legacy_q1_O"] = ref.attention_legacy(Q, K, V, bi, 1 / np.sqrt(32.0))
+
+    # a row whose first key tile holds only -inf scores comes out as zeros in the reference (NaN, then `l > 0` fails)
+    Q, K, V, bi = cases.attn_masked_first_tile_case(d=8, L=100, Lk=200)
+    # the reference's config has one L: pad the queries to Lk rows and keep the first L (rows are independent)
+    Qp = np.zeros((2, 2, 200, 8), np.float32); Qp[:, :, :100] = Q
+    bp = np.zeros((2, 2, 200, 200), np.float32); bp[:, :, :100] = bi
+    o, l_ = ref.flash_attn(Qp, K, V, bp, scale=1 / np.sqrt(32.0))
+    out["fa_masked_O"], out["fa_masked_LSE"] = o[:, :, :100].copy(), l_[:, :, :100].copy()
 
     # pair-track contractions
     l, r = cases.tri_case(6, 20, 24, 28, outgoing=True)

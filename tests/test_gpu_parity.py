@@ -59,9 +59,12 @@ def test_mul_mat_simt(oracle, M, K, N, bias):
 
 @pytest.mark.parametrize("M,K,N", [s for s in MM_SHAPES if s[1] % 4 == 0])
 @pytest.mark.parametrize("bias", [False, True])
-def test_mul_mat_tf32_umma(oracle, M, K, N, bias):
+@pytest.mark.parametrize("mode", [TF32_ROUND, TF32_TMA])
+def test_mul_mat_tf32_umma(oracle, M, K, N, bias, mode):
+    """Both ways of rounding fp32 to tf32 (in shared memory with cvt.rna, or by the TMA unit: the mode the C++
+    forwarders and the benchmark use) meet the required 1e-3."""
     a, b, bi = cases.mul_mat_case(M, K, N, seed=1, bias=bias)
-    got = host(ops.mul_mat_cuda(dev(a), dev(b), None if bi is None else dev(bi), path=PATH_UMMA, tf32_mode=TF32_ROUND))
+    got = host(ops.mul_mat_cuda(dev(a), dev(b), None if bi is None else dev(bi), path=PATH_UMMA, tf32_mode=mode))
     key = f"{'mmb' if bias else 'mm'}_{M}_{K}_{N}"
     ref = GOLD[key] if key in GOLD else oracle.mul_mat_f32(a, b, bi)
     assert cases.rel_err(got, ref) <= TOL_TF32
@@ -74,11 +77,13 @@ CENSUS_SHAPES = [(2601, 128, 256), (2601, 128, 128), (2601, 256, 128), (408, 256
 
 
 @pytest.mark.parametrize("M,K,N", CENSUS_SHAPES)
-def test_mul_mat_dev_forward_census(oracle, M, K, N):
-    """Default dispatch (what the executor gets): tensor cores where TMA can address the operands, CUDA cores otherwise."""
+@pytest.mark.parametrize("mode", [TF32_ROUND, TF32_TMA])
+def test_mul_mat_dev_forward_census(oracle, M, K, N, mode):
+    """Tensor-core dispatch (what the executor gets with PPML_MUL_MAT_TC=1): tensor cores where TMA can address the
+    operands, CUDA cores otherwise."""
     a, b, bi = cases.mul_mat_case(M, K, N, seed=1, bias=True)
     ref = oracle.mul_mat_f32(a, b, bi)
-    assert cases.rel_err(host(ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_AUTO)), ref) <= TOL_TF32
+    assert cases.rel_err(host(ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_AUTO, tf32_mode=mode)), ref) <= TOL_TF32
     assert cases.rel_err(host(ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_SIMT)), ref) <= TOL_FP32
     a16, b16 = dev(a).bfloat16(), dev(b).bfloat16()
     ref16 = oracle.mul_mat_f32(host(a16.float()), host(b16.float()), bi)
@@ -114,6 +119,18 @@ def test_mul_mat_tf32_modes_report_error(oracle, mode):
     err = cases.rel_err(got, oracle.mul_mat_f32(a, b))
     print(f"tf32 mode {mode}: normalised error {err:.3e}")
     assert err <= (TOL_TF32 if mode == TF32_ROUND else 4e-3)
+
+
+def test_mul_mat_tf32_tma_rounding_equals_cvt_rna():
+    """The TMA unit's fp32 -> tf32 conversion rounds like cvt.rna.tf32: the two modes give identical bits."""
+    a, b, bi = cases.mul_mat_case(2048, 256, 256, seed=8, bias=True)
+    r = np.random.default_rng(8)
+    a *= (10.0 ** r.integers(-3, 4, a.shape)).astype(np.float32)        # spread the exponents
+    a[5, :8] = [0.0, -0.0, 1.0, -1.0, 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -11, -(1.0 + 2.0 ** -11), 2.0 ** -120]   # ties and a tiny value
+    c_round = ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_UMMA, tf32_mode=TF32_ROUND)
+    c_tma = ops.mul_mat_cuda(dev(a), dev(b), dev(bi), path=PATH_UMMA, tf32_mode=TF32_TMA)
+    assert torch.equal(c_round, c_tma)
+    assert cases.rel_err(host(c_tma), oracle.mul_mat_f32(a, b, bi)) <= TOL_TF32
 
 
 def test_mul_mat_large_property_linearity():
@@ -398,6 +415,35 @@ def test_attention_output_at_16_byte_offset(oracle):
     rO, _ = oracle.flash_attn(Q, K, V, bi, scale=1 / np.sqrt(32.0))
     assert cases.rel_err(host(O), rO) <= TOL_TF32
     assert float(buf[:4].abs().max()) == 0 and float(buf[-4:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("d,L,Lk,path", [(32, 100, 200, PATH_UMMA), (32, 100, 200, PATH_SIMT), (8, 100, 200, PATH_AUTO),
+                                         (8, 5, 200, PATH_AUTO), (64, 40, 136, PATH_AUTO)])
+def test_attention_first_key_tile_masked(oracle, d, L, Lk, path):
+    """A query row whose first 64 scores (the reference's first key tile) are all -inf: the reference's CPU kernel turns
+    it into O = 0, LSE = -inf although later keys are visible (src/ops/FlashAttn.cpp:94-121); every kernel here does the
+    same.  A row with 63 masked keys is an ordinary row.  Bc < 0 switches the rule off and gives the softmax over the
+    visible keys."""
+    Q, K, V, bi = cases.attn_masked_first_tile_case(d=d, L=L, Lk=Lk)
+    scale = 1 / np.sqrt(32.0)
+    tol_o, tol_l = (TOL_TF32, 2e-3) if path == PATH_UMMA else (TOL_FP32, 1e-5)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=scale, path=path)
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale)
+    O, LSE = host(O), host(LSE)
+    assert np.all(rO[:, :, 3] == 0) and np.all(rL[:, :, 3] == -np.inf)      # what the reference does
+    assert np.all(rO[:, :, 2] == 0) and np.any(rO[:, :, 4] != 0)
+    assert np.all(O[:, :, 3] == 0) and np.all(LSE[:, :, 3] == -np.inf) and np.all(O[:, :, 2] == 0)
+    assert np.isfinite(O).all() and cases.rel_err(O, rO) <= tol_o
+    if (d, L, Lk) == (8, 100, 200):
+        assert cases.rel_err(O, GOLD["fa_masked_O"]) <= tol_o       # produced by the reference's own CPU code
+    fin = np.isfinite(rL)
+    assert np.array_equal(np.isfinite(LSE), fin) and np.abs(LSE[fin] - rL[fin]).max() <= tol_l
+    # rule off: the defined softmax (checked against torch)
+    O2, LSE2 = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), dev(bi), scale=scale, path=path, Bc=-1)
+    s = torch.einsum("bhid,bhjd->bhij", dev(Q), dev(K)) * scale + dev(bi)
+    ref2 = torch.einsum("bhij,bhjd->bhid", torch.softmax(s, dim=-1), dev(V))
+    assert float((O2 - ref2).abs().max() / ref2.abs().max()) <= max(tol_o, 1e-5)
+    assert float((LSE2 - torch.logsumexp(s, dim=-1)).abs().max()) <= max(tol_l, 1e-4)
 
 
 def test_attention_fully_masked_row():

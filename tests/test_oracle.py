@@ -68,6 +68,15 @@ def test_mul_mat_f16_golden(oracle):
     assert np.array_equal(got, GOLD["mm16_40_64_48"])
 
 
+def test_attention_first_key_tile_masked_golden(oracle):
+    """The reference's CPU kernel gives O = 0, LSE = -inf for a row whose first 64 scores are all -inf, even with
+    visible keys behind them (src/ops/FlashAttn.cpp:94-121); the restatement does the same, bit for bit."""
+    Q, K, V, bi = cases.attn_masked_first_tile_case(d=8, L=100, Lk=200)
+    O, LSE = oracle.flash_attn(Q, K, V, bi, scale=1 / np.sqrt(32.0))
+    assert np.array_equal(O, GOLD["fa_masked_O"]) and np.array_equal(LSE, GOLD["fa_masked_LSE"])
+    assert np.all(O[:, :, 3] == 0) and np.all(LSE[:, :, 3] == -np.inf) and np.any(O[:, :, 4] != 0)
+
+
 def _q8_inputs():
     w, x = cases.q8_case(24, 20, 128, seed=2)
     x[3, :32] = 0.0

@@ -81,6 +81,20 @@ def _worker(rank, world, port, q):
     full = shard.all_gather_rows(mine, world).numpy()
     ok["transpose"] = np.array_equal(full, x.transpose(1, 0, 2))
 
+    # unequal shards (7 rows over 2 ranks: 4 + 3) must be refused on every rank, not entered into a collective
+    lo, hi = shard.split(7, world, rank)
+    part = torch.zeros((hi - lo, 5))
+    try:
+        shard.all_gather_rows(part, world)
+        ok["unequal_gather_refused"] = False
+    except ValueError:
+        ok["unequal_gather_refused"] = True
+    try:
+        shard.transpose_exchange(torch.zeros((hi - lo, 4, 2)), world)
+        ok["unequal_transpose_refused"] = False
+    except ValueError:
+        ok["unequal_transpose_refused"] = True
+
     if rank == 0:
         q.put(ok)
     dist.barrier()
