@@ -6,36 +6,36 @@ attention call sites) at L = 256 residues, MSA depth N = 256, d_msa = 256, d_pai
 
   MSA row attention   5 Linears 256->256 on N*L tokens, pair bias Linear 128->8 on L*L tokens, attention
                       (batch N, shared bias [8, L, L], scale 1/sqrt(32))
-  MSA column attn     5 Linears 256->256, attention without bias (batch = chunks of N flat positions)
+  MSA column attn     5 Linears 256->256, attention without bias (batch = chunks of N flat positions), (n, l) transpose
   MSA feed-forward    256->1024, 1024->256
   MSA -> pair         left / right 256->16, outer-product-mean (16 slabs), out 256->128 on L*L tokens
   triangle mult.      out and in: 6 Linears 128->128 each, tri_mul over 128 channel slabs of L x L
   pair row / col attn each: 4 Linears 128->256, bias 128->8, out 256->128, attention (batch L, shared bias,
-                      scale 1/sqrt(16): the reference takes it from config.head_dim)
+                      scale 1/sqrt(16): the reference takes it from config.head_dim); the row variant ends with a transpose
   pair feed-forward   128->256, 256->128
 
 Linears that the reference converts to Q8 (attention projections and the MSA->pair projections,
 src/model/PPML.cpp:4434-4437) run the Q8 kernel with its bias epilogue, the others the fp32 (tf32 tensor-core) kernel.
 LayerNorm, gating, residual adds and the head split views are the reference's elementwise glue and are not part of
 this path: they are not run here, so the figure is the sum of the path's kernels and exchanges, not a forward time.
+Every op takes its input from a tensor generated from a seed common to all ranks (the op chains that need no glue
+between them -- projections -> attention -> output Linear, left / right -> outer-product-mean -- are connected).
 
 Sharding over G ranks follows the reference's flat-buffer semantics: every activation is cut into G contiguous
 flat chunks (token rows; attention batches; tri_mul channel slabs; outer-product-mean d1 slabs).  Exchanges per
 block, all through NCCL into local memory before any kernel reads them: all-gather of each pair bias ([L*L, 8],
-2 MiB, three times), all-gather of the outer-product-mean's `right` operand (4 MiB), and two all-to-alls of 64 MiB in
-total that stand for the (n, l) transposes closing MSA column attention and pair row attention
-(src/modules/Attention.cpp:489, :744).  With G = 1 there is no exchange.  Total work is fixed as G grows ("strong").
-The exchanges run in stream order between the kernels.  Running them asynchronously behind independent products
-(bias gathered during the projections, the Linear before a transpose cut into row chunks whose all-to-alls follow
-the next chunk's product) was measured slower on two GPUs (2.43 against 1.78 ms per block): the collectives' CTAs
-take SMs that the one-CTA-per-SM persistent kernels count on, and every product then ends with a second wave.
+2 MiB, three times), all-gather of the outer-product-mean's `right` operand (4 MiB), and two (n, l) transposes
+(src/modules/Attention.cpp:489, :744: one all-to-all of 64 MiB in total plus local re-layouts each).  With G = 1 the
+transposes are local copies and nothing else is exchanged.  Total work is fixed as G grows ("strong").
 
-The block is timed twice: launched op by op from the host ("eager_ms", with the per-op split of rank 0 from a pass with
-events around every op class), and with the seven compute segments between the exchanges captured as CUDA graphs and
-replayed, the collectives still launched from the host ("value": with several ranks the kernels are short and host
-launch overhead, about 40 us per call through the Python mirror, would otherwise dominate).  Collectives are never
-captured: a captured block with NCCL inside did not finish on two ranks here.
-Prints one JSON line; times are CUDA-event times, maximum over ranks.
+Parity: the same block code runs a second time on the rank's own GPU with G = 1 (the unsharded block, same inputs and
+weights), and every op's sharded result must equal the matching contiguous part of the unsharded result bit for bit
+(token rows, batches and slabs are independent and go through the same tiles in the same order).
+
+Timing: the block is timed launched op by op from the host ("eager_ms", with a per-class split from events around
+every op), and with the compute segments between the exchanges captured as CUDA graphs and replayed, the collectives
+still launched from the host ("ms_per_block").  Collectives are never captured.  Times are CUDA-event times, maximum
+over ranks.
 """
 import argparse
 import json
@@ -44,10 +44,271 @@ import os
 L_RES, N_MSA, D_MSA, D_PAIR, HEADS, HEAD_DIM, OPM_D, TRI_D = 256, 256, 256, 128, 8, 32, 16, 128
 
 
-def run(gpus, steps, warmup, use_graph=True):
+class Block:
+    """The op sequence for one rank of a G-way partition (G = 1: the unsharded block).  Inputs and weights are shared
+    between instances; every instance owns its outputs."""
+
+    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev):
+        self.torch, self.dist, self.ops = torch, dist, ops
+        self.inp, self.weights, self.G, self.rank, self.dev = inputs, weights, G, rank, dev
+        self.out = {}            # named results of the last run
+        self.bufs = {}           # tensors that keep their address from step to step
+        self.timers = {}
+        self.capturing = False
+        self.ctx = {}
+        L, N = L_RES, N_MSA
+        self.tok_msa, self.tok_pair = N * L // G, L * L // G
+
+    # ---- helpers -----------------------------------------------------------------------------------------------
+    def rows(self, name):
+        """This rank's contiguous token rows of a common input."""
+        x = self.inp[name]
+        n = x.shape[0] // self.G
+        return x[self.rank * n:(self.rank + 1) * n]
+
+    def timed(self, name):
+        blk, torch = self, self.torch
+
+        class _T:
+            def __enter__(self):
+                if blk.capturing:
+                    return
+                self.e0 = torch.cuda.Event(enable_timing=True)
+                self.e1 = torch.cuda.Event(enable_timing=True)
+                self.e0.record()
+
+            def __exit__(self, *a):
+                if blk.capturing:
+                    return
+                self.e1.record()
+                blk.timers.setdefault(name, []).append((self.e0, self.e1))
+        return _T()
+
+    def buf(self, tag, shape, like=None):
+        if tag not in self.bufs:
+            self.bufs[tag] = self.torch.empty(shape, device=self.dev, dtype=self.torch.float32 if like is None else like.dtype)
+        return self.bufs[tag]
+
+    def linear(self, x, n_out, q8, tag):
+        """One Linear with bias on this rank's token rows."""
+        from proteinpredictmachinelearning_b200 import PATH_AUTO, TF32_TMA
+        w, b = self.weights[(tag, x.shape[1], n_out, q8)]
+        out = self.buf("lin_" + tag, (x.shape[0], n_out))
+        if q8:
+            self.ops.mul_mat_q8_cuda(w, x, n_out, wtype=2, c_trans=1, bias=b, path=PATH_AUTO, out=out)
+        else:
+            self.ops.mul_mat_cuda(x, w, bias=b, path=PATH_AUTO, tf32_mode=TF32_TMA, out=out)
+        self.out["lin_" + tag] = out
+        return out
+
+    def gather_rows(self, x, tag):
+        """All-gather of the ranks' contiguous row ranges (rank order = row order)."""
+        if self.G == 1:
+            return x
+        full = self.buf("ag_" + tag, (x.shape[0] * self.G,) + tuple(x.shape[1:]))
+        self.dist.all_gather_into_tensor(full, x)
+        return full
+
+    def transpose_nl(self, x, n_total, tag):
+        """The (n, l) transpose of an activation [n * l tokens, C] whose n range is cut over the ranks, as the reference's
+        `permute({0,2,1,3})` copies do on one device: returns this rank's rows [l_loc * n_total, C] of the transposed tensor."""
+        G, C = self.G, x.shape[1]
+        n_loc = n_total // G
+        l_tot = x.shape[0] // n_loc
+        x3 = x.view(n_loc, l_tot, C)
+        if G == 1:
+            out = self.buf("tr_" + tag, (l_tot, n_loc, C))
+            out.copy_(x3.permute(1, 0, 2))
+            return out.view(l_tot * n_loc, C)
+        l_loc = l_tot // G
+        send = self.buf("trs_" + tag, (G, n_loc, l_loc, C))
+        send.copy_(x3.view(n_loc, G, l_loc, C).permute(1, 0, 2, 3))          # [to rank][n][l][c]
+        recv = self.buf("trr_" + tag, (G, n_loc, l_loc, C))
+        self.dist.all_to_all_single(recv, send)
+        out = self.buf("tr_" + tag, (l_loc, G * n_loc, C))
+        out.view(l_loc, G, n_loc, C).copy_(recv.permute(2, 0, 1, 3))         # [l][from rank][n][c]
+        return out.view(l_loc * G * n_loc, C)
+
+    def attention(self, src, batch, bias, scale, tag):
+        """Projections, fused attention over this rank's batches (with the gathered pair bias, if any), output Linear."""
+        d_in = src.shape[1]
+        with self.timed("linear_q8"):
+            q = self.linear(src, HEADS * HEAD_DIM, True, tag + "q")
+            k = self.linear(src, HEADS * HEAD_DIM, True, tag + "k")
+            v = self.linear(src, HEADS * HEAD_DIM, True, tag + "v")
+            self.linear(src, HEADS * HEAD_DIM, True, tag + "g")
+        seq = q.shape[0] // batch
+        shape = (batch, HEADS, seq, HEAD_DIM)                                  # flat reinterpretation, as the reference's views
+        o = self.buf("att_" + tag, shape)
+        with self.timed("attention"):
+            self.ops.flash_attn_forward_cuda(q.view(shape), k.view(shape), v.view(shape), bias, scale=scale,
+                                             bias_bcast=bias is not None, out=o)
+        self.out["att_" + tag] = o
+        with self.timed("linear_q8"):
+            return self.linear(o.view(-1, HEADS * HEAD_DIM), d_in, True, tag + "o")
+
+    def pair_bias(self, tag):
+        with self.timed("linear_q8"):
+            return self.linear(self.rows("x_pair"), HEADS, True, tag + "b")          # [L*L/G, 8]
+
+    def bias_layout(self, gathered, tag):
+        """[L*L, 8] token-major -> [8, L, L], shared by every batch (the reference's permute copy)."""
+        b = self.buf("bias_" + tag, (HEADS, L_RES, L_RES))
+        b.view(HEADS, L_RES * L_RES).copy_(gathered.t())
+        self.out["bias_" + tag] = b
+        return b
+
+    # ---- compute segments (this library's kernels only: each can be captured as a CUDA graph) ---------------------
+    def seg_a(self):
+        self.ctx["mr_b"] = self.pair_bias("mr")
+
+    def seg_b(self):
+        x = self.rows("x_msa")
+        self.attention(x, N_MSA // self.G, self.ctx["mr_bias"], 1.0 / 32 ** 0.5, "mr")
+        self.ctx["col"] = self.attention(x, N_MSA // self.G, None, 1.0 / 32 ** 0.5, "mc")
+
+    def seg_c(self):
+        x = self.rows("x_msa")
+        with self.timed("linear_tf32"):
+            self.linear(x, 4 * D_MSA, False, "ff1")
+            self.linear(self.rows("x_ff"), D_MSA, False, "ff2")
+        with self.timed("linear_q8"):
+            self.ctx["left"] = self.linear(x, OPM_D, True, "ol")
+            self.ctx["right"] = self.linear(x, OPM_D, True, "or")
+
+    def seg_d(self):
+        G, L, N = self.G, L_RES, N_MSA
+        opm = self.buf("opm", (OPM_D // G * OPM_D, L, L, 1))
+        with self.timed("outer_prod_mean"):
+            self.ops.outer_prod_mean_slabs_cuda(self.ctx["left"].view(OPM_D // G, L, N, 1), self.ctx["right_all"].view(OPM_D, L, N, 1), out=opm)
+        self.out["opm"] = opm
+        with self.timed("linear_q8"):
+            self.linear(self.rows("x_opm"), D_PAIR, True, "oo")
+        x = self.rows("x_pair")
+        for direction in (True, False):
+            d = "out" if direction else "in"
+            with self.timed("linear_tf32"):
+                a = self.linear(x, TRI_D, False, "tl" + d)
+                b = self.linear(x, TRI_D, False, "tr" + d)
+                for t in ("tlg", "trg", "tg"):
+                    self.linear(x, TRI_D, False, t + d)
+            with self.timed("tri_mul"):
+                tm = self.ops.tri_mul_cuda(a.view(TRI_D // G, L, L, 1), b.view(TRI_D // G, L, L, 1), float(L), direction)
+            self.out["tri_" + d] = tm
+            with self.timed("linear_tf32"):
+                self.linear(tm.view(self.tok_pair, TRI_D), D_PAIR, False, "to" + d)
+        self.ctx["pr_b"] = self.pair_bias("pr")
+
+    def seg_e(self):
+        self.ctx["row"] = self.attention(self.rows("x_pair"), L_RES // self.G, self.ctx["pr_bias"], 1.0 / 16 ** 0.5, "pr")
+
+    def seg_f(self):
+        self.ctx["pc_b"] = self.pair_bias("pc")
+
+    def seg_g(self):
+        x = self.rows("x_pair")
+        self.attention(x, L_RES // self.G, self.ctx["pc_bias"], 1.0 / 16 ** 0.5, "pc")
+        with self.timed("linear_tf32"):
+            self.linear(x, 2 * D_PAIR, False, "pf1")
+            self.linear(self.rows("x_pff"), D_PAIR, False, "pf2")
+
+    # ---- exchanges (collectives, always launched from the host) ---------------------------------------------------
+    def ex_bias(self, src, dst):
+        def step():
+            with self.timed("exchange"):
+                self.ctx[dst] = self.bias_layout(self.gather_rows(self.ctx[src], dst), dst)
+        return step
+
+    def ex_right(self):
+        with self.timed("exchange"):
+            self.ctx["right_all"] = self.gather_rows(self.ctx["right"], "right")          # [N*L, 16] flat = [16][L][N]
+            self.out["right_all"] = self.ctx["right_all"]
+
+    def ex_transpose(self, src, n_total, dst):
+        def step():
+            with self.timed("exchange"):
+                self.ctx[dst] = self.transpose_nl(self.ctx[src], n_total, dst)
+                self.out[dst] = self.ctx[dst]
+        return step
+
+    def plan(self):
+        segments = [self.seg_a, self.seg_b, self.seg_c, self.seg_d, self.seg_e, self.seg_f, self.seg_g]
+        exchanges = [self.ex_bias("mr_b", "mr_bias"),                # pair bias of MSA row attention
+                     self.ex_transpose("col", N_MSA, "col_t"),       # (n, l) transpose closing column attention
+                     self.ex_right,
+                     self.ex_bias("pr_b", "pr_bias"),
+                     self.ex_transpose("row", L_RES, "row_t"),       # transpose closing pair row attention
+                     self.ex_bias("pc_b", "pc_bias")]
+        return segments, exchanges
+
+    def run(self, graphs=None):
+        segments, exchanges = self.plan()
+        for i, seg in enumerate(segments):
+            if graphs is not None and graphs[i] is not None:
+                graphs[i].replay()
+            else:
+                seg()
+            if i < len(exchanges):
+                exchanges[i]()
+
+
+# per rank and block: bytes received by each collective at G ranks (fp32)
+def exchange_bytes(G):
+    if G == 1:
+        return {}
+    frac = (G - 1) / G
+    return {"all_gather pair bias [L*L, 8] (x3)": int(L_RES * L_RES * HEADS * 4 * frac),
+            "all_gather outer-product-mean right [N*L, 16]": int(N_MSA * L_RES * OPM_D * 4 * frac),
+            "all_to_all MSA (n, l) transpose [N*L, 256] / G": int(N_MSA * L_RES * D_MSA * 4 / G * frac),
+            "all_to_all pair (row, col) transpose [L*L, 128] / G": int(L_RES * L_RES * D_PAIR * 4 / G * frac)}
+
+
+def make_inputs_and_weights(torch, ops, dev):
+    """Inputs and weights from one seed, identical on every rank."""
+    g = torch.Generator(device=dev).manual_seed(5)
+    rnd = lambda *shape: torch.randn(shape, device=dev, generator=g)
+    L, N = L_RES, N_MSA
+    inputs = {"x_msa": rnd(N * L, D_MSA), "x_pair": rnd(L * L, D_PAIR), "x_ff": rnd(N * L, 4 * D_MSA),
+              "x_pff": rnd(L * L, 2 * D_PAIR), "x_opm": rnd(L * L, OPM_D * OPM_D)}
+    spec = []
+    for tag, d_in in (("mr", D_MSA), ("mc", D_MSA), ("pr", D_PAIR), ("pc", D_PAIR)):
+        spec += [(tag + t, d_in, HEADS * HEAD_DIM, True) for t in "qkvg"] + [(tag + "o", HEADS * HEAD_DIM, d_in, True)]
+    spec += [(tag + "b", D_PAIR, HEADS, True) for tag in ("mr", "pr", "pc")]
+    spec += [("ff1", D_MSA, 4 * D_MSA, False), ("ff2", 4 * D_MSA, D_MSA, False), ("ol", D_MSA, OPM_D, True), ("or", D_MSA, OPM_D, True),
+             ("oo", OPM_D * OPM_D, D_PAIR, True), ("pf1", D_PAIR, 2 * D_PAIR, False), ("pf2", 2 * D_PAIR, D_PAIR, False)]
+    for d in ("out", "in"):
+        spec += [(t + d, D_PAIR, TRI_D, False) for t in ("tl", "tr", "tlg", "trg", "tg")] + [("to" + d, TRI_D, D_PAIR, False)]
+    weights = {}
+    for (tag, k, n_out, q8) in spec:
+        w = rnd(n_out, k) * 0.02
+        b = rnd(n_out) * 0.1
+        weights[(tag, k, n_out, q8)] = (ops.quantize_q8_0r(w) if q8 else w, b)
+    return inputs, weights
+
+
+def verify(torch, sharded, full, G, rank):
+    """Every named result of the sharded run against the matching contiguous part of the unsharded run, bit for bit."""
+    bad, n = [], 0
+    for name, got in sharded.out.items():
+        ref = full.out[name]
+        if name.startswith("bias_") or name == "right_all":
+            part = ref                                           # gathered: the whole tensor on every rank
+        else:
+            flat = ref.reshape(-1)
+            per = flat.numel() // G
+            part = flat[rank * per:(rank + 1) * per]
+        n += 1
+        if not torch.equal(got.reshape(-1), part.reshape(-1)):
+            bad.append(name)
+    return n, bad
+
+
+def measure(steps=5, warmup=3, use_graph=True, check=True):
+    """Runs the block on this process's rank (torch.distributed already initialised when WORLD_SIZE > 1) and returns the
+    record (identical on every rank as far as the timing goes; rank 0's split)."""
     import torch
     import torch.distributed as dist
-    from proteinpredictmachinelearning_b200 import PATH_AUTO, TF32_TMA, ops
+    from proteinpredictmachinelearning_b200 import ops
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -61,167 +322,9 @@ def run(gpus, steps, warmup, use_graph=True):
     L, N = L_RES, N_MSA
     for total in (N * L, L * L, N, L, OPM_D, TRI_D):
         if total % G:
-            raise SystemExit(f"{G} ranks do not divide the block's partitions")
-    g = torch.Generator(device=dev).manual_seed(5 + 1000 * rank)
-    rnd = lambda *shape: torch.randn(shape, device=dev, generator=g)
-
-    tok_msa, tok_pair = N * L // G, L * L // G          # this rank's token rows
-    x_msa, x_pair = rnd(tok_msa, D_MSA), rnd(tok_pair, D_PAIR)
-    x_ff, x_pff, x_opm = rnd(tok_msa, 4 * D_MSA), rnd(tok_pair, 2 * D_PAIR), rnd(tok_pair, OPM_D * OPM_D)
-
-    weights = {}
-
-    def linear(x, n_out, q8, tag):
-        """One Linear with bias on this rank's token rows."""
-        k = x.shape[1]
-        key = (tag, k, n_out, q8)
-        if key not in weights:
-            w = rnd(n_out, k) * 0.02
-            weights[key] = (ops.quantize_q8_0r(w) if q8 else w, torch.zeros(n_out, device=dev),
-                            torch.empty(x.shape[0], n_out, device=dev))
-        w, b, out = weights[key]
-        if q8:
-            ops.mul_mat_q8_cuda(w, x, n_out, wtype=2, c_trans=1, bias=b, path=PATH_AUTO, out=out)
-        else:
-            ops.mul_mat_cuda(x, w, bias=b, path=PATH_AUTO, tf32_mode=TF32_TMA, out=out)
-        return out
-
-    bufs = {}
-
-    def gather_rows(x, tag):
-        """All-gather of the ranks' contiguous row ranges (rank order = row order) into a buffer that keeps its address."""
-        if G == 1:
-            return x
-        if tag not in bufs:
-            bufs[tag] = torch.empty((x.shape[0] * G,) + tuple(x.shape[1:]), device=dev, dtype=x.dtype)
-        dist.all_gather_into_tensor(bufs[tag], x)
-        return bufs[tag]
-
-    def exchange(x, tag):
-        """The all-to-all behind a (n, l) transpose of a [rows, channels] activation: every rank keeps 1/G of its rows."""
-        if G == 1:
-            return x
-        if tag not in bufs:
-            bufs[tag] = torch.empty_like(x)
-        dist.all_to_all_single(bufs[tag], x)
-        return bufs[tag]
-
-    timers = {}
-    state = {"capturing": False}
-
-    class timed:
-        def __init__(self, name):
-            self.name = name
-
-        def __enter__(self):
-            if state["capturing"]:
-                return
-            self.e0 = torch.cuda.Event(enable_timing=True)
-            self.e1 = torch.cuda.Event(enable_timing=True)
-            self.e0.record()
-
-        def __exit__(self, *a):
-            if state["capturing"]:
-                return
-            self.e1.record()
-            timers.setdefault(self.name, []).append((self.e0, self.e1))
-
-    def attention(qkv_src, batch, bias_all, scale, tag):
-        """Projections, fused attention over this rank's batches (with the gathered pair bias, if any), output Linear."""
-        d_in = qkv_src.shape[1]
-        with timed("linear_q8"):
-            q = linear(qkv_src, HEADS * HEAD_DIM, True, tag + "q")
-            k = linear(qkv_src, HEADS * HEAD_DIM, True, tag + "k")
-            v = linear(qkv_src, HEADS * HEAD_DIM, True, tag + "v")
-            linear(qkv_src, HEADS * HEAD_DIM, True, tag + "g")
-        bias = None
-        if bias_all is not None:
-            with timed("exchange"):
-                bias = bias_all.t().contiguous().view(HEADS, L, L)              # [8, L, L], shared by every batch
-        seq = q.shape[0] // batch
-        shape = (batch, HEADS, seq, HEAD_DIM)                                  # flat reinterpretation, as the reference's views
-        with timed("attention"):
-            o, _ = ops.flash_attn_forward_cuda(q.view(shape), k.view(shape), v.view(shape), bias, scale=scale,
-                                               bias_bcast=bias is not None)
-        with timed("linear_q8"):
-            out = linear(o.view(-1, HEADS * HEAD_DIM), d_in, True, tag + "o")
-        return out
-
-    def pair_bias(tag):
-        with timed("linear_q8"):
-            return linear(x_pair, HEADS, True, tag + "b")                       # [L*L/G, 8]
-
-    # The block as an alternation of compute segments (this library's kernels only: each can be captured as a CUDA
-    # graph) and exchanges (collectives, always launched from the host).  `ctx` carries tensors between them; all of
-    # them keep their addresses from step to step.
-    ctx = {}
-
-    def seg_a():
-        ctx["mr_b"] = pair_bias("mr")
-
-    def seg_b():
-        attention(x_msa, N // G, ctx["mr_bias"], 1.0 / 32 ** 0.5, "mr")
-        ctx["col"] = attention(x_msa, N // G, None, 1.0 / 32 ** 0.5, "mc")
-
-    def seg_c():
-        with timed("linear_tf32"):
-            linear(x_msa, 4 * D_MSA, False, "ff1")
-            linear(x_ff, D_MSA, False, "ff2")
-        with timed("linear_q8"):
-            ctx["left"] = linear(x_msa, OPM_D, True, "ol")
-            ctx["right"] = linear(x_msa, OPM_D, True, "or")
-
-    def seg_d():
-        with timed("outer_prod_mean"):
-            ops.outer_prod_mean_slabs_cuda(ctx["left"].view(OPM_D // G, L, N, 1), ctx["right_all"].view(OPM_D, L, N, 1))
-        with timed("linear_q8"):
-            linear(x_opm, D_PAIR, True, "oo")
-        for direction in (True, False):
-            with timed("linear_tf32"):
-                a = linear(x_pair, TRI_D, False, "tl" + str(direction))
-                b = linear(x_pair, TRI_D, False, "tr" + str(direction))
-                for t in ("tlg", "trg", "tg"):
-                    linear(x_pair, TRI_D, False, t + str(direction))
-            with timed("tri_mul"):
-                tm = ops.tri_mul_cuda(a.view(TRI_D // G, L, L, 1), b.view(TRI_D // G, L, L, 1), float(L), direction)
-            with timed("linear_tf32"):
-                linear(tm.view(tok_pair, TRI_D), D_PAIR, False, "to" + str(direction))
-        ctx["pr_b"] = pair_bias("pr")
-
-    def seg_e():
-        ctx["row"] = attention(x_pair, L // G, ctx["pr_bias"], 1.0 / 16 ** 0.5, "pr")
-
-    def seg_f():
-        ctx["pc_b"] = pair_bias("pc")
-
-    def seg_g():
-        attention(x_pair, L // G, ctx["pc_bias"], 1.0 / 16 ** 0.5, "pc")
-        with timed("linear_tf32"):
-            linear(x_pair, 2 * D_PAIR, False, "pf1")
-            linear(x_pff, D_PAIR, False, "pf2")
-
-    def ex(fn, src, dst):
-        def step():
-            with timed("exchange"):
-                ctx[dst] = fn(ctx[src], dst)
-        return step
-
-    segments = [seg_a, seg_b, seg_c, seg_d, seg_e, seg_f, seg_g]
-    exchanges = [ex(gather_rows, "mr_b", "mr_bias"),      # pair bias of MSA row attention
-                 ex(exchange, "col", "col_t"),            # (n, l) transpose closing column attention
-                 ex(gather_rows, "right", "right_all"),   # [N*L, 16] flat = [16][L][N]
-                 ex(gather_rows, "pr_b", "pr_bias"),
-                 ex(exchange, "row", "row_t"),            # transpose closing pair row attention
-                 ex(gather_rows, "pc_b", "pc_bias")]
-
-    def block(graphs=None):
-        for i, seg in enumerate(segments):
-            if graphs is not None and graphs[i] is not None:
-                graphs[i].replay()
-            else:
-                seg()
-            if i < len(exchanges):
-                exchanges[i]()
+            return {"unavailable": f"{G} ranks do not divide the block's partitions"}
+    inputs, weights = make_inputs_and_weights(torch, ops, dev)
+    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev)
 
     def barrier():
         if G > 1:
@@ -229,30 +332,56 @@ def run(gpus, steps, warmup, use_graph=True):
         torch.cuda.synchronize()
 
     for _ in range(max(warmup, 3)):
-        block()
+        blk.run()
     code, where = ops.device_status()
     if code != 0:
         raise RuntimeError(f"device abort {code} at {where:#x}")
-    # per-op split: one eager pass sequence with events around every op class
-    timers.clear()
+
+    # ---- parity: the unsharded block on this GPU, same inputs and weights ----------------------------------------
+    n_checked, bad = 0, []
+    if check:
+        if G > 1:
+            full = Block(torch, dist, ops, inputs, weights, 1, 0, dev)
+            full.run()
+            torch.cuda.synchronize()
+            n_checked, bad = verify(torch, blk, full, G, rank)
+            del full
+        else:
+            # one rank: the sharded and the unsharded block are the same code path; check determinism of a second run
+            first = {k: v.clone() for k, v in blk.out.items()}
+            blk.run()
+            torch.cuda.synchronize()
+            n_checked = len(first)
+            bad = [k for k, v in first.items() if not torch.equal(v, blk.out[k])]
+            del first
+        flag = torch.tensor([len(bad)], device=dev)
+        if G > 1:
+            dist.all_reduce(flag)
+        n_bad_all = int(flag.item())
+    else:
+        n_bad_all = None
+
+    # ---- per-class split and eager time ----------------------------------------------------------------------------
+    blk.timers.clear()
     barrier()
     for _ in range(steps):
-        block()
+        blk.run()
     barrier()
-    split = {k: sum(a.elapsed_time(b) for a, b in v) / steps for k, v in timers.items()}
+    split = {k: sum(a.elapsed_time(b) for a, b in v) / steps for k, v in blk.timers.items()}
+    blk.timers.clear()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blk.capturing = True                     # no per-op events from here on
+    barrier()
     e0.record()
     for _ in range(steps):
-        block()
+        blk.run()
     e1.record()
     barrier()
     eager_ms = e0.elapsed_time(e1) / steps
-    # the whole block as one CUDA graph (kernels and collectives): with eight ranks the kernels are short enough that
-    # launching them one by one from the host is what takes the time
     graph_ms, graph_note = None, ""
     if use_graph:
         graphs = []
-        state["capturing"] = True
+        segments, _ = blk.plan()
         for seg in segments:                 # no collective is ever captured; a segment that cannot be captured stays eager
             try:
                 gr = torch.cuda.CUDAGraph()
@@ -262,35 +391,46 @@ def run(gpus, steps, warmup, use_graph=True):
             except Exception as exc:
                 graphs.append(None)
                 graph_note = f"a segment stayed eager: {type(exc).__name__}"
-        state["capturing"] = False
         for _ in range(2):
-            block(graphs)
+            blk.run(graphs)
         barrier()
         e0.record()
         for _ in range(steps):
-            block(graphs)
+            blk.run(graphs)
         e1.record()
         barrier()
         graph_ms = e0.elapsed_time(e1) / steps
         code, where = ops.device_status()
         if code != 0:
             raise RuntimeError(f"device abort {code} at {where:#x}")
+    blk.capturing = False
     best = graph_ms if graph_ms is not None else eager_ms
     ms = torch.tensor([best, eager_ms], device=dev, dtype=torch.float64)
     if G > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        print(json.dumps({"metric": "main IterBlock hot-path ops, ms per block", "value": float(ms[0].item()), "unit": "ms",
-                          "launch": ("cuda graphs for the compute segments, collectives from the host" + (" (" + graph_note + ")" if graph_note else ""))
-                                    if graph_ms is not None else "eager",
-                          "eager_ms": float(ms[1].item()),
-                          "n_gpus": G, "steps": steps, "warmup": max(warmup, 3), "higher_is_better": False,
-                          "scaling": "strong", "dtype": "q8 + tf32, fp32 accumulate", "data": "synthetic",
-                          "config": {"workload": "one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads",
-                                     "blocks_per_structure": 32},
-                          "ms_per_32_blocks": float(ms[0].item()) * 32,
-                          "split_ms_rank0": {k: round(v, 4) for k, v in sorted(split.items())}}), flush=True)
-    if G > 1:
+    total_split = sum(split.values()) or 1.0
+    return {"metric": "main IterBlock hot-path ops, ms per block", "ms_per_block": float(ms[0].item()), "unit": "ms",
+            "ms_per_32_blocks": float(ms[0].item()) * 32, "eager_ms": float(ms[1].item()), "n_gpus": G, "steps": steps,
+            "scaling": "strong", "higher_is_better": False, "dtype": "q8 + tf32, fp32 accumulate", "data": "synthetic, seed 5",
+            "launch": ("cuda graphs for the compute segments, collectives from the host" + (" (" + graph_note + ")" if graph_note else ""))
+                      if graph_ms is not None else "eager",
+            "workload": "one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads; 26 Q8 Linears, 18 fp32 Linears, "
+                        "4 attention calls, 2 tri_mul, 1 outer-product-mean",
+            "split_ms_rank0": {k: round(v, 4) for k, v in sorted(split.items())},
+            "exchange_share": round(split.get("exchange", 0.0) / total_split, 4),
+            "exchange_bytes_per_rank": exchange_bytes(G),
+            "parity": {"ops_checked": n_checked, "mismatching_over_ranks": n_bad_all, "mismatching_here": bad,
+                       "against": "the unsharded block on the same GPU, same inputs and weights, bit for bit" if G > 1
+                                  else "a second run of the same block (one rank: sharded and unsharded coincide), bit for bit"}}
+
+
+def run(gpus, steps, warmup, use_graph=True):
+    import torch.distributed as dist
+    rec = measure(steps, warmup, use_graph)
+    if int(os.environ.get("RANK", "0")) == 0:
+        rec["value"] = rec.get("ms_per_block")
+        print(json.dumps(rec), flush=True)
+    if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
 

@@ -102,7 +102,8 @@ def test_tensor_core_launchers(fh, oracle):
     assert fh.fh_mul_mat_mma_tf32_smem(p(A), p(B), p(Cd), 408, 256, 256) == 0
     assert cases.rel_err(host(Cd), oracle.mul_mat_f32(a, b)) <= TOL_TF32
     a33, b33, _ = cases.mul_mat_case(255, 33, 32, seed=1, bias=False)          # row pitch not a multiple of 16 bytes
-    assert fh.fh_mul_mat_mma_tf32_smem(p(dev(a33)), p(dev(b33)), p(Cd), 255, 33, 32) == 1      # caller falls back
+    A33, B33 = dev(a33), dev(b33)
+    assert fh.fh_mul_mat_mma_tf32_smem(p(A33), p(B33), p(Cd), 255, 33, 32) == 1      # caller falls back
     a16, b16 = A.half(), B.half()
     ref16 = oracle.mul_mat_16(host(a16.view(torch.int16)).view(np.uint16), host(b16.view(torch.int16)).view(np.uint16), None)
     for which in (0, 1, 2):
@@ -123,19 +124,21 @@ def test_q8_forwarders(fh, oracle, with_bias, monkeypatch):
     path = C.c_int(-1)
     torch.cuda.synchronize()
     Bd = None if bias is None else dev(bias)
-    assert fh.fh_mul_mat_q8_cuda(p(dev(W)), p(dev(x)), p(Cd), Mout, Ntok, K, 2, 1, p(Bd), C.byref(path)) == 0
+    Wd, Xd = dev(W), dev(x)                     # keep every device buffer alive until the results have been read
+    assert fh.fh_mul_mat_q8_cuda(p(Wd), p(Xd), p(Cd), Mout, Ntok, K, 2, 1, p(Bd), C.byref(path)) == 0
     assert path.value == 1                                                    # tensor cores
     assert cases.rel_err(host(Cd), oracle.mul_mat_q8(W, x, Mout, bias=bias)) <= TOL_FP32
     # the quantize / dequantize helpers
     q81 = torch.zeros(x.size // 32 * 36, dtype=torch.uint8, device="cuda")
-    assert fh.fh_quantize_rows_q8_1(p(dev(x)), p(q81), x.size) == 0
+    assert fh.fh_quantize_rows_q8_1(p(Xd), p(q81), x.size) == 0
     assert np.array_equal(host(q81), oracle.quantize_q8_1(x))
     y = torch.zeros(x.size, device="cuda")
     assert fh.fh_dequantize_q8(1, p(q81), p(y), x.size) == 0
     assert np.array_equal(host(y), oracle.dequantize(oracle.quantize_q8_1(x), 1))
     q80 = oracle.quantize_q8_0(w)
     yw = torch.zeros(w.size, device="cuda")
-    assert fh.fh_dequantize_q8(0, p(dev(q80)), p(yw), w.size) == 0
+    Q80d = dev(q80)
+    assert fh.fh_dequantize_q8(0, p(Q80d), p(yw), w.size) == 0
     assert np.array_equal(host(yw), oracle.dequantize(q80, 0))
 
 
@@ -150,7 +153,8 @@ def test_flash_attn_forwarder_takes_the_reference_struct(fh, oracle, math_mode, 
     LSE = torch.zeros((B, h, L), device="cuda")
     scale, eps = 0.21, 1e-6                     # not the defaults: both must reach the kernel
     torch.cuda.synchronize()
-    rc = fh.fh_flash_attn_forward(B, h, L, d, int(causal), scale, eps, p(dev(Q)), p(dev(K)), p(dev(V)), p(dev(bi)), p(O), p(LSE))
+    Qd, Kd, Vd, Bd = dev(Q), dev(K), dev(V), dev(bi)
+    rc = fh.fh_flash_attn_forward(B, h, L, d, int(causal), scale, eps, p(Qd), p(Kd), p(Vd), p(Bd), p(O), p(LSE))
     assert rc == 0
     rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, causal=causal, eps=eps)
     assert cases.rel_err(host(O), rO) <= tol
@@ -167,20 +171,23 @@ def test_batched_forwarders(fh, oracle, math_mode, mode, tol):
     ne1 = (C.c_int64 * 4)(48, 40, 3, 2)
     ne = (C.c_int64 * 4)(64, 48, 3, 2)
     torch.cuda.synchronize()
-    fh.fh_out_prod(p(dev(s0)), p(dev(s1)), p(dst), ne0, ne1, ne)
+    S0, S1 = dev(s0), dev(s1)
+    fh.fh_out_prod(p(S0), p(S1), p(dst), ne0, ne1, ne)
     assert cases.rel_err(host(dst), oracle.out_prod(s0, s1)) <= tol
     # tri_mul, both directions
     for outgoing in (True, False):
         l, r = cases.tri_case(6, 128, 128, 128, outgoing=outgoing)
         dst = torch.zeros((6, 128, 128, 1), device="cuda")
         torch.cuda.synchronize()
-        fh.fh_tri_mul(p(dev(l)), p(dev(r)), p(dst), 6, 128, 128, 128, 1, 1.0 / 128, int(outgoing))
+        Ld, Rd = dev(l), dev(r)
+        fh.fh_tri_mul(p(Ld), p(Rd), p(dst), 6, 128, 128, 128, 1, 1.0 / 128, int(outgoing))
         assert cases.rel_err(host(dst), oracle.tri_mul(l, r, 128.0, outgoing)) <= tol
     # outer_prod_mean
     l, r = cases.opm_case(8, 64, 128)
     dst = torch.zeros((64, 64, 64, 1), device="cuda")
     torch.cuda.synchronize()
-    fh.fh_outer_prod_mean(p(dev(l)), p(dev(r)), p(dst), 8, 64, 128, 1, 1.0 / 128)
+    Ld, Rd = dev(l), dev(r)
+    fh.fh_outer_prod_mean(p(Ld), p(Rd), p(dst), 8, 64, 128, 1, 1.0 / 128)
     assert cases.rel_err(host(dst), oracle.outer_prod_mean(l, r)) <= tol
 
 
