@@ -57,7 +57,11 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
+#ifdef PPML_MBAR_TEST_WAIT
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+#endif
         "selp.b32 %0, 1, 0, P;\n\t}\n"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
@@ -146,6 +150,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap,
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
+
+// Tiled bulk store shared -> global (bulk async-group completion): the box at `src_smem`, laid out as the tensor map's
+// swizzle mode says, goes to coordinates (x, y, z); parts of the box outside the tensor are not written.  The writes to
+// shared memory must have been made visible to the async proxy (fence_proxy_async_smem) before the issuing thread runs this.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src_smem, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until the bulk stores committed by this thread have finished reading shared memory (the buffers may be reused)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// waits until the bulk stores committed by this thread are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), completion counted in
 // bytes on the mbarrier.
@@ -266,6 +283,23 @@ __device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
     return v;
+}
+// the same with a compile-time byte offset folded into the instruction (no address arithmetic)
+template <int OFF>
+__device__ __forceinline__ float4 lds_f4_at(uint32_t saddr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint16_t lds_u16_at(uint32_t saddr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(saddr), "n"(OFF));
+    return v;
+}
+// mbarrier arrive by the lane whose `lane` is 0, as one predicated instruction (no divergent region)
+__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, uint32_t lane) {
+    asm volatile("{\n\t.reg .pred P;\n\tsetp.eq.u32 P, %1, 0;\n\t@P mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}\n" ::"r"(bar), "r"(lane) : "memory");
 }
 __device__ __forceinline__ uint16_t lds_u16(uint32_t saddr) {
     uint16_t v;

@@ -16,6 +16,8 @@
 // per thread), warps 4-19 = epilogue (four warps per TMEM lane quarter, 32 columns each).
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "kernels.h"
 #include "tma_host.h"
 
@@ -72,10 +74,11 @@ __host__ __device__ inline SmemLayout q8_layout(int AR, int nblk, int RS, int BS
     L.a_off = 0;
     L.raw_off = L.a_off + AR * kTile;
     L.w_off = L.raw_off + RS * kTile;
-    L.c_off = L.w_off + BS * kTile;                  // 4 KB of the byte 0x80: both operands of the offset MMA
-    L.dw_off = L.c_off + 4096;                       // float [dw_tabs][nblk][128]
+    L.c_off = L.w_off + BS * kTile;                  // 128 bytes of 0x80: one core matrix, both operands of the offset MMA
+    L.dw_off = L.c_off + 128;                        // float [dw_tabs][nblk][128]
     L.da_off = L.dw_off + dw_tabs * nblk * 128 * 4;  // half  [2][nblk][128]
     L.st_off = L.da_off + 2 * nblk * 128 * 2;        // staged stores: kEpiWarps x kStoreBytes
+    L.st_off = (L.st_off + 1023u) & ~1023u;          // the 64-byte swizzle pattern of the store buffers repeats every 512 bytes
     L.bar_off = L.st_off + (staged ? kEpiWarps * kStoreBytes : 0);
     L.bar_off = (L.bar_off + 15u) & ~15u;
     L.total = L.bar_off + 8 * kNumBarriers + 16;
@@ -257,10 +260,15 @@ quantize_q8_planar_kernel(const float* __restrict__ X, int8_t* __restrict__ Aq, 
 
 template <bool SUMI, int QW>      // SUMI: also write the raw int32 block sums (tests); QW: quantizer warps
 __global__ void __launch_bounds__(Roles<QW>::kThreads, 1)
-umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Q8Params p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* sg = smem_raw + (smem_base - smem_u32(smem_raw));
+umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+               const __grid_constant__ CUtensorMap tmC, const Q8Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = smem_u32(smem_raw);
+    uint8_t* sg = smem_raw;
+    if ((smem_base & 1023u) != 0u) {             // the swizzled tiles need a 1024-byte aligned base: refuse to run otherwise
+        if (threadIdx.x == 0) { p.err[0] = ST_DEVICE_ABORT; p.err[1] = 0x1001; }
+        return;
+    }
     const SmemLayout L = q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged);
     const uint32_t bar0 = smem_base + L.bar_off;
     auto raw_full = [&](int s) { return bar0 + 8u * s; };
@@ -304,7 +312,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
     if (warp == kMmaWarp) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
     if (warp == kTmaWarp && lane == 0) { prefetch_tmap(&tmX); prefetch_tmap(&tmW); }
-    for (int i = threadIdx.x; i < 1024; i += kThreads) reinterpret_cast<uint32_t*>(sg + L.c_off)[i] = 0x80808080u;
+    if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(sg + L.c_off)[threadIdx.x] = 0x80808080u;
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -411,11 +419,12 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const uint32_t idesc = make_idesc(2, 1, 1, 0, 0, 128, 128);
             const uint64_t da0 = make_smem_desc(smem_base + L.a_off, 16, 1024, kLayoutSW128);
             const uint64_t db0 = make_smem_desc(smem_base + L.w_off, 16, 1024, kLayoutSW128);
-            // Offset operands: every element is the unsigned byte 128, in the unswizzled K-major layout (8 x 16 byte
-            // core matrices 128 bytes apart along K, 256 bytes apart along the rows), so a second instruction adds
-            // 32 * 128 * 128 = 2^19 to every block sum: the sums read back by the epilogue are never negative.
+            // Offset operands: every element is the unsigned byte 128, in the unswizzled K-major layout.  All core
+            // matrices (8 rows x 16 bytes) are equal, so both strides of the descriptor are zero and one 128-byte core
+            // matrix stands for the whole 128 x 32 operand.  The second instruction adds 32 * 128 * 128 = 2^19 to every
+            // block sum: the sums read back by the epilogue are never negative.
             const uint32_t idesc_off = make_idesc(2, 0, 0, 0, 0, 128, 128);
-            const uint64_t dc = make_smem_desc(smem_base + L.c_off, 128, 256, 0);
+            const uint64_t dc = make_smem_desc(smem_base + L.c_off, 0, 0, 0);
             uint32_t bcnt = 0, n_it = 0, w_ph = 0; int w_s = 0; bool ok = true;
             uint32_t a_slot0 = 0, a_par0 = 0;           // slot and parity of K step 0 of the current item
             int mt = 0, nb0 = 0, nb1 = 0;
@@ -610,9 +619,84 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     rescale(vb, 1, kb, da, dc);
                     return true;
                 };
-                if ((p.nblk & 3) == 0) {
-                    // groups of four blocks on slots 0..3, handed over in pairs; slot numbers and TMEM offsets are
-                    // compile-time constants
+                if (!SUMI && (p.nblk & 3) == 0) {
+                    // Fast path (every K that is a multiple of 128): groups of four blocks on slots 0..3, handed over in
+                    // pairs.  Slot numbers, TMEM offsets and table offsets are compile-time constants; the two table
+                    // pointers advance once per group.  Per block: the two 16-column halves are software-pipelined (the
+                    // TMEM load of the next half is in flight during the arithmetic of this one).
+                    auto half16 = [&](const uint32_t (&v)[16], auto off, float da, float dc, uint32_t dwp, int h) {
+                        constexpr int OFF = decltype(off)::value;
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4) {
+                            float4 w4;
+                            if (j4 == 0) w4 = lds_f4_at<OFF>(dwp);
+                            else if (j4 == 1) w4 = lds_f4_at<OFF + 16>(dwp);
+                            else if (j4 == 2) w4 = lds_f4_at<OFF + 32>(dwp);
+                            else w4 = lds_f4_at<OFF + 48>(dwp);
+                            acc[h * 16 + j4 * 4 + 0] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 0]), da, dc), w4.x, acc[h * 16 + j4 * 4 + 0]);
+                            acc[h * 16 + j4 * 4 + 1] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 1]), da, dc), w4.y, acc[h * 16 + j4 * 4 + 1]);
+                            acc[h * 16 + j4 * 4 + 2] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 2]), da, dc), w4.z, acc[h * 16 + j4 * 4 + 2]);
+                            acc[h * 16 + j4 * 4 + 3] = fmaf(fmaf(__uint_as_float(v[j4 * 4 + 3]), da, dc), w4.w, acc[h * 16 + j4 * 4 + 3]);
+                        }
+                    };
+                    using std::integral_constant;
+                    const uint32_t tf0 = t_full(0), tf2 = t_full(2), te0 = t_empty(0), te2 = t_empty(2);
+                    const float kDc = __uint_as_float(0x80080000u);           // -2^-130: times d_a * 2^100 gives -2^-30 * d_a
+                    uint32_t par = (bcnt >> 2) & 1u;
+                    uint32_t dwp = dw_a0, dap = da_a0;
+                    const int ngroups = p.nblk >> 2;
+                    for (int g4 = 0; g4 < ngroups; ++g4, dwp += 2048u, dap += 1024u, par ^= 1u) {
+                        float da, dc;
+                        // ---- block 0 (slot 0); block 1 is in the same pair: its sums and its scale are complete
+                        da = __half2float(__ushort_as_half(da_raw)) * kTwo100; dc = da * kDc;
+                        tmem_ld_wait();
+                        tmem_ld16(taddr0 + 16u, vb);
+                        da_raw = lds_u16_at<256>(dap);
+                        half16(va, integral_constant<int, 0>{}, da, dc, dwp, 0);
+                        tmem_ld_wait();
+                        tmem_ld16(taddr0 + 128u, va);
+                        half16(vb, integral_constant<int, 64>{}, da, dc, dwp, 1);
+                        // ---- block 1 (slot 1): releases slots 0-1, then needs the pair 2-3
+                        da = __half2float(__ushort_as_half(da_raw)) * kTwo100; dc = da * kDc;
+                        tmem_ld_wait();
+                        tmem_ld16(taddr0 + 128u + 16u, vb);
+                        half16(va, integral_constant<int, 512>{}, da, dc, dwp, 0);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        mbar_arrive_lane0(te0, lane);
+                        if (!mbar_wait(tf2, par, cta_abort, p.err, 0x1401)) { ok = false; break; }
+                        tc_fence_after();
+                        da_raw = lds_u16_at<512>(dap);
+                        tmem_ld16(taddr0 + 256u, va);
+                        half16(vb, integral_constant<int, 512 + 64>{}, da, dc, dwp, 1);
+                        // ---- block 2 (slot 2)
+                        da = __half2float(__ushort_as_half(da_raw)) * kTwo100; dc = da * kDc;
+                        tmem_ld_wait();
+                        tmem_ld16(taddr0 + 256u + 16u, vb);
+                        da_raw = lds_u16_at<768>(dap);
+                        half16(va, integral_constant<int, 1024>{}, da, dc, dwp, 0);
+                        tmem_ld_wait();
+                        tmem_ld16(taddr0 + 384u, va);
+                        half16(vb, integral_constant<int, 1024 + 64>{}, da, dc, dwp, 1);
+                        // ---- block 3 (slot 3): releases slots 2-3; the next group starts on the pair 0-1
+                        da = __half2float(__ushort_as_half(da_raw)) * kTwo100; dc = da * kDc;
+                        tmem_ld_wait();
+                        tmem_ld16(taddr0 + 384u + 16u, vb);
+                        half16(va, integral_constant<int, 1536>{}, da, dc, dwp, 0);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        mbar_arrive_lane0(te2, lane);
+                        if (g4 + 1 < ngroups) {
+                            if (!mbar_wait(tf0, par ^ 1u, cta_abort, p.err, 0x1401)) { ok = false; break; }
+                            tc_fence_after();
+                            da_raw = lds_u16_at<1024>(dap);
+                            tmem_ld16(taddr0, va);
+                        }
+                        half16(vb, integral_constant<int, 1536 + 64>{}, da, dc, dwp, 1);
+                    }
+                    bcnt += static_cast<uint32_t>(p.nblk);
+                } else if ((p.nblk & 3) == 0) {
+                    // the same schedule with run-time slot numbers (the instance that also writes the int32 sums)
                     for (int kb0 = 0; kb0 < p.nblk && ok; kb0 += 4, bcnt += 4) {
                         const uint32_t par = (bcnt >> 2) & 1u;
                         const bool more = kb0 + 4 < p.nblk;
@@ -635,28 +719,26 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
                 }
                 if (p.c_trans && p.staged) {
-                    // row-contiguous stores, 16 columns at a time: thread = row writes four 16-byte chunks into the
-                    // warp's buffer (chunk index XOR (row / 2) % 4 keeps the banks apart), then four lanes cover
-                    // one 64-byte row segment, eight rows per store instruction
-                    uint8_t* stage = sg + L.st_off + (warp - kFirstEpiWarp) * kStoreBytes;
-                    const int cc = lane & 3;
+                    // Asynchronous stores, 16 columns at a time: thread = row writes four 16-byte chunks into the warp's
+                    // 2 KB buffer in the 64-byte swizzle (chunk index XOR (row / 2) % 4: no bank conflicts), then one lane
+                    // hands the 32 x 16 box to the TMA unit, which writes it out while the warp goes on with the next
+                    // blocks; rows past Ntok and columns past Mout are clipped by the tensor map.  A buffer is reused
+                    // once the store before it has finished reading shared memory.
+                    const uint32_t stage = smem_base + L.st_off + (warp - kFirstEpiWarp) * kStoreBytes;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
+                        if (lane == 0) bulk_wait_read_all();
+                        __syncwarp();
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<float4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                                make_float4(acc[16 * h + 4 * j], acc[16 * h + 4 * j + 1], acc[16 * h + 4 * j + 2], acc[16 * h + 4 * j + 3]);
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)),
+                                         "f"(acc[16 * h + 4 * j]), "f"(acc[16 * h + 4 * j + 1]), "f"(acc[16 * h + 4 * j + 2]), "f"(acc[16 * h + 4 * j + 3]) : "memory");
+                        fence_proxy_async_smem();
                         __syncwarp();
-                        const int col = mo0 + 16 * h + cc * 4;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int rr = (lane >> 2) + 8 * i;
-                            const int trow = mt * 128 + q * 32 + rr;
-                            const float4 val = *reinterpret_cast<const float4*>(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) << 4));
-                            if (trow < p.Ntok && col < p.Mout)      // staged mode requires Mout % 4 == 0
-                                *reinterpret_cast<float4*>(p.C + static_cast<size_t>(trow) * p.Mout + col) = val;
+                        if (lane == 0) {
+                            tma_store_3d(&tmC, stage, mo0 + 16 * h, mt * 128 + q * 32, 0);
+                            bulk_commit_group();
                         }
-                        __syncwarp();
                     }
                 } else if (tok < p.Ntok) {
                     if (p.c_trans) {
@@ -679,6 +761,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             __syncwarp();
             if (lane == 0) mbar_arrive(epi_done(n_it & 1u));
         }
+        if (lane == 0) bulk_wait_all();              // this warp's result stores are complete before the CTA leaves
     }
 
     tc_fence_before();
@@ -725,7 +808,7 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     // preference, a second A tile (the next item is quantized while this one multiplies), the scale tables
     // of all column blocks (no refill, at most 32 KB), the per-warp store buffers; what is left goes to the
     // two rings, and an option is dropped when fewer than five stages would remain.
-    const int budget = 226 * 1024;
+    const int budget = 227 * 1024;               // the most dynamic shared memory one CTA can have
     const int total_items = p.m_tiles * p.groups;
     // more token tiles than SMs and enough work per token tile (column blocks x K steps; measured break-even at 8) that
     // quantizing the cut tiles twice pays off: cut the work into equal contiguous ranges instead
@@ -737,7 +820,7 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     p.dw_tabs = (p.n_blocks * p.nblk * 512 <= 32 * 1024) ? p.n_blocks : 1;
     p.staged = p.vec_ok ? 1 : 0;
     auto stages_for = [&]() {
-        return (budget - (static_cast<int>(q8_layout(p.AR, p.nblk, 0, 0, p.dw_tabs, p.staged).total) + 1024)) / kTile;
+        return (budget - static_cast<int>(q8_layout(p.AR, p.nblk, 0, 0, p.dw_tabs, p.staged).total)) / kTile;
     };
     if (stages_for() < 5 && p.dw_tabs > 1) p.dw_tabs = 1;
     if (stages_for() < 5 && abuf > 1) { abuf = 1; p.AR = p.KT; }
@@ -759,7 +842,7 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     const __half* Wd = reinterpret_cast<const __half*>(static_cast<const int8_t*>(W) + static_cast<size_t>(M) * p.nblk * 32);
     p.Wd = Wd; p.C = C; p.bias = bias; p.sumi_out = sumi_out; p.c_trans = c_trans; p.err = err;
 
-    CUtensorMap tmX, tmW;
+    CUtensorMap tmX, tmW, tmC;
     if (p.preq) {
         if (reinterpret_cast<uintptr_t>(scratch) & 255u) return ST_BAD_ARGS;
         int8_t* aq = static_cast<int8_t*>(scratch);
@@ -774,8 +857,10 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     } else
     if (!make_tmap_3d(&tmX, TmaType::F32, X, K, N, 1, static_cast<uint64_t>(K) * 4, 0, 32, 128, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
+    tmC = tmW;                                   // only read by the kernel when the results leave through TMA stores
+    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, 16, 32, 3)) p.staged = 0;
 
-    const int smem = static_cast<int>(q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total) + 1024;
+    const int smem = static_cast<int>(q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total);
     static int configured_smem[64] = {0};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured_smem[dev] < smem) {
@@ -788,9 +873,9 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
         configured_smem[dev] = 227 * 1024;
     }
     const int grid = total_items < sms ? total_items : sms;
-    if (sumi_out != nullptr) umma_q8_kernel<true, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, p);
-    else if (p.blocks_per_group == 1) umma_q8_kernel<false, 4><<<grid, Roles<4>::kThreads, smem, st>>>(tmX, tmW, p);
-    else umma_q8_kernel<false, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, p);
+    if (sumi_out != nullptr) umma_q8_kernel<true, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
+    else if (p.blocks_per_group == 1) umma_q8_kernel<false, 4><<<grid, Roles<4>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
+    else umma_q8_kernel<false, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
