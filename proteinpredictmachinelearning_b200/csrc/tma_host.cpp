@@ -48,7 +48,7 @@ bool make_tmap_3d(CUtensorMap* out, TmaType type, const void* base, uint64_t d0,
     cuuint32_t box[3] = {box0, box1, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(out, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_64B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                    swizzle == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_64B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                             : (swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE),
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;

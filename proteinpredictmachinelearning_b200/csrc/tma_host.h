@@ -13,7 +13,8 @@ enum class TmaType { F32, TF32, F16, BF16, U8 };
 // of d1 and d2 and must be multiples of 16; base must be 16-byte aligned.  The box is
 // box0 x box1 x 1.  swizzle: 0 none, 1 the 128-byte swizzle (16-byte chunks; box0 * element size == 128),
 // 2 the 128-byte swizzle with 32-byte chunks (the only layout the tensor core reads 32-bit operands from
-// when their row index, not K, is contiguous), 3 the 64-byte swizzle (box0 * element size == 64).
+// when their row index, not K, is contiguous), 3 the 64-byte swizzle (box0 * element size == 64), 4 the 32-byte swizzle
+// (box0 * element size == 32).
 // Out-of-range elements read as zero.  Returns false when the driver rejects the arguments.
 bool make_tmap_3d(CUtensorMap* out, TmaType type, const void* base,
                   uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,

@@ -49,7 +49,8 @@ struct Q8Params {
     int AR;                    // 16 KB slots of quantized A, used as a ring over (item, K step): KT = resident, 2 KT = resident
                                // and double-buffered across items, 3 = a short ring (items with a single column block)
     int dw_tabs;               // scale tables held in smem: n_blocks (all resident, filled once) or 1 (refilled per column block)
-    int staged;                // 1: results leave through per-warp transposition buffers (row-contiguous stores)
+    int staged;                // columns of the per-warp store buffer (32 rows x staged fp32: 8, 16 or 32; the results leave
+                               // through TMA stores), 0: plain stores from registers
     int preq;                  // 1: the activations were quantized by a kernel of their own: int8 tiles and scale tables
                                //    come in by TMA, the quantizer warps idle (tmX then maps the int8 matrix)
     const __half* da_t;        // preq: activation scales [token tile][nblk][128]
@@ -66,7 +67,6 @@ struct SmemLayout {
     uint32_t a_off, raw_off, w_off, c_off, dw_off, da_off, st_off, bar_off, total;
 };
 
-constexpr int kStoreBytes = 32 * 64;                // one epilogue warp's 32 rows x 16 columns transposition buffer
 constexpr int kNumBarriers = 4 * kMaxStages + 4 * kMaxKT + 8 + 4;
 
 __host__ __device__ inline SmemLayout q8_layout(int AR, int nblk, int RS, int BS, int dw_tabs, int staged) {
@@ -77,9 +77,9 @@ __host__ __device__ inline SmemLayout q8_layout(int AR, int nblk, int RS, int BS
     L.c_off = L.w_off + BS * kTile;                  // 128 bytes of 0x80: one core matrix, both operands of the offset MMA
     L.dw_off = L.c_off + 128;                        // float [dw_tabs][nblk][128]
     L.da_off = L.dw_off + dw_tabs * nblk * 128 * 4;  // half  [2][nblk][128]
-    L.st_off = L.da_off + 2 * nblk * 128 * 2;        // staged stores: kEpiWarps x kStoreBytes
-    L.st_off = (L.st_off + 1023u) & ~1023u;          // the 64-byte swizzle pattern of the store buffers repeats every 512 bytes
-    L.bar_off = L.st_off + (staged ? kEpiWarps * kStoreBytes : 0);
+    L.st_off = L.da_off + 2 * nblk * 128 * 2;        // store buffers: kEpiWarps x (32 rows x staged columns) fp32
+    L.st_off = (L.st_off + 1023u) & ~1023u;          // the swizzle patterns of the store buffers repeat every 256 to 1024 bytes
+    L.bar_off = L.st_off + kEpiWarps * 32 * staged * 4;
     L.bar_off = (L.bar_off + 15u) & ~15u;
     L.total = L.bar_off + 8 * kNumBarriers + 16;
     return L;
@@ -719,27 +719,36 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
                 }
                 if (p.c_trans && p.staged) {
-                    // Asynchronous stores, 16 columns at a time: thread = row writes four 16-byte chunks into the warp's
-                    // 2 KB buffer in the 64-byte swizzle (chunk index XOR (row / 2) % 4: no bank conflicts), then one lane
-                    // hands the 32 x 16 box to the TMA unit, which writes it out while the warp goes on with the next
-                    // blocks; rows past Ntok and columns past Mout are clipped by the tensor map.  A buffer is reused
-                    // once the store before it has finished reading shared memory.
-                    const uint32_t stage = smem_base + L.st_off + (warp - kFirstEpiWarp) * kStoreBytes;
+                    // Asynchronous stores, `staged` columns at a time: thread = row writes its 16-byte chunks into the warp's
+                    // buffer (rows of 32, 64 or 128 bytes in the TMA swizzle of that width: address bits 4.. XOR address bits
+                    // 7.., which also keeps the banks apart), then one lane hands the 32-row box to the TMA unit, which writes
+                    // it out while the warp goes on with the next blocks; rows past Ntok and columns past Mout are clipped by
+                    // the tensor map.  The buffer is reused once the store before it has finished reading shared memory.
+                    auto store_cols = [&](auto sc_c) {
+                        constexpr int SC = decltype(sc_c)::value, PITCH = SC * 4, NCH = SC / 4;
+                        const uint32_t stage = smem_base + L.st_off + (warp - kFirstEpiWarp) * (32 * PITCH);
+                        const uint32_t row_off = lane * PITCH;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        if (lane == 0) bulk_wait_read_all();
-                        __syncwarp();
+                        for (int c0 = 0; c0 < 32; c0 += SC) {
+                            if (lane == 0) bulk_wait_read_all();
+                            __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)),
-                                         "f"(acc[16 * h + 4 * j]), "f"(acc[16 * h + 4 * j + 1]), "f"(acc[16 * h + 4 * j + 2]), "f"(acc[16 * h + 4 * j + 3]) : "memory");
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tma_store_3d(&tmC, stage, mo0 + 16 * h, mt * 128 + q * 32, 0);
-                            bulk_commit_group();
+                            for (int j = 0; j < NCH; ++j) {
+                                const uint32_t off = row_off + (j << 4);
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage + (off ^ (((off >> 7) & (NCH - 1)) << 4))),
+                                             "f"(acc[c0 + 4 * j]), "f"(acc[c0 + 4 * j + 1]), "f"(acc[c0 + 4 * j + 2]), "f"(acc[c0 + 4 * j + 3]) : "memory");
+                            }
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_3d(&tmC, stage, mo0 + c0, mt * 128 + q * 32, 0);
+                                bulk_commit_group();
+                            }
                         }
-                    }
+                    };
+                    if (p.staged == 16) store_cols(std::integral_constant<int, 16>{});
+                    else if (p.staged == 8) store_cols(std::integral_constant<int, 8>{});
+                    else store_cols(std::integral_constant<int, 32>{});
                 } else if (tok < p.Ntok) {
                     if (p.c_trans) {
                         float* dst = p.C + static_cast<size_t>(tok) * p.Mout + mo0;
@@ -818,10 +827,13 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     const bool ring = p.blocks_per_group == 1 && p.KT >= 3;    // every item has one column block: A is consumed once
     p.AR = ring ? (p.preq ? 4 : 3) : p.KT * abuf;
     p.dw_tabs = (p.n_blocks * p.nblk * 512 <= 32 * 1024) ? p.n_blocks : 1;
-    p.staged = p.vec_ok ? 1 : 0;
+    p.staged = p.vec_ok ? 16 : 0;
     auto stages_for = [&]() {
         return (budget - static_cast<int>(q8_layout(p.AR, p.nblk, 0, 0, p.dw_tabs, p.staged).total)) / kTile;
     };
+    // what is given up, in this order, while fewer than five ring stages would remain (four for the store buffers):
+    // the resident scale tables, the second A tile, the store buffers.  (At K = 1024 the resident A tile leaves no room
+    // for them: narrower buffers paid for with a raw stage were measured slower, 370 against 334 us at 65536 x 1024 x 512.)
     if (stages_for() < 5 && p.dw_tabs > 1) p.dw_tabs = 1;
     if (stages_for() < 5 && abuf > 1) { abuf = 1; p.AR = p.KT; }
     if (stages_for() < 4) p.staged = 0;
@@ -858,7 +870,9 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     if (!make_tmap_3d(&tmX, TmaType::F32, X, K, N, 1, static_cast<uint64_t>(K) * 4, 0, 32, 128, 1)) return ST_UNSUPPORTED_PATH;
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
     tmC = tmW;                                   // only read by the kernel when the results leave through TMA stores
-    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, 16, 32, 3)) p.staged = 0;
+    // box = staged columns x 32 rows; swizzle of the box width (32, 64 or 128 bytes)
+    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, p.staged, 32,
+                                  p.staged == 32 ? 1 : (p.staged == 16 ? 3 : 4))) p.staged = 0;
 
     const int smem = static_cast<int>(q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total);
     static int configured_smem[64] = {0};
