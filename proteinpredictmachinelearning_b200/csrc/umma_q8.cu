@@ -544,11 +544,21 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 // wait until every epilogue warp has finished with the previous one, fill, publish.
                 const uint32_t dw_a0 = smem_base + L.dw_off + ((p.dw_tabs > 1 ? nb : 0) * p.nblk * 128 + cg * 32) * 4;
                 if (!dw_resident) {
+                    // this thread's share of the table (column etid % 128, every fourth block): the global loads are
+                    // issued before the wait for the other warps, so their latency hides behind it
+                    float wv[kMaxKT];
+                    {
+                        const int col = etid & 127, mo = nb * 128 + col;
+                        const __half* src = p.Wd + static_cast<size_t>(mo) * p.nblk + (etid >> 7);
+#pragma unroll
+                        for (int t = 0; t < kMaxKT; ++t)
+                            wv[t] = (mo < p.Mout && 4 * t + (etid >> 7) < p.nblk) ? __half2float(src[4 * t]) * kTwo49 : 0.0f;
+                    }
                     if (!mbar_wait(dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
-                    for (int i = etid; i < p.nblk * 128; i += 32 * kEpiWarps) {
-                        const int kb = i >> 7, col = i & 127;
-                        const int mo = nb * 128 + col;
-                        dw_s[i] = (mo < p.Mout) ? __half2float(p.Wd[static_cast<size_t>(mo) * p.nblk + kb]) * kTwo49 : 0.0f;
+#pragma unroll
+                    for (int t = 0; t < kMaxKT; ++t) {
+                        const int i = etid + t * (32 * kEpiWarps);
+                        if (i < p.nblk * 128) dw_s[i] = wv[t];
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(dw_full);
@@ -888,7 +898,11 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     }
     const int grid = total_items < sms ? total_items : sms;
     if (sumi_out != nullptr) umma_q8_kernel<true, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
-    else if (p.blocks_per_group == 1) umma_q8_kernel<false, 4><<<grid, Roles<4>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
+    // four quantizer warps where the quantizer sets the pace: items with one column block, and K = 1024 with up to four
+    // (the A tile is not double-buffered there, so every item starts by waiting for its first blocks; measured 177 against
+    // 194 us at 65536 x 1024 x 256, 317 against 324 at N = 512, but 584 against 547 at N = 1024)
+    else if (p.blocks_per_group == 1 || (!p.preq && p.KT == kMaxKT && p.blocks_per_group <= 4))
+        umma_q8_kernel<false, 4><<<grid, Roles<4>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
     else umma_q8_kernel<false, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
