@@ -54,6 +54,27 @@ int ppml_b200_device_status(int* where);
 int ppml_b200_mul_mat_f32(const float* A, const float* B, float* C, int M, int K, int N, const float* bias,
                           int path, int tf32_mode, void* stream);
 
+/* A Linear fused with its elementwise neighbours (no counterpart as one call in the reference, which runs them as
+ * separate graph nodes):
+ *   LayerNorm in front (LayerNorm::forward, src/model/Embedding.cpp:268-289 = OP_NORM, src/backend/CPUKernels.cpp:1488-1512,
+ *   then * gamma + beta): pass ln_mean_rstd [M][2] from ppml_b200_row_stats on the raw activations A, ln_u [N], the
+ *   weights Wg and the vector v (as `bias`) from ppml_b200_layernorm_fold; the result is LayerNorm(A) W^T + b without
+ *   the normalised activations ever being written:  out = rstd_m * (A Wg^T - mean_m * u) + v.
+ *   Activation gate behind (OP_ACT_MUL, src/backend/CPUKernels.cpp:1947-1967; act_mul(gate_logits, x, kind) in
+ *   src/modules/Attention.cpp:390): with `gate` [M][N] the result is act(out) * gate; with gate == NULL and act != 0
+ *   it is act(out).  act: 0 none, 1 sigmoid, 2 silu, 3 gelu (tanh form), 4 tanh, 5 relu, the reference's formulas.
+ * Both are optional and combine.  The product runs on the raw rows of A: when |mean| is much larger than the standard
+ * deviation of a row the tf32 path loses accuracy by that ratio; path = PPML_B200_PATH_SIMT is exact fp32. */
+int ppml_b200_mul_mat_f32_fused(const float* A, const float* B, float* C, int M, int K, int N, const float* bias,
+                                const float* ln_mean_rstd, const float* ln_u, const float* gate, int act,
+                                int path, int tf32_mode, void* stream);
+/* (mean, 1 / sqrt(var + eps)) of every row of x [M][K], variance as in OP_NORM (mean of squared differences). */
+int ppml_b200_row_stats(const float* x, float* mean_rstd, int64_t M, int K, float eps, void* stream);
+/* Weight-side terms, once per layer: Wg[n][k] = W[n][k] * gamma[k], u[n] = sum_k Wg[n][k], v[n] = sum_k W[n][k] * beta[k] + bias[n]
+ * (bias may be NULL). */
+int ppml_b200_layernorm_fold(const float* W, const float* gamma, const float* beta, const float* bias, float* Wg, float* u, float* v,
+                             int N, int K, void* stream);
+
 /* ---- OP_MUL_MAT, 16-bit operands, fp32 output ------------------------------------------------
  * fp16: replaces mul_mat_mma_f16_smem / mul_mat_mma_f16 / mul_mat_cuda_f16
  * (src/backend/CUDAKernels.cpp:199, :195, :182).  bf16 has no counterpart in the reference (its type
@@ -122,6 +143,29 @@ int ppml_b200_quantize_q8_0_host(const float* src, void* blocks34, int64_t n);
 int ppml_b200_repack_q8_0_host(const void* blocks34, int64_t nblocks, void* q8_0r);
 int ppml_b200_quantize_q8_0r(const float* w_dev, void* q8_0r_dev, int64_t ne, void* stream);
 int64_t ppml_b200_q8_0r_bytes(int64_t numel);
+/* repack_q8_0_host on the device: 34-byte Q8_0 blocks (device, 2-byte aligned) -> planar Q8_0R (device, 4-byte aligned). */
+int ppml_b200_repack_q8_0(const void* blocks34_dev, int64_t nblocks, void* q8_0r_dev, void* stream);
+
+/* ---- Q8_0 weights on disk --------------------------------------------------------------------
+ * No counterpart in the reference, which refuses to save quantized tensors (src/model/GGUF.cpp:204-213) and
+ * re-quantizes on the host at every start (src/model/PPML.cpp:4504-4524).  The container is the reference's
+ * GGUF dialect (magic 0x46554747, version 3, "layout_hash" metadata, absolute tensor offsets, 32-byte alignment);
+ * tensors are fp32 (type 0) or ggml Q8_0 (type 8: 34-byte blocks of half d + 32 int8), quantized with the host
+ * rule of include/ppml/QuantBlocks.h:62-79.  Shapes are rows x cols with cols innermost; Q8_0 needs cols % 32 == 0.
+ * write: 0 ok, 1 bad arguments, 2 cols not a multiple of 32, 3 cannot open, 4 write error.
+ * load: puts tensor `index` into device memory -- a Q8_0 tensor as planar Q8_0R (ppml_b200_q8_file_nbytes bytes), an
+ * fp32 tensor as it is; with scratch_dev (same size, device) the blocks are split by a kernel, without it on the host.
+ * The call returns after the copy has finished.  0 ok, 1 bad arguments, 3 pinned allocation, 4 read error, 6 copy. */
+int ppml_b200_q8_file_write(const char* path, int n_tensors, const char* const* names, const float* const* weights_host,
+                            const int64_t* rows, const int64_t* cols, const int* as_q8);
+void* ppml_b200_q8_file_open(const char* path);              /* NULL when the file is missing or malformed */
+void ppml_b200_q8_file_close(void* handle);
+int ppml_b200_q8_file_count(void* handle);
+int ppml_b200_q8_file_find(void* handle, const char* name);  /* index or -1 */
+int ppml_b200_q8_file_info(void* handle, int index, char* name, int name_cap, int64_t* rows, int64_t* cols, int* is_q8);
+int64_t ppml_b200_q8_file_nbytes(void* handle, int index);
+int ppml_b200_q8_file_layout_hash(void* handle, char* hex17); /* 0: the stored hash matches names and shapes, 2: it does not */
+int ppml_b200_q8_file_load(void* handle, int index, void* dst_dev, void* scratch_dev, void* stream);
 
 /* ---- OP_FLASH_ATTN_EXT forward ---------------------------------------------------------------
  * Replaces flash_attn_forward_cuda (src/backend/CUDAKernels.cpp:174; include/ppml/FlashAttn.h:60;

@@ -23,6 +23,7 @@
 #include "ppml/ComputeGraph.h"
 #include "ppml/Context.h"
 #include "ppml/FlashAttn.h"
+#include "ppml/GGUF.h"
 #include "ppml/QuantBlocks.h"
 
 using namespace ppml;
@@ -148,6 +149,28 @@ void ref_dequantize_q8_0(const void* src, float* dst, int64_t n) {
 }
 void ref_dequantize_q8_1(const void* src, float* dst, int64_t n) {
     dequantize_q8_1_host(static_cast<const block_q8_1*>(src), dst, n);
+}
+
+// The reference's own checkpoint reader (src/model/GGUF.cpp:314-470) on a file of fp32 tensors: builds parameter tensors
+// of the given shapes (rows x cols, cols innermost), calls load_gguf with the names (so the stored layout hash is
+// checked against names and shapes) and copies the loaded values out.  0 ok, 1 the reader threw.
+int ref_gguf_load(const char* path, int n, const char* const* names, const int64_t* rows, const int64_t* cols, float* const* out) {
+    ArenaScope scope;
+    try {
+        std::vector<TensorF32*> params;
+        std::vector<std::string> tnames;
+        std::vector<std::vector<float>> store(static_cast<size_t>(n));
+        for (int i = 0; i < n; ++i) {
+            store[i].assign(static_cast<size_t>(rows[i] * cols[i]), 0.0f);
+            params.push_back(leaf({cols[i], rows[i]}, store[i].data()));
+            tnames.push_back(names[i]);
+        }
+        load_gguf(path, params, tnames);
+        for (int i = 0; i < n; ++i) std::memcpy(out[i], store[i].data(), store[i].size() * sizeof(float));
+        return 0;
+    } catch (const std::exception&) {
+        return 1;
+    }
 }
 
 }  // extern "C"

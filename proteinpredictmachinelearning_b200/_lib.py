@@ -24,6 +24,9 @@ SIGNATURES = {
     "ppml_b200_hw_supported": (_i, [C.POINTER(_i), C.POINTER(_i)]),
     "ppml_b200_device_status": (_i, [C.POINTER(_i)]),
     "ppml_b200_mul_mat_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp]),
+    "ppml_b200_mul_mat_f32_fused": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ppml_b200_row_stats": (_i, [_vp, _vp, _i64, _i, _f, _vp]),
+    "ppml_b200_layernorm_fold": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "ppml_b200_mul_mat_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "ppml_b200_mul_mat_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "ppml_b200_mul_mat_f32_as_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
@@ -39,6 +42,16 @@ SIGNATURES = {
     "ppml_b200_repack_q8_0_host": (_i, [_vp, _i64, _vp]),
     "ppml_b200_quantize_q8_0r": (_i, [_vp, _vp, _i64, _vp]),
     "ppml_b200_q8_0r_bytes": (_i64, [_i64]),
+    "ppml_b200_repack_q8_0": (_i, [_vp, _i64, _vp, _vp]),
+    "ppml_b200_q8_file_write": (_i, [C.c_char_p, _i, C.POINTER(C.c_char_p), C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i)]),
+    "ppml_b200_q8_file_open": (_vp, [C.c_char_p]),
+    "ppml_b200_q8_file_close": (None, [_vp]),
+    "ppml_b200_q8_file_count": (_i, [_vp]),
+    "ppml_b200_q8_file_find": (_i, [_vp, C.c_char_p]),
+    "ppml_b200_q8_file_info": (_i, [_vp, _i, C.c_char_p, _i, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i)]),
+    "ppml_b200_q8_file_nbytes": (_i64, [_vp, _i]),
+    "ppml_b200_q8_file_layout_hash": (_i, [_vp, C.c_char_p]),
+    "ppml_b200_q8_file_load": (_i, [_vp, _i, _vp, _vp, _vp]),
     "ppml_b200_flash_attn_forward": (_i, [C.POINTER(FlashCfg), _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ppml_b200_flash_attn_forward_ex": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ppml_b200_flash_attn_forward_16": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),

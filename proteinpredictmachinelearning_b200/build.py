@@ -14,7 +14,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
 SOURCES = ["simt_kernels.cu", "umma_gemm.cu", "umma_q8.cu", "umma_attn.cu", "noalloc.cu", "capi.cu",
-           "tma_host.cpp", "host_quant.cpp", "ppml_forwarders.cpp"]
+           "tma_host.cpp", "host_quant.cpp", "q8_file.cpp", "ppml_forwarders.cpp"]
 
 
 def _sources():

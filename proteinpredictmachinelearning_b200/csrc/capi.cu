@@ -79,14 +79,17 @@ bool q8_two_pass(int M, int N, int K) {
     return (N + 127) / 128 <= num_sms() && K >= 1024;
 }
 
+struct FusedEpi { const float* ln_stats = nullptr; const float* ln_u = nullptr; const float* gate = nullptr; int act = 0; };
+
 int mul_mat_any(const void* A, const void* B, float* C, int M, int K, int N, const float* bias, int path,
-                int elem, int tf32_mode, cudaStream_t st) {
+                int elem, int tf32_mode, cudaStream_t st, const FusedEpi& fe = FusedEpi()) {
     if (!A || !B || !C || M <= 0 || K <= 0 || N <= 0 || !path_ok(path)) return ST_BAD_ARGS;
     if (path != PPML_B200_PATH_SIMT) {
         UmmaGemmArgs a{};
         a.A = A; a.B = B; a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1;
         a.lda = K; a.ldb = K; a.a_batch = 0; a.b_batch = 0; a.ldc = N; a.c_batch = 0;
         a.bias = bias; a.alpha = 1.0f; a.clamp = 0; a.opm_D = 0; a.opm_L = 0; a.elem = elem; a.tf32_mode = tf32_mode;
+        a.ln_stats = fe.ln_stats; a.ln_u = fe.ln_u; a.gate = fe.gate; a.act = fe.act;
         const int rc = launch_umma_gemm(a, st);
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
     }
@@ -94,7 +97,8 @@ int mul_mat_any(const void* A, const void* B, float* C, int M, int K, int N, con
     p.M = M; p.N = N; p.K = K;
     p.a_sm = K; p.a_sk = 1; p.b_sn = K; p.b_sk = 1; p.c_sm = N; p.c_sn = 1;
     p.planes = 1; p.ne2 = 1; p.a_div2 = 1; p.a_div3 = 1;
-    p.bias = bias; p.bias_seed = (elem == 0) ? 1 : 0; p.alpha = 1.0f;
+    p.bias = bias; p.bias_seed = (elem == 0 && fe.ln_stats == nullptr) ? 1 : 0; p.alpha = 1.0f;
+    p.ln_stats = fe.ln_stats; p.ln_u = fe.ln_u; p.gate = fe.gate; p.act = fe.act;
     return launch_simt_contract(A, B, C, p, elem, st);
 }
 
@@ -136,6 +140,25 @@ int ppml_b200_mul_mat_f32(const float* A, const float* B, float* C, int M, int K
                           int path, int tf32_mode, void* stream) {
     if (tf32_mode < 0 || tf32_mode > 2) return ST_BAD_ARGS;
     return mul_mat_any(A, B, C, M, K, N, bias, path, 0, tf32_mode, as_stream(stream));
+}
+
+int ppml_b200_mul_mat_f32_fused(const float* A, const float* B, float* C, int M, int K, int N, const float* bias,
+                                const float* ln_mean_rstd, const float* ln_u, const float* gate, int act,
+                                int path, int tf32_mode, void* stream) {
+    if (tf32_mode < 0 || tf32_mode > 2 || act < 0 || act > 5) return ST_BAD_ARGS;
+    if ((ln_mean_rstd == nullptr) != (ln_u == nullptr)) return ST_BAD_ARGS;
+    if (ln_mean_rstd && (reinterpret_cast<uintptr_t>(ln_mean_rstd) & 7u)) return ST_BAD_ARGS;
+    if (gate && (reinterpret_cast<uintptr_t>(gate) & 15u) && (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0)) return ST_BAD_ARGS;
+    FusedEpi fe;
+    fe.ln_stats = ln_mean_rstd; fe.ln_u = ln_u; fe.gate = gate; fe.act = act;
+    return mul_mat_any(A, B, C, M, K, N, bias, path, 0, tf32_mode, as_stream(stream), fe);
+}
+int ppml_b200_row_stats(const float* x, float* mean_rstd, int64_t M, int K, float eps, void* stream) {
+    return launch_row_stats(x, mean_rstd, M, K, eps, as_stream(stream));
+}
+int ppml_b200_layernorm_fold(const float* W, const float* gamma, const float* beta, const float* bias, float* Wg, float* u, float* v,
+                             int N, int K, void* stream) {
+    return launch_ln_fold(W, gamma, beta, bias, Wg, u, v, N, K, as_stream(stream));
 }
 
 int ppml_b200_mul_mat_f16(const void* A16, const void* B16, float* C, int M, int K, int N, const float* bias,
@@ -246,6 +269,9 @@ int ppml_b200_quantize_q8_0r(const float* w_dev, void* q8_0r_dev, int64_t ne, vo
     return launch_quantize_q8_0r(w_dev, q8_0r_dev, ne, as_stream(stream));
 }
 int64_t ppml_b200_q8_0r_bytes(int64_t numel) { return numel / 32 * 34; }
+int ppml_b200_repack_q8_0(const void* blocks34_dev, int64_t nblocks, void* q8_0r_dev, void* stream) {
+    return launch_repack_q8_0(blocks34_dev, nblocks, q8_0r_dev, as_stream(stream));
+}
 
 namespace {
 // elem: 0 = fp32, 1 = bf16, 2 = fp16 Q/K/V

@@ -23,13 +23,21 @@ struct SimtContract {
     float alpha;
     int clamp;                  // NaN -> 0, clamp to +-1e4
     long long opm_D, opm_L, opm_B;   // opm_L > 0: blocked outer-product-mean store
+    // fused neighbours of a Linear (see GemmParams in umma_gemm.cuh); plain mul_mat only
+    const float* ln_stats; const float* ln_u; const float* gate; int act;
 };
 int launch_simt_contract(const void* A, const void* B, float* C, const SimtContract& p, int elem /*0 f32,1 f16,2 bf16*/,
                          cudaStream_t st);
 
+// per row of x [M][K]: (mean, 1 / sqrt(var + eps)) with the reference's two-pass variance (src/backend/CPUKernels.cpp:1498-1511)
+int launch_row_stats(const float* x, float* mean_rstd, long long M, int K, float eps, cudaStream_t st);
+// Wg[n][k] = W[n][k] * gamma[k], u[n] = sum_k Wg[n][k], v[n] = sum_k W[n][k] * beta[k] + bias[n]
+int launch_ln_fold(const float* W, const float* gamma, const float* beta, const float* bias, float* Wg, float* u, float* v, int N, int K,
+                   cudaStream_t st);
 int launch_cast(const float* x, void* y, long long n, int to_bf16, cudaStream_t st);
 int launch_quantize_q8_1(const float* x, void* y, long long ne, cudaStream_t st);
 int launch_quantize_q8_0r(const float* w, void* out, long long ne, cudaStream_t st);
+int launch_repack_q8_0(const void* blocks34, long long nblocks, void* q8_0r, cudaStream_t st);
 int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaStream_t st);
 int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
                    const float* bias, int* sumi_out, cudaStream_t st);
@@ -53,6 +61,7 @@ struct UmmaGemmArgs {
     int elem;                          // 0 fp32 (tf32 math), 1 fp16, 2 bf16
     int tf32_mode;                     // fp32 only: 0 round in smem (rna), 1 TMA tf32 type, 2 truncate
     int mn_major;                      // 1: A[b][k][m], B[b][k][n] (row index contiguous; lda / ldb = k pitch), fp32 only
+    const float* ln_stats; const float* ln_u; const float* gate; int act;      // fused LayerNorm algebra / activation gate
 };
 int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st);
 

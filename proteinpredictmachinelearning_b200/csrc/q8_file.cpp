@@ -22,7 +22,6 @@
 #include <vector>
 
 #include "../../include/ppml_b200.h"
-#include "kernels.h"
 
 namespace {
 
@@ -232,7 +231,7 @@ int ppml_b200_q8_file_load(void* handle, int index, void* dst_dev, void* scratch
         if (scratch_dev) {
             // blocks as they are on disk -> device scratch, then one kernel splits them into the two planes
             if (cudaMemcpyAsync(scratch_dev, host, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) rc = 6;
-            else rc = ppml_b200::launch_repack_q8_0(scratch_dev, nb, dst_dev, st);
+            else rc = ppml_b200_repack_q8_0(scratch_dev, nb, dst_dev, st);
         } else {
             std::vector<uint8_t> planar(bytes);
             if (ppml_b200_repack_q8_0_host(host, nb, planar.data()) != 0) rc = 5;

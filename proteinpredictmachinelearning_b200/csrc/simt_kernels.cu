@@ -33,6 +33,18 @@ template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; 
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// the activations of the reference's act_fwd_scalar (src/backend/CPUKernels.cpp:1903-1916), same formulas
+__device__ __forceinline__ float act_scalar(int kind, float x) {
+    switch (kind) {
+        case 1: return 1.0f / (1.0f + expf(-x));
+        case 2: return x / (1.0f + expf(-x));
+        case 3: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        case 4: return tanhf(x);
+        case 5: return x > 0.0f ? x : 0.0f;
+        default: return x;
+    }
+}
+
 template <typename T, bool A_KFAST, bool B_KFAST>
 __global__ void __launch_bounds__(256)
 simt_contract_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restrict__ C, SimtContract p) {
@@ -95,6 +107,10 @@ simt_contract_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __
                 const long long n = n0 + tx * 4 + j;
                 if (n >= p.N) continue;
                 float v = acc[i][j] * p.alpha;
+                if (p.ln_stats != nullptr) {           // LayerNorm folded into the Linear (bias_seed is 0 here)
+                    const float2 st2 = *reinterpret_cast<const float2*>(p.ln_stats + 2 * m);
+                    v = fmaf(-st2.x, p.ln_u[n], v) * st2.y;
+                }
                 if (!p.bias_seed && p.bias != nullptr) v += p.bias[n];
                 if (p.clamp) {
                     if (!(v == v)) v = 0.0f; else v = fminf(fmaxf(v, -1e4f), 1e4f);
@@ -104,6 +120,8 @@ simt_contract_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __
                     const long long d2 = n / p.opm_L, jj = n - d2 * p.opm_L;
                     Cp[(((d1 * p.opm_D + d2) * p.opm_L + ii) * p.opm_L + jj) * p.opm_B] = v;
                 } else {
+                    if (p.gate != nullptr) v = act_scalar(p.act, v) * p.gate[m * p.c_sm + n * p.c_sn];
+                    else if (p.act != 0) v = act_scalar(p.act, v);
                     Cp[m * p.c_sm + n * p.c_sn] = v;
                 }
             }
@@ -129,6 +147,67 @@ int launch_simt_contract(const void* A, const void* B, float* C, const SimtContr
     if (elem == 0) return launch_contract_t<float>(static_cast<const float*>(A), static_cast<const float*>(B), C, p, st);
     if (elem == 1) return launch_contract_t<__half>(static_cast<const __half*>(A), static_cast<const __half*>(B), C, p, st);
     return launch_contract_t<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), C, p, st);
+}
+
+// =============================================================================================
+// LayerNorm folded into the Linear that follows it: per-row statistics of the activations and the weight-side terms.
+// The statistics follow the reference's OP_NORM (src/backend/CPUKernels.cpp:1498-1511): mean, then the mean of the
+// squared differences, then 1 / sqrt(var + eps); one warp per row.
+// =============================================================================================
+__global__ void __launch_bounds__(256)
+row_stats_kernel(const float* __restrict__ x, float* __restrict__ mean_rstd, long long M, int K, float eps) {
+    const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const float* xr = x + row * K;
+    float s = 0.0f;
+    for (int k = lane; k < K; k += 32) s += xr[k];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    const float mean = s / static_cast<float>(K);
+    float v = 0.0f;
+    for (int k = lane; k < K; k += 32) { const float d = xr[k] - mean; v = fmaf(d, d, v); }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == 0) {
+        mean_rstd[2 * row] = mean;
+        mean_rstd[2 * row + 1] = 1.0f / sqrtf(v / static_cast<float>(K) + eps);
+    }
+}
+
+int launch_row_stats(const float* x, float* mean_rstd, long long M, int K, float eps, cudaStream_t st) {
+    if (!x || !mean_rstd || M <= 0 || K <= 0) return ST_BAD_ARGS;
+    const long long grid = (M + 7) / 8;
+    if (grid > 0x7fffffffLL) return ST_BAD_ARGS;
+    row_stats_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(x, mean_rstd, M, K, eps);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// One warp per output feature n: Wg[n][k] = W[n][k] * gamma[k], u[n] = sum_k Wg[n][k], v[n] = sum_k W[n][k] * beta[k] + bias[n]
+__global__ void __launch_bounds__(256)
+ln_fold_kernel(const float* __restrict__ W, const float* __restrict__ gamma, const float* __restrict__ beta,
+               const float* __restrict__ bias, float* __restrict__ Wg, float* __restrict__ u, float* __restrict__ v, int N, int K) {
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float su = 0.0f, sv = 0.0f;
+    for (int k = lane; k < K; k += 32) {
+        const float w = W[static_cast<long long>(n) * K + k];
+        const float wg = w * gamma[k];
+        Wg[static_cast<long long>(n) * K + k] = wg;
+        su += wg;
+        sv = fmaf(w, beta[k], sv);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) { su += __shfl_xor_sync(0xffffffffu, su, off); sv += __shfl_xor_sync(0xffffffffu, sv, off); }
+    if (lane == 0) { u[n] = su; v[n] = sv + (bias ? bias[n] : 0.0f); }
+}
+
+int launch_ln_fold(const float* W, const float* gamma, const float* beta, const float* bias, float* Wg, float* u, float* v, int N, int K,
+                   cudaStream_t st) {
+    if (!W || !gamma || !beta || !Wg || !u || !v || N <= 0 || K <= 0) return ST_BAD_ARGS;
+    ln_fold_kernel<<<(N + 7) / 8, 256, 0, st>>>(W, gamma, beta, bias, Wg, u, v, N, K);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
 // =============================================================================================
@@ -244,6 +323,35 @@ int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaSt
     if (grid > 0x7fffffffLL) return ST_BAD_ARGS;
     dequantize_q8_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(static_cast<const uint8_t*>(x), y, ne,
                                                                       kind == 0 ? 34 : 36, kind == 0 ? 2 : 4);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// =============================================================================================
+// Q8_0 blocks as they lie on disk (34 bytes: half d, 32 int8; 2-byte aligned) -> planar Q8_0R ([nb * 32] int8, then
+// [nb] half scales).  One thread per 4 quants; the thread of a block's first word also moves the scale.
+// =============================================================================================
+__global__ void __launch_bounds__(256)
+repack_q8_0_kernel(const uint8_t* __restrict__ blocks, uint32_t* __restrict__ qs, uint16_t* __restrict__ d, long long nwords) {
+    const long long w = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (w >= nwords) return;
+    const long long b = w >> 3;
+    const int j = static_cast<int>(w & 7);
+    const uint8_t* src = blocks + b * 34;
+    const uint16_t lo = *reinterpret_cast<const uint16_t*>(src + 2 + 4 * j);
+    const uint16_t hi = *reinterpret_cast<const uint16_t*>(src + 4 + 4 * j);
+    qs[w] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+    if (j == 0) d[b] = *reinterpret_cast<const uint16_t*>(src);
+}
+
+int launch_repack_q8_0(const void* blocks34, long long nblocks, void* q8_0r, cudaStream_t st) {
+    if (!blocks34 || !q8_0r || nblocks <= 0) return ST_BAD_ARGS;
+    if ((reinterpret_cast<uintptr_t>(blocks34) & 1u) || (reinterpret_cast<uintptr_t>(q8_0r) & 3u)) return ST_BAD_ARGS;
+    const long long nwords = nblocks * 8;
+    const long long grid = (nwords + 255) / 256;
+    if (grid > 0x7fffffffLL) return ST_BAD_ARGS;
+    uint8_t* out = static_cast<uint8_t*>(q8_0r);
+    repack_q8_0_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(static_cast<const uint8_t*>(blocks34), reinterpret_cast<uint32_t*>(out),
+                                                                    reinterpret_cast<uint16_t*>(out + nblocks * 32), nwords);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 

@@ -129,6 +129,7 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st) {
     p.k_steps = (a.K + bk - 1) / bk;
     p.C = a.C; p.ldc = a.ldc; p.c_batch = a.c_batch;
     p.bias = a.bias; p.alpha = a.alpha; p.clamp = a.clamp;
+    p.ln_stats = a.ln_stats; p.ln_u = a.ln_u; p.gate = a.gate; p.act = a.act;
     p.opm_D = a.opm_D; p.opm_L = a.opm_L;
     p.ab_fmt = (a.elem == 2) ? 1 : 0;
     p.err = err;

@@ -31,6 +31,14 @@ struct GemmParams {
     int vec_ok;             // 1: float4 stores are legal (alignment checked on the host)
     int opm_D, opm_L;       // OPM_BLOCKED: row = d1*L+i, col = d2*L+j -> ((d1*D+d2)*L+i)*L+j
     int ab_fmt;             // operand format of the f16 kind: 0 = fp16, 1 = bf16
+    // fused neighbours of a Linear (all optional):
+    //   ln_stats [M][2] = (mean, 1 / sqrt(var + eps)) of every row of A, ln_u [N]: the product ran on the raw rows with
+    //   weights pre-scaled by gamma, and  out = rstd * (acc - mean * u[n]) + bias[n]  is LayerNorm(x) W^T + b
+    //   gate [M][N] (row stride ldc), act: out = act(out) * gate  (the reference's OP_ACT_MUL on a Linear's output)
+    const float* ln_stats;
+    const float* ln_u;
+    const float* gate;
+    int act;                // 0 none, 1 sigmoid, 2 silu, 3 gelu (tanh form), 4 tanh, 5 relu
     int* err;               // device error word
 };
 
@@ -48,7 +56,19 @@ __host__ __device__ constexpr int gemm_num_stages() {
 
 constexpr int kEpiStagePitch = 144;                       // bytes per staged row: 32 floats + 16 bytes of padding
 constexpr int kEpiStageBytes = 32 * kEpiStagePitch;       // one warp's 32 x 32 transposition buffer
-constexpr int kEpiBiasBytes = 256 * 4;                    // one warp's copy of the tile's bias slice
+constexpr int kEpiBiasBytes = 2 * 256 * 4;                // one warp's copy of the tile's bias slice and of its u slice
+
+// the activations of the reference's act_fwd_scalar (src/backend/CPUKernels.cpp:1903-1916), same formulas
+__device__ __forceinline__ float act_apply(int kind, float x) {
+    switch (kind) {
+        case 1: return 1.0f / (1.0f + expf(-x));
+        case 2: return x / (1.0f + expf(-x));
+        case 3: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        case 4: return tanhf(x);
+        case 5: return x > 0.0f ? x : 0.0f;
+        default: return x;
+    }
+}
 
 // dynamic smem: [stages x (A tile | B tile)] (1024-byte aligned), the barriers, then per epilogue warp a
 // transposition buffer and a bias slice
@@ -216,6 +236,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
                 for (int j = lane; j < BN; j += 32) bias_s[j] = 0.0f;
             }
+            float ln_mean = 0.0f, ln_rstd = 1.0f;
+            if (p.ln_stats != nullptr) {
+                for (int j = lane; j < BN; j += 32) bias_s[256 + j] = (col0 + j < p.N) ? p.ln_u[col0 + j] : 0.0f;
+                const int rown = mt * 128 + q * 32 + lane;
+                if (rown < p.M) {
+                    const float2 st2 = *reinterpret_cast<const float2*>(p.ln_stats + 2 * (static_cast<long long>(b) * p.M + rown));
+                    ln_mean = st2.x; ln_rstd = st2.y;
+                }
+            }
             __syncwarp();
             if (!mbar_wait(tfull_bar(acc), acc_ph, cta_abort, p.err, 0x301)) { ok = false; break; }
             tc_fence_after();
@@ -236,6 +265,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     f[j4 * 4 + 2] = fmaf(__uint_as_float(v[j4 * 4 + 2]), p.alpha, b4.z);
                     f[j4 * 4 + 3] = fmaf(__uint_as_float(v[j4 * 4 + 3]), p.alpha, b4.w);
                 }
+                if (p.ln_stats != nullptr) {
+                    // f = alpha * acc + bias so far; the LayerNorm form is rstd * (alpha * acc - mean * u) + bias
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float bj = bias_s[c * 32 + j];
+                        f[j] = fmaf(fmaf(-ln_mean, bias_s[256 + c * 32 + j], f[j] - bj), ln_rstd, bj);
+                    }
+                }
                 if (p.clamp) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -243,6 +280,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         x = (x == x) ? fminf(fmaxf(x, -1e4f), 1e4f) : 0.0f;
                         f[j] = x;
                     }
+                }
+                if (p.act != 0 && p.gate == nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = act_apply(p.act, f[j]);
                 }
                 if (p.vec_ok) {
 #pragma unroll
@@ -256,9 +297,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     for (int i = 0; i < 8; ++i) {
                         const int rr = (lane >> 3) + 4 * i;
                         const int row = row0 + rr;
-                        const float4 val = *reinterpret_cast<const float4*>(stage + rr * kEpiStagePitch + cc * 16);
+                        float4 val = *reinterpret_cast<const float4*>(stage + rr * kEpiStagePitch + cc * 16);
                         if (row < p.M && col < p.N) {    // vec_ok: N, ldc (or L) are multiples of 4
                             if constexpr (EPI == Epi::ROW_MAJOR) {
+                                if (p.gate != nullptr) {         // read with the same coalesced pattern as the store
+                                    const float4 g4 = *reinterpret_cast<const float4*>(p.gate + static_cast<long long>(b) * p.c_batch +
+                                                                                        static_cast<long long>(row) * p.ldc + col);
+                                    val.x = act_apply(p.act, val.x) * g4.x; val.y = act_apply(p.act, val.y) * g4.y;
+                                    val.z = act_apply(p.act, val.z) * g4.z; val.w = act_apply(p.act, val.w) * g4.w;
+                                }
                                 *reinterpret_cast<float4*>(p.C + static_cast<long long>(b) * p.c_batch +
                                                            static_cast<long long>(row) * p.ldc + col) = val;
                             } else {
@@ -278,7 +325,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             const int col = cbase + j;
                             if (col < p.N) {
                                 if constexpr (EPI == Epi::ROW_MAJOR) {
-                                    p.C[static_cast<long long>(b) * p.c_batch + static_cast<long long>(row) * p.ldc + col] = f[j];
+                                    const long long off = static_cast<long long>(b) * p.c_batch + static_cast<long long>(row) * p.ldc + col;
+                                    p.C[off] = (p.gate != nullptr) ? act_apply(p.act, f[j]) * p.gate[off] : f[j];
                                 } else {
                                     const int L = p.opm_L, D = p.opm_D;
                                     const int d1 = row / L, ii = row - d1 * L;

@@ -50,6 +50,39 @@ def mul_mat_cuda(A, B, bias=None, path=PATH_AUTO, tf32_mode=TF32_TMA, out=None):
     return Cout
 
 
+ACT = {"none": 0, "sigmoid": 1, "silu": 2, "gelu": 3, "tanh": 4, "relu": 5}
+
+
+def layernorm_fold(W, gamma, beta, bias=None):
+    """Weight-side terms of LayerNorm -> Linear, once per layer: (Wg, u, v)."""
+    W = _f32c(W)
+    N, K = W.shape
+    Wg, u, v = torch.empty_like(W), torch.empty(N, device=W.device), torch.empty(N, device=W.device)
+    _check(_lib.load().ppml_b200_layernorm_fold(_p(W), _p(gamma), _p(beta), _p(bias), _p(Wg), _p(u), _p(v), N, K, _stream()), "layernorm_fold")
+    return Wg, u, v
+
+
+def row_stats(x, eps=1e-5):
+    x = _f32c(x)
+    M, K = x.shape
+    out = torch.empty((M, 2), device=x.device, dtype=torch.float32)
+    _check(_lib.load().ppml_b200_row_stats(_p(x), _p(out), M, K, float(eps), _stream()), "row_stats")
+    return out
+
+
+def mul_mat_fused(A, B, bias=None, ln_stats=None, ln_u=None, gate=None, act="none", path=PATH_AUTO, tf32_mode=TF32_TMA, out=None):
+    """A Linear with LayerNorm folded in front (ln_stats from row_stats(A), B / bias / ln_u from layernorm_fold) and / or an
+    activation gate behind (act(out) * gate)."""
+    A, B = _f32c(A), _f32c(B)
+    M, K = A.shape
+    N = B.shape[0]
+    Cout = out if out is not None else torch.empty((M, N), device=A.device, dtype=torch.float32)
+    rc = _lib.load().ppml_b200_mul_mat_f32_fused(_p(A), _p(B), _p(Cout), M, K, N, _p(bias), _p(ln_stats), _p(ln_u), _p(gate), ACT[act],
+                                                 path, tf32_mode, _stream())
+    _check(rc, "mul_mat_f32_fused")
+    return Cout
+
+
 def mul_mat_16(A16, B16, bias=None, path=PATH_AUTO, out=None):
     """16-bit operands (torch.float16 or torch.bfloat16), fp32 output; replaces the mul_mat_*f16* launchers."""
     assert A16.dtype == B16.dtype and A16.dtype in (torch.float16, torch.bfloat16)

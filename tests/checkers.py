@@ -175,6 +175,38 @@ class Oracle:
         return (Cout, sumi) if want_sumi else Cout
 
 
+def layer_norm_f32(x, gamma, beta, eps):
+    """LayerNorm::forward of the reference (src/model/Embedding.cpp:268-289): OP_NORM along the feature axis
+    (src/backend/CPUKernels.cpp:1498-1512: mean, mean of squared differences, 1 / sqrt(var + eps), all in fp32 and in
+    this order), then * gamma + beta."""
+    x = np.asarray(x, np.float32)
+    D = np.float32(x.shape[1])
+    mean = (np.add.reduce(x, axis=1, dtype=np.float32) / D).astype(np.float32)
+    diff = (x - mean[:, None]).astype(np.float32)
+    var = (np.add.reduce(diff * diff, axis=1, dtype=np.float32) / D).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt(var + np.float32(eps))).astype(np.float32)
+    return ((diff * inv[:, None]) * np.asarray(gamma, np.float32) + np.asarray(beta, np.float32)).astype(np.float32)
+
+
+def act_mul_f32(x, g, kind):
+    """OP_ACT_MUL (src/backend/CPUKernels.cpp:1903-1916, :1947-1967): act(x) * g with the reference's formulas in fp32."""
+    x = np.asarray(x, np.float32)
+    one = np.float32(1.0)
+    if kind == "sigmoid":
+        a = one / (one + np.exp(-x))
+    elif kind == "silu":
+        a = x / (one + np.exp(-x))
+    elif kind == "gelu":
+        a = np.float32(0.5) * x * (one + np.tanh(np.float32(np.sqrt(2.0 / np.pi)) * (x + np.float32(0.044715) * x * x * x)))
+    elif kind == "tanh":
+        a = np.tanh(x)
+    elif kind == "relu":
+        a = np.maximum(x, np.float32(0.0))
+    else:
+        a = x
+    return (a.astype(np.float32) * np.asarray(g, np.float32)).astype(np.float32)
+
+
 class Ref:
     """numpy front end of the reference's own CPU implementation (oracle/_ref/libppml_ref.so)."""
 
