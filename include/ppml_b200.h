@@ -202,6 +202,20 @@ int ppml_b200_flash_attn_forward_16(const ppml_b200_flash_cfg* cfg, int Lk, int6
                                     const void* Q16, const void* K16, const void* V16, const float* bias,
                                     float* O, float* LSE, int is_bf16, int path, void* stream);
 
+/* The fused op on token-major operands, with the output gate folded in (no counterpart in the reference as one call: there
+ * every attention is wrapped in permute copies -- head split {2,0,1,3} in src/modules/Attention.cpp:363-370, flash layout
+ * {1,0,2,3} three times in and once out in src/core/ComputeGraphHelper.cpp:455-483, head merge {1,2,0,3} in
+ * src/modules/Attention.cpp:385 -- and followed by act_mul(gate, merged, sigmoid), :390).  Q, K, V are the outputs of the
+ * projection Linears as they lie: [B][L][ld_q] and [B][Lk][ld_kv] fp32 with head h in columns [h*d, (h+1)*d) (ld >= h*d,
+ * so Q, K, V may also be column ranges of one wider fused projection).  O is written token-major too, [B][L][ld_o], which
+ * is what the output Linear reads; with `gate` ([B][L][ld_gate], the gate Linear's output) the result is
+ * act(gate) * softmax(..) V (act as in ppml_b200_mul_mat_f32_fused; the model uses sigmoid).  bias, LSE, Lk and
+ * bias_batch_stride as in ppml_b200_flash_attn_forward_ex. */
+int ppml_b200_flash_attn_forward_tokens(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
+                                        const float* Q, const float* K, const float* V, int64_t ld_q, int64_t ld_kv,
+                                        const float* bias, const float* gate, int64_t ld_gate, int act, float* O, int64_t ld_o,
+                                        float* LSE, int path, void* stream);
+
 /* ---- OP_OUT_PROD -------------------------------------------------------------------------------
  * Replaces out_prod_cuda (src/backend/CUDAKernels.cpp:201; src/cuda/OutProdKernel.cu:211-260):
  * dst[i0,i1,i2,i3] = sum_k s0[i0,k,i2/(ne2/ne02),i3/(ne3/ne03)] * s1[i1,k,i2,i3]; dims in the graph's

@@ -55,6 +55,7 @@ SIGNATURES = {
     "ppml_b200_flash_attn_forward": (_i, [C.POINTER(FlashCfg), _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ppml_b200_flash_attn_forward_ex": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ppml_b200_flash_attn_forward_16": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "ppml_b200_flash_attn_forward_tokens": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i, _vp, _i64, _vp, _i, _vp]),
     "ppml_b200_out_prod": (_i, [_vp, _vp, _vp] + [_i64] * 12 + [_i, _vp]),
     "ppml_b200_tri_mul": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _vp]),
     "ppml_b200_outer_prod_mean": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _f, _i, _vp]),

@@ -276,9 +276,11 @@ int ppml_b200_repack_q8_0(const void* blocks34_dev, int64_t nblocks, void* q8_0r
 namespace {
 // elem: 0 = fp32, 1 = bf16, 2 = fp16 Q/K/V
 int flash_attn_any(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride, const void* Q, const void* K,
-                   const void* V, int elem, const float* bias, float* O, float* LSE, int path, void* stream) {
+                   const void* V, int elem, const float* bias, float* O, float* LSE, int path, void* stream,
+                   const AttnLayout* layout = nullptr) {
     if (!cfg || !Q || !K || !V || !O || !path_ok(path)) return ST_BAD_ARGS;
     if (cfg->B <= 0 || cfg->h <= 0 || cfg->L <= 0 || cfg->d <= 0 || Lk <= 0) return ST_BAD_ARGS;
+    const AttnLayout lay = layout ? *layout : AttnLayout::flash(cfg->h, cfg->L, Lk, cfg->d);
     const float scale = (cfg->scale > 0.f) ? cfg->scale : 1.0f / std::sqrt(static_cast<float>(cfg->d));
     // Bc is the key tile of the reference's CPU kernel (<= 0 there means 64, src/ops/FlashAttn.cpp:58); it only matters
     // for rows whose first Bc scores are all -inf, which that kernel turns into O = 0, LSE = -inf.  Bc < 0 here switches
@@ -286,11 +288,11 @@ int flash_attn_any(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_st
     const int ft = cfg->Bc < 0 ? 0 : (cfg->Bc == 0 ? 64 : cfg->Bc);
     if (path != PPML_B200_PATH_SIMT) {
         const int rc = launch_umma_attn(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0,
-                                        scale, cfg->softmax_eps, bias_batch_stride, ft, as_stream(stream));
+                                        scale, cfg->softmax_eps, bias_batch_stride, ft, lay, as_stream(stream));
         if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
     }
     return launch_attn_rowwarp(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
-                               cfg->softmax_eps, bias_batch_stride, ft, as_stream(stream));
+                               cfg->softmax_eps, bias_batch_stride, ft, lay, as_stream(stream));
 }
 }  // namespace
 
@@ -304,6 +306,22 @@ int ppml_b200_flash_attn_forward_16(const ppml_b200_flash_cfg* cfg, int Lk, int6
                                     const void* Q16, const void* K16, const void* V16, const float* bias,
                                     float* O, float* LSE, int is_bf16, int path, void* stream) {
     return flash_attn_any(cfg, Lk, bias_batch_stride, Q16, K16, V16, is_bf16 ? 1 : 2, bias, O, LSE, path, stream);
+}
+
+int ppml_b200_flash_attn_forward_tokens(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_stride,
+                                        const float* Q, const float* K, const float* V, int64_t ld_q, int64_t ld_kv,
+                                        const float* bias, const float* gate, int64_t ld_gate, int act, float* O, int64_t ld_o,
+                                        float* LSE, int path, void* stream) {
+    if (!cfg || cfg->h <= 0 || cfg->d <= 0 || cfg->L <= 0 || Lk <= 0) return ST_BAD_ARGS;
+    const int64_t hd = static_cast<int64_t>(cfg->h) * cfg->d;
+    if (ld_q < hd || ld_kv < hd || ld_o < hd || (gate && ld_gate < hd) || act < 0 || act > 5) return ST_BAD_ARGS;
+    AttnLayout lay{};
+    lay.q_l = ld_q; lay.q_h = cfg->d; lay.q_b = ld_q * cfg->L;
+    lay.k_l = lay.v_l = ld_kv; lay.k_h = lay.v_h = cfg->d; lay.k_b = lay.v_b = ld_kv * Lk;
+    lay.o_l = ld_o; lay.o_h = cfg->d; lay.o_b = ld_o * cfg->L;
+    lay.g_l = ld_gate; lay.g_h = cfg->d; lay.g_b = ld_gate * cfg->L;
+    lay.gate = gate; lay.act = gate ? act : 0;
+    return flash_attn_any(cfg, Lk, bias_batch_stride, Q, K, V, 0, bias, O, LSE, path, stream, &lay);
 }
 
 int ppml_b200_flash_attn_forward(const ppml_b200_flash_cfg* cfg, const float* Q, const float* K, const float* V,

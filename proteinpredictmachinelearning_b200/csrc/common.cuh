@@ -151,6 +151,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap,
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar, int x, int y, int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 // Tiled bulk store shared -> global (bulk async-group completion): the box at `src_smem`, laid out as the tensor map's
 // swizzle mode says, goes to coordinates (x, y, z); parts of the box outside the tensor are not written.  The writes to
 // shared memory must have been made visible to the async proxy (fence_proxy_async_smem) before the issuing thread runs this.

@@ -42,11 +42,30 @@ int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaSt
 int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
                    const float* bias, int* sumi_out, cudaStream_t st);
 // elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16; bias, O and LSE are fp32
+// Where the attention operands live.  Element (b, h, i, dd) of Q is at Q[b * q_b + h * q_h + i * q_l + dd] (K, V, O alike;
+// the head dim is always contiguous).  flash(): the fused op's own layout [B][h][L][d] (include/ppml/FlashAttn.h:24-32);
+// tokens(): the layout of the Linear that produced the operand, [B][L][ld] with head h in columns [h * d, (h + 1) * d) --
+// what the reference only reaches through its permute copies (src/core/ComputeGraphHelper.cpp:455-483).
+// gate (optional, strides g_*): O = act(gate) * O, the OP_ACT_MUL node behind every attention of the model
+// (src/modules/Attention.cpp:390).
+struct AttnLayout {
+    long long q_b, q_h, q_l, k_b, k_h, k_l, v_b, v_h, v_l, o_b, o_h, o_l, g_b, g_h, g_l;
+    const float* gate; int act;
+    static AttnLayout flash(int H, int L, int Lk, int d) {
+        AttnLayout a{};
+        a.q_l = a.k_l = a.v_l = a.o_l = d;
+        a.q_h = a.o_h = static_cast<long long>(L) * d; a.k_h = a.v_h = static_cast<long long>(Lk) * d;
+        a.q_b = a.o_b = a.q_h * H; a.k_b = a.v_b = a.k_h * H;
+        a.g_b = a.o_b; a.g_h = a.o_h; a.g_l = a.o_l;
+        a.gate = nullptr; a.act = 0;
+        return a;
+    }
+};
 // ft: keys of the reference's first softmax tile (its Bc); a row whose first ft scores are all -inf gives O = 0, LSE = -inf
 // as the reference's CPU kernel does; 0 switches that off
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                        long long bias_batch_stride, int ft, cudaStream_t st);
+                        long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st);
 
 // tcgen05 paths (umma_gemm.cu / umma_q8.cu / umma_attn.cu).  Each returns ST_UNSUPPORTED_PATH when the
 // shape or the alignment rules it out, so that the caller can take the CUDA-core kernel.
@@ -71,7 +90,7 @@ size_t umma_q8_scratch_bytes(int N, int K);
 
 int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                     long long bias_batch_stride, int ft, cudaStream_t st);
+                     long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st);
 
 int num_sms();
 

@@ -437,17 +437,18 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                     const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
-                    int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft) {
+                    int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft,
+                    const AttnLayout lay) {
     extern __shared__ float qs[];                    // [4][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int i = blockIdx.x * 4 + warp;
     const int hh = blockIdx.y, b = blockIdx.z;
     const size_t bh = static_cast<size_t>(b) * H + hh;
-    const T* Qb = Q + bh * static_cast<size_t>(L) * d;
-    const T* Kb = K + bh * static_cast<size_t>(Lk) * d;
-    const T* Vb = V + bh * static_cast<size_t>(Lk) * d;
+    const T* Qb = Q + b * lay.q_b + hh * lay.q_h;
+    const T* Kb = K + b * lay.k_b + hh * lay.k_h;
+    const T* Vb = V + b * lay.v_b + hh * lay.v_h;
     float* myq = qs + warp * d;
-    if (i < L) for (int dd = lane; dd < d; dd += 32) myq[dd] = attn_ld(Qb + static_cast<size_t>(i) * d + dd);
+    if (i < L) for (int dd = lane; dd < d; dd += 32) myq[dd] = attn_ld(Qb + static_cast<size_t>(i) * lay.q_l + dd);
     __syncwarp();
     if (i >= L) return;
     const float* Bb = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
@@ -460,7 +461,7 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
         const int j = j0 + lane;
         float s = -CUDART_INF_F;
         if (j < jmax) {
-            const T* k = Kb + static_cast<size_t>(j) * d;
+            const T* k = Kb + static_cast<size_t>(j) * lay.k_l;
             float dot = 0.0f;
             for (int dd = 0; dd < d; ++dd) dot = fmaf(myq[dd], attn_ld(k + dd), dot);
             s = dot * scale;
@@ -483,7 +484,7 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
         const int nj = (jmax - j0 < 32) ? (jmax - j0) : 32;
         for (int jj = 0; jj < nj; ++jj) {
             const float p = __shfl_sync(0xffffffffu, pj, jj);
-            const T* v = Vb + static_cast<size_t>(j0 + jj) * d;
+            const T* v = Vb + static_cast<size_t>(j0 + jj) * lay.v_l;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int dd = lane + 32 * t;
@@ -496,11 +497,16 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
         for (int off = 16; off > 0; off >>= 1) mfirst = fmaxf(mfirst, __shfl_xor_sync(0xffffffffu, mfirst, off));
         if (mfirst == -CUDART_INF_F) l = 0.0f;       // the reference's first key tile is fully masked: O = 0, LSE = -inf
     }
-    float* o = O + bh * static_cast<size_t>(L) * d + static_cast<size_t>(i) * d;
+    const long long ooff = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l;
+    const long long goff = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l;
+    float* o = O + ooff;
     if (l > 0.0f) {
         const float inv = 1.0f / (l + eps);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) { const int dd = lane + 32 * t; if (dd < d) o[dd] = acc[t] * inv; }
+        for (int t = 0; t < 4; ++t) {
+            const int dd = lane + 32 * t;
+            if (dd < d) o[dd] = lay.gate ? act_scalar(lay.act, lay.gate[goff + dd]) * (acc[t] * inv) : acc[t] * inv;
+        }
         if (LSE && lane == 0) LSE[bh * L + i] = m + logf(l + eps);
     } else {
 #pragma unroll
@@ -525,7 +531,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(128)
 attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                       const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
-                      int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft) {
+                      int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft,
+                      const AttnLayout lay) {
     constexpr int kTile = 32;
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr int kPer = (kTile * D + 127) / 128;               // K (and V) elements each thread moves per tile
@@ -538,12 +545,12 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
     const int i = blockIdx.x * 128 + threadIdx.x;
     const int hh = blockIdx.y, b = blockIdx.z;
     const size_t bh = static_cast<size_t>(b) * H + hh;
-    const T* Kb = K + bh * static_cast<size_t>(Lk) * D;
-    const T* Vb = V + bh * static_cast<size_t>(Lk) * D;
+    const T* Kb = K + b * lay.k_b + hh * lay.k_h;
+    const T* Vb = V + b * lay.v_b + hh * lay.v_h;
     const bool row_ok = i < L;
     float q[D];
 #pragma unroll
-    for (int dd = 0; dd < D; ++dd) q[dd] = row_ok ? attn_ld(Q + (bh * L + i) * D + dd) * scale : 0.0f;
+    for (int dd = 0; dd < D; ++dd) q[dd] = row_ok ? attn_ld(Q + b * lay.q_b + hh * lay.q_h + static_cast<long long>(i) * lay.q_l + dd) * scale : 0.0f;
     // bias: every warp brings the 32 x 32 tile of its own rows through shared memory (row by row, 128 contiguous bytes
     // per request) and each thread then reads its row back with 16-byte loads; the pitch of 36 floats keeps both sides
     // free of bank conflicts
@@ -566,8 +573,8 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
         for (int c = 0; c < kPer; ++c) {
             const int e = threadIdx.x + c * 128;
             const bool ok = e < kTile * D && j0 + e / D < Lk;
-            kreg[c] = ok ? attn_ld(Kb + static_cast<size_t>(j0) * D + e) : 0.0f;
-            vreg[c] = ok ? attn_ld(Vb + static_cast<size_t>(j0) * D + e) : 0.0f;
+            kreg[c] = ok ? attn_ld(Kb + static_cast<long long>(j0 + e / D) * lay.k_l + e % D) : 0.0f;
+            vreg[c] = ok ? attn_ld(Vb + static_cast<long long>(j0 + e / D) * lay.v_l + e % D) : 0.0f;
         }
     };
     auto fetch_bias = [&](int j0, int buf) {
@@ -650,11 +657,13 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
     }
     if (!row_ok) return;
     if (ft > 0 && mfirst == -CUDART_INF_F) l = 0.0f; // the reference's first key tile is fully masked: O = 0, LSE = -inf
-    float* o = O + (bh * L + i) * D;
+    const long long ooff = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l;
+    const long long goff = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l;
+    float* o = O + ooff;
     float inv = 0.0f, lse = -CUDART_INF_F;
     if (l > 0.0f) { inv = 1.0f / (l + eps); lse = m + logf(l + eps); }
 #pragma unroll
-    for (int dd = 0; dd < D; ++dd) o[dd] = acc[dd] * inv;
+    for (int dd = 0; dd < D; ++dd) o[dd] = lay.gate ? act_scalar(lay.act, lay.gate[goff + dd]) * (acc[dd] * inv) : acc[dd] * inv;
     if (LSE) LSE[bh * L + i] = lse;
 }
 
@@ -666,7 +675,7 @@ __global__ void __launch_bounds__(128)
 attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                      const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
                      int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, long long rows_total,
-                     int ft) {
+                     int ft, const AttnLayout lay) {
     constexpr float kLog2e = 1.4426950408889634f;
     const int lane = threadIdx.x & 31;
     const long long row = blockIdx.x * 4LL + (threadIdx.x >> 5);          // flattened (batch, head, query)
@@ -677,9 +686,9 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
     const long long b = bh / H;
     float q[D];
 #pragma unroll
-    for (int dd = 0; dd < D; ++dd) q[dd] = attn_ld(Q + row * D + dd) * scale;
-    const T* Kb = K + bh * static_cast<long long>(Lk) * D;
-    const T* Vb = V + bh * static_cast<long long>(Lk) * D;
+    for (int dd = 0; dd < D; ++dd) q[dd] = attn_ld(Q + b * lay.q_b + hh * lay.q_h + static_cast<long long>(i) * lay.q_l + dd) * scale;
+    const T* Kb = K + b * lay.k_b + hh * lay.k_h;
+    const T* Vb = V + b * lay.v_b + hh * lay.v_h;
     const float* Bb = bias ? bias + b * bias_batch_stride + (static_cast<long long>(hh) * L + i) * Lk : nullptr;
     const int jmax = causal ? min(i + 1, Lk) : Lk;
     float m = -CUDART_INF_F, l = 0.0f;
@@ -691,7 +700,7 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
     for (int j = lane; j < jmax; j += 32) {
         float s = 0.0f;
 #pragma unroll
-        for (int dd = 0; dd < D; ++dd) s = fmaf(q[dd], attn_ld(Kb + static_cast<long long>(j) * D + dd), s);
+        for (int dd = 0; dd < D; ++dd) s = fmaf(q[dd], attn_ld(Kb + static_cast<long long>(j) * lay.k_l + dd), s);
         if (Bb) s += Bb[j];
         if (j < ft) mfirst = fmaxf(mfirst, s);
         const float m_new = fmaxf(m, s);
@@ -700,7 +709,7 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
         const float pj = exp2f((s - m_new) * kLog2e);
         l = fmaf(l, alpha, pj);
 #pragma unroll
-        for (int dd = 0; dd < D; ++dd) acc[dd] = fmaf(acc[dd], alpha, pj * attn_ld(Vb + static_cast<long long>(j) * D + dd));
+        for (int dd = 0; dd < D; ++dd) acc[dd] = fmaf(acc[dd], alpha, pj * attn_ld(Vb + static_cast<long long>(j) * lay.v_l + dd));
         m = m_new;
     }
     float mw = m;
@@ -722,75 +731,79 @@ attn_keylanes_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
         float a = acc[dd] * f;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-        if (lane == 0) O[row * D + dd] = a * inv;
+        if (lane == 0) {
+            const long long oo = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l + dd;
+            const long long go = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l + dd;
+            O[oo] = lay.gate ? act_scalar(lay.act, lay.gate[go]) * (a * inv) : a * inv;
+        }
     }
     if (LSE && lane == 0) LSE[row] = lse;
 }
 
 template <typename T>
 bool launch_attn_keylanes(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
-                          int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, cudaStream_t st) {
+                          int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st) {
     const long long rows = static_cast<long long>(B) * H * L;
     const long long blocks = (rows + 3) / 4;
     if (blocks > 0x7fffffffLL) return false;
     const unsigned grid = static_cast<unsigned>(blocks);
-    if (d == 4) attn_keylanes_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft);
-    else if (d == 8) attn_keylanes_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft);
-    else if (d == 16) attn_keylanes_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft);
+    if (d == 4) attn_keylanes_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft, lay);
+    else if (d == 8) attn_keylanes_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft, lay);
+    else if (d == 16) attn_keylanes_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, rows, ft, lay);
     else return false;
     return true;
 }
 
 template <typename T>
 bool launch_attn_rowthread(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
-                           int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, cudaStream_t st) {
+                           int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st) {
     dim3 grid((L + 127) / 128, H, B);
-    if (d == 4) attn_rowthread_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft);
-    else if (d == 8) attn_rowthread_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft);
-    else if (d == 16) attn_rowthread_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft);
+    if (d == 4) attn_rowthread_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, lay);
+    else if (d == 8) attn_rowthread_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, lay);
+    else if (d == 16) attn_rowthread_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, lay);
     else return false;
     return true;
 }
 
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                        long long bias_batch_stride, int ft, cudaStream_t st) {
+                        long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st) {
     if (d > 128 || H > 65535 || B > 65535 || elem < 0 || elem > 2) return ST_BAD_ARGS;
     // small head dims with enough query rows to fill CTAs of one thread per row
     if ((d == 4 || d == 8 || d == 16) && L < 32) {
         bool done;
         if (elem == 0) done = launch_attn_keylanes(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
-                                                   bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
+                                                   bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay, st);
         else if (elem == 1) done = launch_attn_keylanes(static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
                                                         static_cast<const __nv_bfloat16*>(V), bias, O, LSE, B, H, L, Lk, d, causal, scale, eps,
-                                                        bias_batch_stride, ft, st);
+                                                        bias_batch_stride, ft, lay, st);
         else done = launch_attn_keylanes(static_cast<const __half*>(Q), static_cast<const __half*>(K), static_cast<const __half*>(V),
-                                         bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
+                                         bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay, st);
         if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
     }
     if ((d == 4 || d == 8 || d == 16) && L >= 32) {
         bool done;
         if (elem == 0) done = launch_attn_rowthread(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
-                                                    bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
+                                                    bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay, st);
         else if (elem == 1) done = launch_attn_rowthread(static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
                                                          static_cast<const __nv_bfloat16*>(V), bias, O, LSE, B, H, L, Lk, d, causal, scale, eps,
-                                                         bias_batch_stride, ft, st);
+                                                         bias_batch_stride, ft, lay, st);
         else done = launch_attn_rowthread(static_cast<const __half*>(Q), static_cast<const __half*>(K), static_cast<const __half*>(V),
-                                          bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, st);
+                                          bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay, st);
         if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
     }
     dim3 grid((L + 3) / 4, H, B);
     const size_t smem = 4 * d * sizeof(float);
     if (elem == 0)
         attn_rowwarp_kernel<float><<<grid, 128, smem, st>>>(static_cast<const float*>(Q), static_cast<const float*>(K),
-            static_cast<const float*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft);
+            static_cast<const float*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay);
     else if (elem == 1)
         attn_rowwarp_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(Q),
             static_cast<const __nv_bfloat16*>(K), static_cast<const __nv_bfloat16*>(V), bias, O, LSE, H, L, Lk, d, causal,
-            scale, eps, bias_batch_stride, ft);
+            scale, eps, bias_batch_stride, ft, lay);
     else
         attn_rowwarp_kernel<__half><<<grid, 128, smem, st>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
-            static_cast<const __half*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft);
+            static_cast<const __half*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 

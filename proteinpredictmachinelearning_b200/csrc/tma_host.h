@@ -20,6 +20,11 @@ bool make_tmap_3d(CUtensorMap* out, TmaType type, const void* base,
                   uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,
                   uint32_t box0, uint32_t box1, int swizzle);
 
+// The same for a 4-D tensor [d3][d2][d1][d0] with arbitrary (16-byte multiple) strides of d1, d2 and d3; box0 x box1 x 1 x 1.
+// The strides need not be ordered: d1 may be the dimension with the largest stride.
+bool make_tmap_4d(CUtensorMap* out, TmaType type, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                  uint64_t stride1_bytes, uint64_t stride2_bytes, uint64_t stride3_bytes, uint32_t box0, uint32_t box1, int swizzle);
+
 inline int tma_elem_size(TmaType t) {
     switch (t) { case TmaType::F32: case TmaType::TF32: return 4; case TmaType::F16: case TmaType::BF16: return 2; default: return 1; }
 }

@@ -68,6 +68,18 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r; asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c)); return r;
 }
 
+// activation of a gate value, the reference's formulas (src/backend/CPUKernels.cpp:1903-1916)
+__device__ __forceinline__ float act_gate(int kind, float x) {
+    switch (kind) {
+        case 1: return 1.0f / (1.0f + expf(-x));
+        case 2: return x / (1.0f + expf(-x));
+        case 3: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        case 4: return tanhf(x);
+        case 5: return x > 0.0f ? x : 0.0f;
+        default: return x;
+    }
+}
+
 // two probabilities as one 32-bit word of the operand type, the first in the low half (the lower key index)
 template <int ELEM>
 __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
@@ -87,7 +99,11 @@ struct AttnParams {
     float* LSE;
     int q_tiles, k_tiles;
     int total_items;             // B * H * q_tiles
-    int o_align32;               // O is 32-byte aligned: rows can be written with 256-bit stores
+    int o_align32;               // O rows are 32-byte aligned: they can be written with 256-bit stores
+    long long o_b, o_h, o_l;     // element strides of O over batch, head and query row
+    long long g_b, g_h, g_l;     // the same for the gate
+    const float* gate;           // optional: O = act(gate) * O
+    int act;
     int ft_tiles;                // > 0: a row whose first ft_tiles key tiles hold only -inf scores gives O = 0, LSE = -inf,
                                  //      as the reference's CPU kernel does for its first key tile (src/ops/FlashAttn.cpp:94-121)
     int* err;
@@ -167,7 +183,7 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 // the Q tile is free once the score products of the previous item have been computed
                 if (!mbar_wait(q_empty, (ic & 1u) ^ 1u, cta_abort, p.err, 0x2100)) break;
                 mbar_arrive_expect_tx(q_full, kTileQ);
-                tma_load_3d(sb + kOffQ, &tmQ, q_full, 0, q0, bh);
+                tma_load_4d(sb + kOffQ, &tmQ, q_full, 0, q0, hh, b);
                 const int brow0 = hh * p.L + q0;                         // first bias row of this tile
                 const int bbatch = (p.bias_batch_stride != 0) ? b : 0;
                 for (int j = 0; j < k_tiles; ++j, ++tc) {
@@ -182,10 +198,10 @@ umma_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                     if (!mbar_wait(k_empty(s), ph ^ 1u, cta_abort, p.err, 0x2101)) { ok = false; break; }
                     mbar_arrive_expect_tx(k_full(s), kTileKV);
-                    tma_load_3d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, bh);
+                    tma_load_4d(sb + kOffK + s * kTileKV, &tmK, k_full(s), 0, j * kBN, hh, b);
                     if (!mbar_wait(v_empty(s), ph ^ 1u, cta_abort, p.err, 0x2102)) { ok = false; break; }
                     mbar_arrive_expect_tx(v_full(s), kTileKV);
-                    tma_load_3d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, bh);
+                    tma_load_4d(sb + kOffV + s * kTileKV, &tmV, v_full(s), 0, j * kBN, hh, b);
                 }
             }
         }
@@ -290,7 +306,7 @@ int launch_attn_elem(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUten
 // elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16 (bias, O and LSE are fp32 in every case)
 int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                      int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
-                     long long bias_batch_stride, int ft, cudaStream_t st) {
+                     long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st) {
     if (d != kD) return ST_UNSUPPORTED_PATH;
     if (ft < 0 || ft % kBN) return ST_UNSUPPORTED_PATH;       // the first-tile rule is checked per key tile of this kernel
     if (elem < 0 || elem > 2) return ST_BAD_ARGS;
@@ -307,18 +323,25 @@ int launch_umma_attn(const void* Q, const void* K, const void* V, int elem, cons
     const long long items = BH * p.q_tiles;
     if (items <= 0 || items > 0x7fffffffLL || Lk <= 0) return ST_BAD_ARGS;
     p.total_items = static_cast<int>(items);
-    p.o_align32 = (reinterpret_cast<uintptr_t>(O) & 31u) == 0 ? 1 : 0;
+    p.o_b = lay.o_b; p.o_h = lay.o_h; p.o_l = lay.o_l; p.gate = lay.gate; p.act = lay.act;
+    p.g_b = lay.g_b; p.g_h = lay.g_h; p.g_l = lay.g_l;
+    if ((lay.o_b | lay.o_h | lay.o_l) & 3) return ST_UNSUPPORTED_PATH;          // 16-byte rows at least
+    if (lay.gate && ((lay.g_b | lay.g_h | lay.g_l) & 3)) return ST_UNSUPPORTED_PATH;
+    if (lay.gate && (reinterpret_cast<uintptr_t>(lay.gate) & 15u)) return ST_UNSUPPORTED_PATH;
+    p.o_align32 = ((reinterpret_cast<uintptr_t>(O) & 31u) == 0 && ((lay.o_b | lay.o_h | lay.o_l) & 7) == 0 &&
+                   (!lay.gate || (reinterpret_cast<uintptr_t>(lay.gate) & 31u) == 0)) ? 1 : 0;
     p.ft_tiles = ft / kBN;
     const long long resident = static_cast<long long>(kCtasPerSm) * num_sms();     // persistent CTAs
     const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
     CUtensorMap tmQ, tmK, tmV, tmB;
     // fp32 rows are 128 bytes (128-byte swizzle; V in its 32-byte-chunk form), 16-bit rows 64 bytes (64-byte swizzle)
     const TmaType ty = elem == 0 ? TmaType::TF32 : (elem == 1 ? TmaType::BF16 : TmaType::F16);
-    const uint64_t row = static_cast<uint64_t>(kD) * (elem == 0 ? 4 : 2);
+    const uint64_t es = elem == 0 ? 4 : 2;
     const int sw_qk = elem == 0 ? 1 : 3, sw_v = elem == 0 ? 2 : 3;
-    if (!make_tmap_3d(&tmQ, ty, Q, kD, L, BH, row, static_cast<uint64_t>(L) * row, kD, kBM, sw_qk)) return ST_UNSUPPORTED_PATH;
-    if (!make_tmap_3d(&tmK, ty, K, kD, Lk, BH, row, static_cast<uint64_t>(Lk) * row, kD, kBN, sw_qk)) return ST_UNSUPPORTED_PATH;
-    if (!make_tmap_3d(&tmV, ty, V, kD, Lk, BH, row, static_cast<uint64_t>(Lk) * row, kD, kBN, sw_v)) return ST_UNSUPPORTED_PATH;
+    // dims (d, sequence row, head, batch), each with the stride the layout gives it
+    if (!make_tmap_4d(&tmQ, ty, Q, kD, L, H, B, lay.q_l * es, lay.q_h * es, lay.q_b * es, kD, kBM, sw_qk)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_4d(&tmK, ty, K, kD, Lk, H, B, lay.k_l * es, lay.k_h * es, lay.k_b * es, kD, kBN, sw_qk)) return ST_UNSUPPORTED_PATH;
+    if (!make_tmap_4d(&tmV, ty, V, kD, Lk, H, B, lay.v_l * es, lay.v_h * es, lay.v_b * es, kD, kBN, sw_v)) return ST_UNSUPPORTED_PATH;
     // bias rows are (head, query) pairs, [B or 1][H * L][Lk]; fp32 as it is (no tf32 rounding)
     tmB = tmQ;
     if (bias) {

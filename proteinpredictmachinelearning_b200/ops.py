@@ -217,6 +217,34 @@ def flash_attn_forward_cuda(Q, K, V, bias=None, scale=0.0, causal=False, eps=1e-
     return O, LSE
 
 
+def flash_attn_tokens(Q, K, V, heads, bias=None, gate=None, act="sigmoid", scale=0.0, causal=False, eps=1e-9, bias_bcast=False,
+                      path=PATH_AUTO, out=None, Bc=64):
+    """Attention on token-major operands: Q [B, L, >= heads*d] (a column range of a wider tensor is fine: the row stride is
+    taken from the tensor), K / V [B, Lk, ...]; O [B, L, heads*d] token-major; gate (optional, O's shape): act(gate) * O.
+    Returns (O, LSE [B, heads, L])."""
+    B, L, _ = Q.shape
+    Lk = K.shape[1]
+    assert Q.stride(2) == 1 and K.stride(2) == 1 and V.stride(2) == 1 and K.stride(1) == V.stride(1)
+    d = (out.shape[2] if out is not None else (gate.shape[2] if gate is not None else Q.shape[2])) // heads
+    hd = heads * d
+    O = torch.empty((B, L, hd), device=Q.device, dtype=torch.float32) if out is None else out
+    assert Q.stride(0) == Q.stride(1) * L and K.stride(0) == K.stride(1) * Lk and V.stride(0) == V.stride(1) * Lk
+    assert O.stride(2) == 1 and O.stride(0) == O.stride(1) * L
+    ld_g = 0
+    if gate is not None:
+        assert gate.stride(2) == 1 and gate.stride(0) == gate.stride(1) * L
+        ld_g = gate.stride(1)
+    LSE = torch.empty((B, heads, L), device=Q.device, dtype=torch.float32)
+    cfg = FlashCfg(B, heads, L, d, int(causal), float(scale), float(eps), 64, int(Bc))
+    if bias is not None:
+        bias = _f32c(bias)
+    stride = 0 if (bias is None or bias_bcast) else heads * L * Lk
+    rc = _lib.load().ppml_b200_flash_attn_forward_tokens(C.byref(cfg), Lk, stride, _p(Q), _p(K), _p(V), Q.stride(1), K.stride(1), _p(bias),
+                                                        _p(gate), ld_g, ACT[act], _p(O), O.stride(1), _p(LSE), path, _stream())
+    _check(rc, "flash_attn_forward_tokens")
+    return O, LSE
+
+
 def out_prod_cuda(s0, s1, path=PATH_AUTO):
     """s0 [ne03,ne02,K,ne00], s1 [ne13,ne12,K,ne10] (torch order = reversed graph dims) -> [ne3,ne2,ne10,ne00]."""
     s0, s1 = _f32c(s0), _f32c(s1)

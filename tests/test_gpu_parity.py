@@ -498,6 +498,41 @@ def test_attention_first_key_tile_masked(oracle, d, L, Lk, path):
     assert float((LSE2 - torch.logsumexp(s, dim=-1)).abs().max()) <= max(tol_l, 1e-4)
 
 
+@pytest.mark.parametrize("B,h,L,d,Lk,bias,path,tol,ltol", [
+    (3, 8, 256, 32, None, True, PATH_UMMA, TOL_TF32, 2e-3),      # main-track heads on the tensor cores
+    (2, 8, 51, 32, None, True, PATH_AUTO, TOL_FP32, 1e-5),       # dev size: 51 keys with a bias -> CUDA cores
+    (4, 8, 100, 8, None, True, PATH_AUTO, TOL_FP32, 1e-5),       # extra-MSA heads (d = 8): thread-per-row kernel
+    (5, 8, 1, 8, 64, False, PATH_AUTO, TOL_FP32, 1e-5),          # global column attention: one query, keys over lanes
+    (2, 4, 70, 64, 44, True, PATH_AUTO, TOL_FP32, 1e-5),         # generic kernel
+])
+def test_attention_on_token_major_operands_with_gate(oracle, B, h, L, d, Lk, bias, path, tol, ltol):
+    """The projections' outputs as they lie ([B][L][h*d], here as column ranges of one fused [B][L][4*h*d] buffer) in,
+    the gated, head-merged result out -- against the reference's chain: head-split permutes, fused attention in its own
+    layout, head-merge permute, act_mul(gate, merged, sigmoid)."""
+    from checkers import act_mul_f32
+    r = np.random.default_rng(B + L + d)
+    hd = h * d
+    Lk_ = L if Lk is None else Lk
+    qg = (r.standard_normal((B, L, 2 * hd)) / np.sqrt(32.0)).astype(np.float32)        # [q | gate logits]
+    kv = (r.standard_normal((B, Lk_, 2 * hd)) / np.sqrt(32.0)).astype(np.float32)      # [k | v]
+    qg[..., hd:] *= 4.0
+    bi = r.standard_normal((h, L, Lk_)).astype(np.float32) if bias else None
+    scale = 1 / np.sqrt(32.0)
+    split = lambda t, n: np.ascontiguousarray(t.reshape(t.shape[0], n, h, d).transpose(0, 2, 1, 3))   # [B][h][n][d]
+    rO, rL = oracle.flash_attn(split(qg[..., :hd], L), split(kv[..., :hd], Lk_), split(kv[..., hd:], Lk_), bi, scale=scale,
+                               bias_bcast=bias)
+    merged = np.ascontiguousarray(rO.transpose(0, 2, 1, 3)).reshape(B, L, hd)
+    ref = act_mul_f32(qg[..., hd:], merged, "sigmoid")
+    QG, KV = dev(qg), dev(kv)
+    O, LSE = ops.flash_attn_tokens(QG[..., :hd], KV[..., :hd], KV[..., hd:], h, bias=None if bi is None else dev(bi),
+                                   gate=QG[..., hd:], act="sigmoid", scale=scale, bias_bcast=bias, path=path)
+    assert cases.rel_err(host(O), ref) <= tol
+    assert np.abs(host(LSE) - rL).max() <= ltol
+    O2, _ = ops.flash_attn_tokens(QG[..., :hd], KV[..., :hd], KV[..., hd:], h, bias=None if bi is None else dev(bi),
+                                  scale=scale, bias_bcast=bias, path=path)             # without the gate
+    assert cases.rel_err(host(O2), merged) <= tol
+
+
 def test_attention_fully_masked_row():
     Q, K, V, bi = cases.attn_case(1, 1, 4, 8, seed=7)
     bi[0, 0, 2, :] = -np.inf
