@@ -253,6 +253,32 @@ int ppml_b200_outer_prod_mean_16(const void* left16, const void* right16, float*
 int ppml_b200_outer_prod_mean_slabs(const float* left, const float* right, float* dst, int64_t D_left, int64_t D,
                                     int64_t L, int64_t N, int64_t B, float inv_N, int path, void* stream);
 
+/* ---- exchanges of the sharded block over peer memory --------------------------------------------------
+ * No counterpart in the reference (it has no multi-GPU path).  One process per GPU; buffers that peers write into and
+ * the flag block are plain device allocations shared through CUDA IPC at set-up:
+ *   p = ppml_b200_peer_alloc(bytes) (zero-filled), ppml_b200_peer_export(p, handle[64]) -> send the 64 bytes to the other
+ *   ranks by any means -> q = ppml_b200_peer_open(handle) maps a peer's allocation (ppml_b200_peer_close / _free at the end).
+ * dst_ptrs / out_ptrs / flag_ptrs are host arrays of `world` device pointers, entry r = rank r's buffer as mapped in THIS
+ * process (entry `rank` = the local allocation).  Flag blocks hold ppml_b200_peer_flag_bytes() bytes.  `site` (0..15)
+ * names the exchange inside the block: every site has its own flags and epoch, and all ranks must run the same sequence of
+ * sites.  Each call is one kernel on `stream`: arrive round, plain stores into the peers' buffers, landed round; when it
+ * has run, this rank's own buffer is complete and every later kernel on the stream may read it (locally).  A launch can
+ * be recorded in a CUDA graph.  Waits are bounded: a rank whose peers do not show up within about 1.5 s leaves status 8 in
+ * the device error word (ppml_b200_device_status) and returns.  world <= 8.
+ *   all_gather: `bytes_per_rank` (multiple of 16) from src to offset rank * bytes_per_rank of every rank's buffer.
+ *   transpose:  x [n_loc][L][C] fp32, this rank's n range of an [n][l][C] activation -> out [L / world][world * n_loc][C] on
+ *               the rank that owns l: the reference's (n, l) permute copies (src/modules/Attention.cpp:489, :744). */
+int ppml_b200_peer_flag_bytes(void);
+void* ppml_b200_peer_alloc(int64_t bytes);
+void ppml_b200_peer_free(void* p);
+int ppml_b200_peer_export(void* p, void* handle64);
+void* ppml_b200_peer_open(const void* handle64);
+void ppml_b200_peer_close(void* p);
+int ppml_b200_peer_all_gather(const void* src, void* const* dst_ptrs, int64_t bytes_per_rank, int rank, int world,
+                              void* const* flag_ptrs, int site, void* stream);
+int ppml_b200_peer_transpose(const float* x, void* const* out_ptrs, int n_loc, int L, int C, int rank, int world,
+                             void* const* flag_ptrs, int site, void* stream);
+
 /* ---- per-shape statistics ----------------------------------------------------------------------------
  * Replace mulmat_stats_cuda_begin / mulmat_stats_cuda_end (src/backend/CUDAKernels.cpp:190-191;
  * src/cuda/CUDAKernels.cu:1693-1732): event pair around one launch, totals per (path, M, K, N).

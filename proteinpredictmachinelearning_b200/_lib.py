@@ -64,6 +64,14 @@ SIGNATURES = {
     "ppml_b200_set_q8_two_pass": (None, [_i]),
     "ppml_b200_q8_kernel_launches": (_i, [_i, _i, _i]),
     "ppml_b200_outer_prod_mean_slabs": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f, _i, _vp]),
+    "ppml_b200_peer_flag_bytes": (_i, []),
+    "ppml_b200_peer_alloc": (_vp, [_i64]),
+    "ppml_b200_peer_free": (None, [_vp]),
+    "ppml_b200_peer_export": (_i, [_vp, _vp]),
+    "ppml_b200_peer_open": (_vp, [_vp]),
+    "ppml_b200_peer_close": (None, [_vp]),
+    "ppml_b200_peer_all_gather": (_i, [_vp, C.POINTER(_vp), _i64, _i, _i, C.POINTER(_vp), _i, _vp]),
+    "ppml_b200_peer_transpose": (_i, [_vp, C.POINTER(_vp), _i, _i, _i, _i, _i, C.POINTER(_vp), _i, _vp]),
     "ppml_b200_mulmat_stats_begin": (None, [_i, _i, _i]),
     "ppml_b200_mulmat_stats_end": (None, [C.c_char_p]),
     "ppml_b200_mulmat_stats_dump": (_i, [C.c_char_p, _i]),

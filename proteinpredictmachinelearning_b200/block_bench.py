@@ -48,9 +48,13 @@ class Block:
     """The op sequence for one rank of a G-way partition (G = 1: the unsharded block).  Inputs and weights are shared
     between instances; every instance owns its outputs."""
 
-    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev):
+    SITES = {"mr_bias": 0, "col_t": 1, "right": 2, "pr_bias": 3, "row_t": 4, "pc_bias": 5}
+
+    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None):
         self.torch, self.dist, self.ops = torch, dist, ops
         self.inp, self.weights, self.G, self.rank, self.dev = inputs, weights, G, rank, dev
+        self.peers = peers if G > 1 else None      # shard.PeerBuffers: exchanges as single kernels over peer memory
+        self.peer_ptrs = {}
         self.out = {}            # named results of the last run
         self.bufs = {}           # tensors that keep their address from step to step
         self.timers = {}
@@ -105,6 +109,12 @@ class Block:
         """All-gather of the ranks' contiguous row ranges (rank order = row order)."""
         if self.G == 1:
             return x
+        if self.peers is not None:
+            key = "ag_" + tag
+            if key not in self.bufs:
+                self.bufs[key], self.peer_ptrs[key] = self.peers.tensor((x.shape[0] * self.G,) + tuple(x.shape[1:]))
+            self.peers.all_gather(x, self.peer_ptrs[key], self.SITES[tag])
+            return self.bufs[key]
         full = self.buf("ag_" + tag, (x.shape[0] * self.G,) + tuple(x.shape[1:]))
         self.dist.all_gather_into_tensor(full, x)
         return full
@@ -121,6 +131,12 @@ class Block:
             out.copy_(x3.permute(1, 0, 2))
             return out.view(l_tot * n_loc, C)
         l_loc = l_tot // G
+        if self.peers is not None:
+            key = "tr_" + tag
+            if key not in self.bufs:
+                self.bufs[key], self.peer_ptrs[key] = self.peers.tensor((l_loc, G * n_loc, C))
+            self.peers.transpose(x, self.peer_ptrs[key], n_loc, l_tot, C, self.SITES[tag])
+            return self.bufs[key].view(l_loc * G * n_loc, C)
         send = self.buf("trs_" + tag, (G, n_loc, l_loc, C))
         send.copy_(x3.view(n_loc, G, l_loc, C).permute(1, 0, 2, 3))          # [to rank][n][l][c]
         recv = self.buf("trr_" + tag, (G, n_loc, l_loc, C))
@@ -324,7 +340,25 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
         if total % G:
             return {"unavailable": f"{G} ranks do not divide the block's partitions"}
     inputs, weights = make_inputs_and_weights(torch, ops, dev)
-    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev)
+    # exchanges: single kernels over peer memory (CUDA IPC) by default, NCCL collectives launched from the host when
+    # that cannot be set up or PPML_B200_EXCHANGE=nccl asks for them
+    peers, exchange_mode = None, "none (one rank)"
+    if G > 1:
+        exchange_mode = "nccl collectives launched from the host"
+        if os.environ.get("PPML_B200_EXCHANGE", "peer") != "nccl":
+            from proteinpredictmachinelearning_b200 import shard
+            try:
+                peers = shard.PeerBuffers(G, rank)
+                good = 1
+            except Exception:
+                peers, good = None, 0
+            flag = torch.tensor([good], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                peers = None
+            else:
+                exchange_mode = "one kernel per exchange: stores into the peers' buffers between two flag rounds"
+    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev, peers=peers)
 
     def barrier():
         if G > 1:
@@ -380,26 +414,44 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
     eager_ms = e0.elapsed_time(e1) / steps
     graph_ms, graph_note = None, ""
     if use_graph:
-        graphs = []
-        segments, _ = blk.plan()
-        for seg in segments:                 # no collective is ever captured; a segment that cannot be captured stays eager
+        whole = None
+        if G == 1 or peers is not None:
+            # no NCCL call inside: the whole block (compute and exchange kernels) is one graph
             try:
-                gr = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gr):
-                    seg()
-                graphs.append(gr)
+                whole = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(whole):
+                    blk.run()
             except Exception as exc:
-                graphs.append(None)
-                graph_note = f"a segment stayed eager: {type(exc).__name__}"
+                whole, graph_note = None, f"whole-block capture failed: {type(exc).__name__}"
+            if G > 1:                        # all ranks replay, or none does
+                flag = torch.tensor([1 if whole is not None else 0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) == 0:
+                    whole = None
+        graphs = []
+        if whole is None:
+            segments, _ = blk.plan()
+            for seg in segments:             # no collective is ever captured; a segment that cannot be captured stays eager
+                try:
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        seg()
+                    graphs.append(gr)
+                except Exception as exc:
+                    graphs.append(None)
+                    graph_note = f"a segment stayed eager: {type(exc).__name__}"
+        step = whole.replay if whole is not None else (lambda: blk.run(graphs))
         for _ in range(2):
-            blk.run(graphs)
+            step()
         barrier()
         e0.record()
         for _ in range(steps):
-            blk.run(graphs)
+            step()
         e1.record()
         barrier()
         graph_ms = e0.elapsed_time(e1) / steps
+        if whole is not None:
+            graph_note = "the whole block is one graph"
         code, where = ops.device_status()
         if code != 0:
             raise RuntimeError(f"device abort {code} at {where:#x}")
@@ -409,11 +461,18 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
     if G > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     total_split = sum(split.values()) or 1.0
+    if peers is not None:
+        torch.cuda.synchronize()
+        if G > 1:
+            dist.barrier()
+        blk.bufs.clear()
+        peers.close()
     return {"metric": "main IterBlock hot-path ops, ms per block", "ms_per_block": float(ms[0].item()), "unit": "ms",
             "ms_per_32_blocks": float(ms[0].item()) * 32, "eager_ms": float(ms[1].item()), "n_gpus": G, "steps": steps,
             "scaling": "strong", "higher_is_better": False, "dtype": "q8 + tf32, fp32 accumulate", "data": "synthetic, seed 5",
-            "launch": ("cuda graphs for the compute segments, collectives from the host" + (" (" + graph_note + ")" if graph_note else ""))
+            "launch": ("cuda graphs" + (" (" + graph_note + ")" if graph_note else " for the compute segments, collectives from the host"))
                       if graph_ms is not None else "eager",
+            "exchange": exchange_mode,
             "workload": "one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads; 26 Q8 Linears, 18 fp32 Linears, "
                         "4 attention calls, 2 tri_mul, 1 outer-product-mean",
             "split_ms_rank0": {k: round(v, 4) for k, v in sorted(split.items())},

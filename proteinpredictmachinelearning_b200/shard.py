@@ -88,3 +88,81 @@ def transpose_exchange(x_local, world, group=None):
     recv = send.new_empty(send.shape)                                                    # [from rank][n][l][c]
     dist.all_to_all_single(recv, send, group=group)
     return recv.permute(2, 0, 1, 3).reshape(l_loc, world * n_loc, C).contiguous()
+
+
+class PeerBuffers:
+    """Device buffers that the other ranks of the box write into directly (csrc/peer_exchange.cu): allocated by the
+    library, shared once through CUDA IPC handles sent over the process group, wrapped as torch tensors for local use."""
+
+    def __init__(self, world, rank, group=None):
+        import ctypes as C
+        from . import _lib
+        self.C, self.lib = C, _lib.load()
+        self.world, self.rank, self.group = world, rank, group
+        self.local, self.mapped = [], []
+        self.flags = self._share(self.lib.ppml_b200_peer_flag_bytes())
+
+    def _share(self, nbytes):
+        """Allocates `nbytes` here, maps every peer's allocation of the same call; returns (local pointer, ctypes array of
+        `world` pointers with entry `rank` = local)."""
+        import torch.distributed as dist
+        C = self.C
+        p = self.lib.ppml_b200_peer_alloc(int(nbytes))
+        if not p:
+            raise RuntimeError("peer_alloc failed")
+        self.local.append(p)
+        ptrs = [None] * self.world
+        ptrs[self.rank] = p
+        if self.world > 1:
+            h = C.create_string_buffer(64)
+            if self.lib.ppml_b200_peer_export(C.c_void_p(p), h) != 0:
+                raise RuntimeError("peer_export failed")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(h.raw), group=self.group)
+            for r in range(self.world):
+                if r != self.rank:
+                    q = self.lib.ppml_b200_peer_open(C.create_string_buffer(handles[r], 64))
+                    if not q:
+                        raise RuntimeError(f"peer_open failed for rank {r}")
+                    self.mapped.append(q)
+                    ptrs[r] = q
+        return p, (C.c_void_p * self.world)(*ptrs)
+
+    def tensor(self, shape, dtype=None):
+        """A zero-filled fp32 tensor in shared memory: (local torch view, peer pointer array)."""
+        import math
+        import torch
+        nbytes = 4 * math.prod(shape)
+        p, arr = self._share((nbytes + 255) // 256 * 256)
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (p, False), "version": 2}
+        return torch.as_tensor(_Raw(), device="cuda"), arr
+
+    def _stream(self, stream):
+        import torch
+        if stream is not None:
+            return stream
+        s = torch.cuda.current_stream().cuda_stream       # the capture stream while a CUDA graph is being recorded
+        return self.C.c_void_p(s) if s else None
+
+    def all_gather(self, x, dst_ptrs, site, stream=None):
+        stream = self._stream(stream)
+        rc = self.lib.ppml_b200_peer_all_gather(self.C.c_void_p(x.data_ptr()), dst_ptrs, x.numel() * x.element_size(), self.rank, self.world,
+                                                self.flags[1], site, stream)
+        if rc != 0:
+            raise RuntimeError(f"peer_all_gather failed with status {rc}")
+
+    def transpose(self, x, out_ptrs, n_loc, L, Cc, site, stream=None):
+        stream = self._stream(stream)
+        rc = self.lib.ppml_b200_peer_transpose(self.C.c_void_p(x.data_ptr()), out_ptrs, n_loc, L, Cc, self.rank, self.world,
+                                               self.flags[1], site, stream)
+        if rc != 0:
+            raise RuntimeError(f"peer_transpose failed with status {rc}")
+
+    def close(self):
+        for q in self.mapped:
+            self.lib.ppml_b200_peer_close(self.C.c_void_p(q))
+        for p in self.local:
+            self.lib.ppml_b200_peer_free(self.C.c_void_p(p))
+        self.mapped, self.local = [], []

@@ -127,3 +127,33 @@ def test_split_properties():
                 assert all(lo % align == 0 or lo == total for lo, _ in parts)
     with pytest.raises(ValueError):
         shard.split(10, 2, 2)
+
+
+@pytest.mark.gpu
+def test_peer_exchange_kernels_on_one_rank():
+    """The exchange kernels with a world of one rank (the flag rounds see only the rank itself): the all-gather is a copy,
+    the (n, l) transpose a local transpose; repeated launches advance the epoch, also when replayed from a CUDA graph."""
+    from proteinpredictmachinelearning_b200 import ops, shard
+    peers = shard.PeerBuffers(1, 0)
+    try:
+        g = torch.Generator(device="cuda").manual_seed(1)
+        x = torch.randn((6, 8, 12), device="cuda", generator=g)
+        out, out_ptrs = peers.tensor((8, 6, 12))
+        gat, gat_ptrs = peers.tensor((6, 8, 12))
+        for _ in range(3):
+            peers.transpose(x, out_ptrs, 6, 8, 12, site=1)
+            peers.all_gather(x, gat_ptrs, site=0)
+        torch.cuda.synchronize()
+        assert torch.equal(out, x.permute(1, 0, 2).contiguous()) and torch.equal(gat, x)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            peers.transpose(x, out_ptrs, 6, 8, 12, site=1)
+        x.mul_(2.0)
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, x.permute(1, 0, 2).contiguous())
+        assert ops.device_status() == (0, 0)
+        del out, gat
+    finally:
+        peers.close()
