@@ -677,8 +677,8 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one pass of the sweep (36 launches of umma_q8_kernel) from one ncu
 # capture on a B200, divided by 36; the capture command and the per-launch figures are in
-# profiles/q8_sweep_dram_traffic.md.  Below the algorithmic bytes: part of each result is still in L2 at kernel end.
-Q8_SWEEP_DRAM_BYTES_PER_LAUNCH = 71.8e6
+# profiles/q8_sweep_launches_and_dram.md.  Below the algorithmic bytes: part of each result is still in L2 at kernel end.
+Q8_SWEEP_DRAM_BYTES_PER_LAUNCH = 76.4e6
 
 
 def single_kernel(args):
