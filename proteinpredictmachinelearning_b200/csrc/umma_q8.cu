@@ -60,6 +60,8 @@ struct Q8Params {
     int* sumi_out;
     int c_trans;
     int vec_ok;
+    int vec32_ok;              // C rows and base 32-byte aligned: the unstaged store writes whole 128-byte lines (256-bit stores)
+    int dw_vec;                // K a multiple of 256 and aligned scales: the table refill reads eight scales per 16-byte load
     int* err;
 };
 
@@ -547,18 +549,37 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     // this thread's share of the table (column etid % 128, every fourth block): the global loads are
                     // issued before the wait for the other warps, so their latency hides behind it
                     float wv[kMaxKT];
-                    {
-                        const int col = etid & 127, mo = nb * 128 + col;
+                    const int col = etid & 127, mo = nb * 128 + col;
+                    if (p.dw_vec) {
+                        // eight consecutive blocks of one column per thread: one 16-byte load
+                        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+                        const int kb0 = (etid >> 7) * 8;
+                        if (mo < p.Mout && kb0 < p.nblk)
+                            raw = __ldg(reinterpret_cast<const uint4*>(p.Wd + static_cast<size_t>(mo) * p.nblk + kb0));
+                        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            wv[2 * t] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] & 0xffffu))) * kTwo49;
+                            wv[2 * t + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] >> 16))) * kTwo49;
+                        }
+                    } else {
                         const __half* src = p.Wd + static_cast<size_t>(mo) * p.nblk + (etid >> 7);
 #pragma unroll
                         for (int t = 0; t < kMaxKT; ++t)
                             wv[t] = (mo < p.Mout && 4 * t + (etid >> 7) < p.nblk) ? __half2float(src[4 * t]) * kTwo49 : 0.0f;
                     }
                     if (!mbar_wait(dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
+                    if (p.dw_vec) {
+                        const int kb0 = (etid >> 7) * 8;
 #pragma unroll
-                    for (int t = 0; t < kMaxKT; ++t) {
-                        const int i = etid + t * (32 * kEpiWarps);
-                        if (i < p.nblk * 128) dw_s[i] = wv[t];
+                        for (int t = 0; t < kMaxKT; ++t)
+                            if (kb0 + t < p.nblk) dw_s[(kb0 + t) * 128 + col] = wv[t];
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < kMaxKT; ++t) {
+                            const int i = etid + t * (32 * kEpiWarps);
+                            if (i < p.nblk * 128) dw_s[i] = wv[t];
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(dw_full);
@@ -725,8 +746,16 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 if (!dw_resident) { __syncwarp(); if (lane == 0) mbar_arrive(dw_free); ++dwcnt; }
                 const int mo0 = nb * 128 + cg * 32;
                 if (p.bias != nullptr) {
+                    if (mo0 + 32 <= p.Mout && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + mo0 + j));
+                            acc[j] += b4.x; acc[j + 1] += b4.y; acc[j + 2] += b4.z; acc[j + 3] += b4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
+                    }
                 }
                 if (p.c_trans && p.staged) {
                     // Asynchronous stores, `staged` columns at a time: thread = row writes its 16-byte chunks into the warp's
@@ -759,6 +788,39 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     if (p.staged == 16) store_cols(std::integral_constant<int, 16>{});
                     else if (p.staged == 8) store_cols(std::integral_constant<int, 8>{});
                     else store_cols(std::integral_constant<int, 32>{});
+                } else if (p.vec32_ok && mo0 + 32 <= p.Mout) {
+                    // No room for store buffers (K = 1024: the resident A tile).  A thread holds 32 consecutive floats of
+                    // its row; stored as they lie, every store instruction would touch 32 different lines with 16 bytes each
+                    // and the load/store unit takes one line per cycle.  Two exchange steps over the lane bits 3-4 regroup
+                    // the data so that lane l holds, for s = 0..3, the 32-byte piece (l >> 3) of row 8 s + (l & 7): a store
+                    // instruction then writes eight whole 128-byte lines.
+#pragma unroll
+                    for (int st = 0; st < 2; ++st) {
+                        const int lbit = 8 << st, pbit = 8 << st;          // lane bit 3 + st pairs with piece bit st (8 or 16 floats)
+                        const bool up = (lane & lbit) != 0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if ((j & pbit) == 0) {
+                                // the lane with the bit clear keeps piece j and sends j + pbit; its partner the reverse
+                                const float send = up ? acc[j] : acc[j + pbit];
+                                const float got = __shfl_xor_sync(0xffffffffu, send, lbit);
+                                if (up) acc[j] = got; else acc[j + pbit] = got;
+                            }
+                        }
+                    }
+                    const int piece = lane >> 3;
+#pragma unroll
+                    for (int s4 = 0; s4 < 4; ++s4) {
+                        // register group s4 now holds floats 8 * piece .. 8 * piece + 7 of row (lane & 7) + 8 * s4
+                        const int r = q * 32 + (lane & 7) + 8 * s4;
+                        const int t2 = mt * 128 + r;
+                        if (t2 < p.Ntok) {
+                            float* dst = p.C + static_cast<size_t>(t2) * p.Mout + mo0 + 8 * piece;
+                            asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst),
+                                         "f"(acc[8 * s4]), "f"(acc[8 * s4 + 1]), "f"(acc[8 * s4 + 2]), "f"(acc[8 * s4 + 3]),
+                                         "f"(acc[8 * s4 + 4]), "f"(acc[8 * s4 + 5]), "f"(acc[8 * s4 + 6]), "f"(acc[8 * s4 + 7]) : "memory");
+                        }
+                    }
                 } else if (tok < p.Ntok) {
                     if (p.c_trans) {
                         float* dst = p.C + static_cast<size_t>(tok) * p.Mout + mo0;
@@ -823,6 +885,7 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     p.blocks_per_group = (p.n_blocks + groups - 1) / groups;
     p.groups = (p.n_blocks + p.blocks_per_group - 1) / p.blocks_per_group;
     p.vec_ok = c_trans && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) && (M % 4 == 0);
+    p.vec32_ok = c_trans && ((reinterpret_cast<uintptr_t>(C) & 31u) == 0) && (M % 8 == 0);
     // Shared memory: the quantized A tile and the activation-scale table are fixed; then, in this order of
     // preference, a second A tile (the next item is quantized while this one multiplies), the scale tables
     // of all column blocks (no refill, at most 32 KB), the per-warp store buffers; what is left goes to the
@@ -863,6 +926,7 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     if (p.BS > kMaxStages) p.BS = kMaxStages;
     const __half* Wd = reinterpret_cast<const __half*>(static_cast<const int8_t*>(W) + static_cast<size_t>(M) * p.nblk * 32);
     p.Wd = Wd; p.C = C; p.bias = bias; p.sumi_out = sumi_out; p.c_trans = c_trans; p.err = err;
+    p.dw_vec = (p.nblk % 8 == 0) && ((reinterpret_cast<uintptr_t>(Wd) & 15u) == 0);
 
     CUtensorMap tmX, tmW, tmC;
     if (p.preq) {
