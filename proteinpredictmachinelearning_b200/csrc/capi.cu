@@ -70,13 +70,17 @@ void* ensure_scratch(int kind, size_t bytes, cudaStream_t st) {
 // tiles than SMs (33 vs 44 us at 65536 x 128 x 128, 126 vs 197 us at 65536 x 1024 x 128: the extra pass over X costs
 // more than the quantizer warps do); with few token tiles and a long K the in-kernel quantizer is a serial chain of
 // K / 32 steps on two or four warps, and the two-pass form wins (33 vs 41 us at 408 x 1024 x N, 58 vs 68 us at
-// 2601 x 1024 x 1024).  PPML_B200_Q8_TWO_PASS=0 / 1 or ppml_b200_set_q8_two_pass() force the choice (measurements, tests).
+// 2601 x 1024 x 1024).  M = weight rows, N = tokens.  PPML_B200_Q8_TWO_PASS=0 / 1 or ppml_b200_set_q8_two_pass() force the choice (measurements, tests).
 int g_q8_two_pass = [] { const char* e = std::getenv("PPML_B200_Q8_TWO_PASS"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
 bool q8_two_pass(int M, int N, int K) {
     const int forced = g_q8_two_pass;
     if (forced >= 0) return forced == 1;
-    (void)M;
-    return (N + 127) / 128 <= num_sms() && K >= 1024;
+    // K >= 1024: the quantized A tile fills the shared memory, and the one-pass form has no room for its result store
+    // buffers.  With two or more weight column blocks the two-pass form, which needs no raw activation stages and keeps
+    // the buffers, is faster although it reads the activations twice (442 vs 495 us at 65536 x 1024 x 1024, 258 vs 291 at
+    // 512 weight rows, 165 vs 168 at 256; 126 vs 110 at 128).
+    if (K < 1024) return false;
+    return (N + 127) / 128 <= num_sms() || M >= 256;
 }
 
 struct FusedEpi { const float* ln_stats = nullptr; const float* ln_u = nullptr; const float* gate = nullptr; int act = 0; };

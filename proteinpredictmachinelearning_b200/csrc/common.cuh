@@ -167,6 +167,8 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src_smem
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until the bulk stores committed by this thread have finished reading shared memory (the buffers may be reused)
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// the same, but the most recently committed group may still be reading (two buffers used in turn)
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // waits until the bulk stores committed by this thread are complete
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

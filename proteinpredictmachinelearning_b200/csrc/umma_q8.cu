@@ -49,6 +49,8 @@ struct Q8Params {
     int AR;                    // 16 KB slots of quantized A, used as a ring over (item, K step): KT = resident, 2 KT = resident
                                // and double-buffered across items, 3 = a short ring (items with a single column block)
     int dw_tabs;               // scale tables held in smem: n_blocks (all resident, filled once) or 1 (refilled per column block)
+    int st_box;                // columns of one TMA store (the box width): `staged`, or half of it when the buffer is used
+                               // as two halves in turn (a half is refilled while the store of the other half still reads)
     int staged;                // columns of the per-warp store buffer (32 rows x staged fp32: 8, 16 or 32; the results leave
                                // through TMA stores), 0: plain stores from registers
     int preq;                  // 1: the activations were quantized by a kernel of their own: int8 tiles and scale tables
@@ -258,6 +260,76 @@ quantize_q8_planar_kernel(const float* __restrict__ X, int8_t* __restrict__ Aq, 
         *reinterpret_cast<uint32_t*>(Aq + off) = pack_s8(qi[1], qi[0], pack_s8(qi[3], qi[2], 0u));
     }
     if (sub == 0) da_t[(static_cast<size_t>(row >> 7) * nblk + kb) * 128 + (row & 127)] = __float2half_rn(d);
+}
+
+// The same quantizer for K a multiple of 128, built for bandwidth: a CTA takes a tile of 128 token rows x KW elements
+// (KW = 128 or 256); a thread handles 32-byte pieces (eight values, four threads per quant block), consecutive threads
+// consecutive pieces of a row, so a warp reads 1 KB and writes 256 bytes contiguously, with four pieces per thread in
+// flight.  The scales of the tile go through shared memory and leave as KW / 32 contiguous rows of 128.
+template <int KW>
+__global__ void __launch_bounds__(256)
+quantize_q8_planar_tile_kernel(const float* __restrict__ X, int8_t* __restrict__ Aq, __half* __restrict__ da_t,
+                               int Ntok, int K, int nblk) {
+    constexpr int NB = KW / 32;                   // quant blocks per row of the tile
+    constexpr int PIECES = 128 * KW / 8;          // 32-byte pieces in the tile
+    constexpr int ITERS = PIECES / 256;
+    __shared__ __half sc[NB][128];
+    const int tile_row0 = blockIdx.y * 128, k0 = blockIdx.x * KW;
+#pragma unroll 4
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = it * 256 + threadIdx.x;
+        const int r = c / (KW / 8), pc = c % (KW / 8);            // row in the tile, piece in the row
+        const int row = tile_row0 + r;
+        const bool live = row < Ntok;
+        const size_t off = static_cast<size_t>(row) * K + k0 + pc * 8;
+        float x[8];
+        if (live) {
+            const float4 v0 = __ldg(reinterpret_cast<const float4*>(X + off));
+            const float4 v1 = __ldg(reinterpret_cast<const float4*>(X + off + 4));
+            x[0] = v0.x; x[1] = v0.y; x[2] = v0.z; x[3] = v0.w; x[4] = v1.x; x[5] = v1.y; x[6] = v1.z; x[7] = v1.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] = 0.0f;
+        }
+        const int sub = pc & 3;
+        float amax = fabsf(x[0]), vmax = x[0];
+        int idx = sub * 8;
+#pragma unroll
+        for (int e = 1; e < 8; ++e) {
+            if (fabsf(x[e]) > amax) { amax = fabsf(x[e]); vmax = x[e]; idx = sub * 8 + e; }
+        }
+#pragma unroll
+        for (int o = 2; o > 0; o >>= 1) {
+            const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+            const float ov = __shfl_xor_sync(0xffffffffu, vmax, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oa > amax || (oa == amax && oi < idx)) { amax = oa; vmax = ov; idx = oi; }
+        }
+        const float d = (amax == 0.0f) ? 0.0f : vmax * -0.0078125f;
+        const float inv = (d == 0.0f) ? 0.0f : 1.0f / d;
+        if (live) {
+            int qi[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float y = x[e] * inv;
+                float t;
+                asm("add.rz.f32 %0, %1, %2;" : "=f"(t) : "f"(y), "f"(copysignf(0.5f, y)));
+                qi[e] = f2i_rz(t);
+            }
+            uint2 o2;
+            o2.x = pack_s8(qi[1], qi[0], pack_s8(qi[3], qi[2], 0u));
+            o2.y = pack_s8(qi[5], qi[4], pack_s8(qi[7], qi[6], 0u));
+            *reinterpret_cast<uint2*>(Aq + off) = o2;
+        }
+        if (sub == 0) sc[pc >> 2][r] = __float2half_rn(live ? d : 0.0f);
+    }
+    __syncthreads();
+    // NB rows of 128 scales: [token tile][kb][128]
+    for (int i = threadIdx.x; i < NB * 64; i += 256) {
+        const int kb = i >> 6, pr = i & 63;
+        const __half2 h2 = *reinterpret_cast<const __half2*>(&sc[kb][2 * pr]);
+        *reinterpret_cast<__half2*>(da_t + (static_cast<size_t>(blockIdx.y) * nblk + blockIdx.x * NB + kb) * 128 + 2 * pr) = h2;
+    }
 }
 
 template <bool SUMI, int QW>      // SUMI: also write the raw int32 block sums (tests); QW: quantizer warps
@@ -536,6 +608,48 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (lane == 0) mbar_arrive(dw_full);
             if (!mbar_wait(dw_full, 0u, cta_abort, p.err, 0x1404)) ok = false;
         }
+        // Refill of the weight-scale table (when the tables of all column blocks do not fit): this thread's share of
+        // column block `nbx` is read from global memory into registers ...
+        auto dw_load = [&](int nbx, float (&wv)[kMaxKT]) {
+            const int col = etid & 127, mo = nbx * 128 + col;
+            if (p.dw_vec) {
+                // eight consecutive blocks of one column per thread: one 16-byte load
+                uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+                const int kb0 = (etid >> 7) * 8;
+                if (mo < p.Mout && kb0 < p.nblk)
+                    raw = __ldg(reinterpret_cast<const uint4*>(p.Wd + static_cast<size_t>(mo) * p.nblk + kb0));
+                const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    wv[2 * t] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] & 0xffffu))) * kTwo49;
+                    wv[2 * t + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] >> 16))) * kTwo49;
+                }
+            } else {
+                const __half* src = p.Wd + static_cast<size_t>(mo) * p.nblk + (etid >> 7);
+#pragma unroll
+                for (int t = 0; t < kMaxKT; ++t)
+                    wv[t] = (mo < p.Mout && 4 * t + (etid >> 7) < p.nblk) ? __half2float(src[4 * t]) * kTwo49 : 0.0f;
+            }
+        };
+        // ... and written to shared memory once every epilogue warp has finished with the table before it.
+        auto dw_publish = [&](const float (&wv)[kMaxKT]) -> bool {
+            if (!mbar_wait(dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) return false;
+            if (p.dw_vec) {
+                const int col = etid & 127, kb0 = (etid >> 7) * 8;
+#pragma unroll
+                for (int t = 0; t < kMaxKT; ++t)
+                    if (kb0 + t < p.nblk) dw_s[(kb0 + t) * 128 + col] = wv[t];
+            } else {
+#pragma unroll
+                for (int t = 0; t < kMaxKT; ++t) {
+                    const int i = etid + t * (32 * kEpiWarps);
+                    if (i < p.nblk * 128) dw_s[i] = wv[t];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dw_full);
+            return true;
+        };
         int mt = 0, nb0 = 0, nb1 = 0;
         for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
             const int tok = mt * 128 + row;
@@ -546,43 +660,13 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 // wait until every epilogue warp has finished with the previous one, fill, publish.
                 const uint32_t dw_a0 = smem_base + L.dw_off + ((p.dw_tabs > 1 ? nb : 0) * p.nblk * 128 + cg * 32) * 4;
                 if (!dw_resident) {
-                    // this thread's share of the table (column etid % 128, every fourth block): the global loads are
-                    // issued before the wait for the other warps, so their latency hides behind it
-                    float wv[kMaxKT];
-                    const int col = etid & 127, mo = nb * 128 + col;
-                    if (p.dw_vec) {
-                        // eight consecutive blocks of one column per thread: one 16-byte load
-                        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-                        const int kb0 = (etid >> 7) * 8;
-                        if (mo < p.Mout && kb0 < p.nblk)
-                            raw = __ldg(reinterpret_cast<const uint4*>(p.Wd + static_cast<size_t>(mo) * p.nblk + kb0));
-                        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            wv[2 * t] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] & 0xffffu))) * kTwo49;
-                            wv[2 * t + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] >> 16))) * kTwo49;
-                        }
-                    } else {
-                        const __half* src = p.Wd + static_cast<size_t>(mo) * p.nblk + (etid >> 7);
-#pragma unroll
-                        for (int t = 0; t < kMaxKT; ++t)
-                            wv[t] = (mo < p.Mout && 4 * t + (etid >> 7) < p.nblk) ? __half2float(src[4 * t]) * kTwo49 : 0.0f;
+                    // The first column block of an item fills the table here; the later ones were filled at the end of the
+                    // block before them (loads issued before its result stores, table written after them).
+                    if (nb == nb0) {
+                        float wv[kMaxKT];
+                        dw_load(nb, wv);
+                        if (!dw_publish(wv)) { ok = false; break; }
                     }
-                    if (!mbar_wait(dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) { ok = false; break; }
-                    if (p.dw_vec) {
-                        const int kb0 = (etid >> 7) * 8;
-#pragma unroll
-                        for (int t = 0; t < kMaxKT; ++t)
-                            if (kb0 + t < p.nblk) dw_s[(kb0 + t) * 128 + col] = wv[t];
-                    } else {
-#pragma unroll
-                        for (int t = 0; t < kMaxKT; ++t) {
-                            const int i = etid + t * (32 * kEpiWarps);
-                            if (i < p.nblk * 128) dw_s[i] = wv[t];
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(dw_full);
                     if (!mbar_wait(dw_full, dwcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
                 }
                 float acc[32];
@@ -743,7 +827,10 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     }
                 }
                 if (!ok) break;
+                float wv_next[kMaxKT];
+                const bool refill_next = !dw_resident && nb + 1 < nb1;
                 if (!dw_resident) { __syncwarp(); if (lane == 0) mbar_arrive(dw_free); ++dwcnt; }
+                if (refill_next) dw_load(nb + 1, wv_next);       // in flight during the result stores
                 const int mo0 = nb * 128 + cg * 32;
                 if (p.bias != nullptr) {
                     if (mo0 + 32 <= p.Mout && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
@@ -763,13 +850,14 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     // 7.., which also keeps the banks apart), then one lane hands the 32-row box to the TMA unit, which writes
                     // it out while the warp goes on with the next blocks; rows past Ntok and columns past Mout are clipped by
                     // the tensor map.  The buffer is reused once the store before it has finished reading shared memory.
-                    auto store_cols = [&](auto sc_c) {
-                        constexpr int SC = decltype(sc_c)::value, PITCH = SC * 4, NCH = SC / 4;
-                        const uint32_t stage = smem_base + L.st_off + (warp - kFirstEpiWarp) * (32 * PITCH);
+                    auto store_cols = [&](auto sc_c, auto nbuf_c) {
+                        constexpr int SC = decltype(sc_c)::value, NBUF = decltype(nbuf_c)::value, PITCH = SC * 4, NCH = SC / 4;
+                        const uint32_t stage0 = smem_base + L.st_off + (warp - kFirstEpiWarp) * (32 * PITCH * NBUF);
                         const uint32_t row_off = lane * PITCH;
 #pragma unroll
                         for (int c0 = 0; c0 < 32; c0 += SC) {
-                            if (lane == 0) bulk_wait_read_all();
+                            const uint32_t stage = stage0 + ((c0 / SC) % NBUF) * (32 * PITCH);
+                            if (lane == 0) { if (NBUF == 2) bulk_wait_read_but_one(); else bulk_wait_read_all(); }
                             __syncwarp();
 #pragma unroll
                             for (int j = 0; j < NCH; ++j) {
@@ -785,9 +873,11 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             }
                         }
                     };
-                    if (p.staged == 16) store_cols(std::integral_constant<int, 16>{});
-                    else if (p.staged == 8) store_cols(std::integral_constant<int, 8>{});
-                    else store_cols(std::integral_constant<int, 32>{});
+                    using std::integral_constant;
+                    if (p.st_box == 8 && p.staged == 16) store_cols(integral_constant<int, 8>{}, integral_constant<int, 2>{});
+                    else if (p.st_box == 16) store_cols(integral_constant<int, 16>{}, integral_constant<int, 1>{});
+                    else if (p.st_box == 8) store_cols(integral_constant<int, 8>{}, integral_constant<int, 1>{});
+                    else store_cols(integral_constant<int, 32>{}, integral_constant<int, 1>{});
                 } else if (p.vec32_ok && mo0 + 32 <= p.Mout) {
                     // No room for store buffers (K = 1024: the resident A tile).  A thread holds 32 consecutive floats of
                     // its row; stored as they lie, every store instruction would touch 32 different lines with 16 bytes each
@@ -838,6 +928,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             if (mo0 + j < p.Mout) p.C[static_cast<size_t>(mo0 + j) * p.Ntok + tok] = acc[j];
                     }
                 }
+                if (refill_next && !dw_publish(wv_next)) { ok = false; break; }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(epi_done(n_it & 1u));
@@ -909,9 +1000,10 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     // for them: narrower buffers paid for with a raw stage were measured slower, 370 against 334 us at 65536 x 1024 x 512.)
     if (stages_for() < 5 && p.dw_tabs > 1) p.dw_tabs = 1;
     if (stages_for() < 5 && abuf > 1) { abuf = 1; p.AR = p.KT; }
-    if (stages_for() < 4) p.staged = 0;
+    // (activations that arrive quantized need no raw stages: two weight stages are enough there)
+    if (stages_for() < (p.preq ? 2 : 4)) p.staged = 0;
     int stages = stages_for();
-    if (stages < 3) return ST_UNSUPPORTED_PATH;
+    if (stages < (p.preq ? 2 : 3)) return ST_UNSUPPORTED_PATH;
     if (stages > 2 * kMaxStages) stages = 2 * kMaxStages;
     if (p.preq) {
         // no raw fp32 stages: everything goes to the weight ring
@@ -937,7 +1029,15 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
         const long long nthreads = static_cast<long long>(p.m_tiles) * 128 * p.nblk * 8;
         const long long qgrid = nthreads / 256;
         if (qgrid > 0x7fffffffLL) return ST_UNSUPPORTED_PATH;
-        quantize_q8_planar_kernel<<<static_cast<unsigned>(qgrid), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk, nthreads);
+        const bool x_aligned = (reinterpret_cast<uintptr_t>(X) & 15u) == 0;
+        // (the tile kernels want a few CTAs per SM; with few token tiles the one-piece-per-thread kernel spreads wider)
+        const bool wide = static_cast<long long>(p.m_tiles) * (K / 128) >= 4LL * sms;
+        if (wide && x_aligned && K % 256 == 0 && p.m_tiles <= 65535)
+            quantize_q8_planar_tile_kernel<256><<<dim3(K / 256, p.m_tiles), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk);
+        else if (wide && x_aligned && K % 128 == 0 && p.m_tiles <= 65535)
+            quantize_q8_planar_tile_kernel<128><<<dim3(K / 128, p.m_tiles), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk);
+        else
+            quantize_q8_planar_kernel<<<static_cast<unsigned>(qgrid), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk, nthreads);
         if (cudaGetLastError() != cudaSuccess) return ST_QUANT;
         if (!make_tmap_3d(&tmX, TmaType::U8, aq, K, N, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
     } else
@@ -945,8 +1045,12 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
     tmC = tmW;                                   // only read by the kernel when the results leave through TMA stores
     // box = staged columns x 32 rows; swizzle of the box width (32, 64 or 128 bytes)
-    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, p.staged, 32,
-                                  p.staged == 32 ? 1 : (p.staged == 16 ? 3 : 4))) p.staged = 0;
+    // (one buffer of 16 columns: its second store of a column block waits about 1 200 cycles for the first one to be read,
+    // but the same 2 KB used as two halves of 8 columns in turn was slower, 93 against 81 us at 65536 x 128 x 1024: stores
+    // of 32-byte rows cost the TMA unit more than the wait)
+    p.st_box = p.staged;
+    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, p.st_box, 32,
+                                  p.st_box == 32 ? 1 : (p.st_box == 16 ? 3 : 4))) p.staged = 0;
 
     const int smem = static_cast<int>(q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total);
     static int configured_smem[64] = {0};
