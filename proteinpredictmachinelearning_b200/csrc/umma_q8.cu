@@ -49,8 +49,6 @@ struct Q8Params {
     int AR;                    // 16 KB slots of quantized A, used as a ring over (item, K step): KT = resident, 2 KT = resident
                                // and double-buffered across items, 3 = a short ring (items with a single column block)
     int dw_tabs;               // scale tables held in smem: n_blocks (all resident, filled once) or 1 (refilled per column block)
-    int st_box;                // columns of one TMA store (the box width): `staged`, or half of it when the buffer is used
-                               // as two halves in turn (a half is refilled while the store of the other half still reads)
     int staged;                // columns of the per-warp store buffer (32 rows x staged fp32: 8, 16 or 32; the results leave
                                // through TMA stores), 0: plain stores from registers
     int preq;                  // 1: the activations were quantized by a kernel of their own: int8 tiles and scale tables
@@ -332,7 +330,63 @@ quantize_q8_planar_tile_kernel(const float* __restrict__ X, int8_t* __restrict__
     }
 }
 
-template <bool SUMI, int QW>      // SUMI: also write the raw int32 block sums (tests); QW: quantizer warps
+// Refill of the weight-scale table in shared memory, fp32 [nblk][128] of d_w * 2^49 for one weight column block (used
+// when the tables of all column blocks do not fit).  Thread `etid` of the 512 epilogue threads handles column
+// etid % 128.  Not inlined: these run once per column block and must not take registers from the block loop.
+//   load (16-byte form, nblk a multiple of 8): eight consecutive blocks of the column, kept as raw halves so that
+//   nothing waits for the load until the values are needed
+static __device__ __noinline__ uint4 q8_dw_load_vec(const __half* Wd, int Mout, int nblk, int nbx, int etid) {
+    const int mo = nbx * 128 + (etid & 127), kb0 = (etid >> 7) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (mo < Mout && kb0 < nblk) raw = __ldg(reinterpret_cast<const uint4*>(Wd + static_cast<size_t>(mo) * nblk + kb0));
+    return raw;
+}
+//   publish: wait until every epilogue warp has finished with the table before (phase parity `free_par` of dw_free),
+//   write this thread's values, arrive on dw_full
+static __device__ __noinline__ bool q8_dw_publish_vec(uint4 raw, float* dw_s, int nblk, int etid, int lane, uint32_t dw_free,
+                                                      uint32_t dw_full, uint32_t free_par, volatile int* cta_abort, int* err) {
+    if (!mbar_wait(dw_free, free_par, cta_abort, err, 0x1402)) return false;
+    const float kTwo49 = __uint_as_float((127u + 49u) << 23);
+    const int col = etid & 127, kb0 = (etid >> 7) * 8;
+    const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        if (kb0 + 2 * t < nblk) {
+            dw_s[(kb0 + 2 * t) * 128 + col] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] & 0xffffu))) * kTwo49;
+            dw_s[(kb0 + 2 * t + 1) * 128 + col] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] >> 16))) * kTwo49;
+        }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(dw_full);
+    return true;
+}
+//   any nblk: every fourth block of the column per thread, loaded and published in one go
+static __device__ __noinline__ bool q8_dw_fill_scalar(const __half* Wd, int Mout, int nblk, int nbx, float* dw_s, int etid, int lane,
+                                                      uint32_t dw_free, uint32_t dw_full, uint32_t free_par,
+                                                      volatile int* cta_abort, int* err) {
+    const float kTwo49 = __uint_as_float((127u + 49u) << 23);
+    const int mo = nbx * 128 + (etid & 127);
+    const __half* src = Wd + static_cast<size_t>(mo) * nblk + (etid >> 7);
+    float wv[kMaxKT];
+#pragma unroll
+    for (int t = 0; t < kMaxKT; ++t)
+        wv[t] = (mo < Mout && 4 * t + (etid >> 7) < nblk) ? __half2float(src[4 * t]) * kTwo49 : 0.0f;
+    if (!mbar_wait(dw_free, free_par, cta_abort, err, 0x1402)) return false;
+#pragma unroll
+    for (int t = 0; t < kMaxKT; ++t) {
+        const int i = etid + t * (32 * kEpiWarps);
+        if (i < nblk * 128) dw_s[i] = wv[t];
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(dw_full);
+    return true;
+}
+
+// SUMI: also write the raw int32 block sums (tests); QW: quantizer warps; RESIDENT: the weight-scale tables of all column
+// blocks are in shared memory (the instance then holds no refill code: even unused, it cost the block loop registers,
+// 98 against 81 us at 65536 x 128 x 1024)
+// STAGED: the results leave through the per-warp store buffers (the instance then holds none of the other store paths).
+template <bool SUMI, int QW, bool RESIDENT, bool STAGED>
 __global__ void __launch_bounds__(Roles<QW>::kThreads, 1)
 umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                const __grid_constant__ CUtensorMap tmC, const Q8Params p) {
@@ -595,7 +649,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const int row = q * 32 + lane;                     // token row inside the tile
         const uint32_t taddr0 = tmem_base + cg * 32 + (static_cast<uint32_t>(q * 32) << 16);
         uint32_t bcnt = 0, n_it = 0, dwcnt = 0; bool ok = true;
-        const bool dw_resident = p.dw_tabs == p.n_blocks;  // (one column block in all: trivially resident)
+        const bool dw_resident = RESIDENT || p.dw_tabs == p.n_blocks;  // (one column block in all: trivially resident)
         const float kTwo100 = __uint_as_float((127u + 100u) << 23), kTwo49 = __uint_as_float((127u + 49u) << 23);
         if (dw_resident) {
             for (int i = etid; i < p.n_blocks * p.nblk * 128; i += 32 * kEpiWarps) {
@@ -608,48 +662,6 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (lane == 0) mbar_arrive(dw_full);
             if (!mbar_wait(dw_full, 0u, cta_abort, p.err, 0x1404)) ok = false;
         }
-        // Refill of the weight-scale table (when the tables of all column blocks do not fit): this thread's share of
-        // column block `nbx` is read from global memory into registers ...
-        auto dw_load = [&](int nbx, float (&wv)[kMaxKT]) {
-            const int col = etid & 127, mo = nbx * 128 + col;
-            if (p.dw_vec) {
-                // eight consecutive blocks of one column per thread: one 16-byte load
-                uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-                const int kb0 = (etid >> 7) * 8;
-                if (mo < p.Mout && kb0 < p.nblk)
-                    raw = __ldg(reinterpret_cast<const uint4*>(p.Wd + static_cast<size_t>(mo) * p.nblk + kb0));
-                const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    wv[2 * t] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] & 0xffffu))) * kTwo49;
-                    wv[2 * t + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(rw[t] >> 16))) * kTwo49;
-                }
-            } else {
-                const __half* src = p.Wd + static_cast<size_t>(mo) * p.nblk + (etid >> 7);
-#pragma unroll
-                for (int t = 0; t < kMaxKT; ++t)
-                    wv[t] = (mo < p.Mout && 4 * t + (etid >> 7) < p.nblk) ? __half2float(src[4 * t]) * kTwo49 : 0.0f;
-            }
-        };
-        // ... and written to shared memory once every epilogue warp has finished with the table before it.
-        auto dw_publish = [&](const float (&wv)[kMaxKT]) -> bool {
-            if (!mbar_wait(dw_free, (dwcnt & 1u) ^ 1u, cta_abort, p.err, 0x1402)) return false;
-            if (p.dw_vec) {
-                const int col = etid & 127, kb0 = (etid >> 7) * 8;
-#pragma unroll
-                for (int t = 0; t < kMaxKT; ++t)
-                    if (kb0 + t < p.nblk) dw_s[(kb0 + t) * 128 + col] = wv[t];
-            } else {
-#pragma unroll
-                for (int t = 0; t < kMaxKT; ++t) {
-                    const int i = etid + t * (32 * kEpiWarps);
-                    if (i < p.nblk * 128) dw_s[i] = wv[t];
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(dw_full);
-            return true;
-        };
         int mt = 0, nb0 = 0, nb1 = 0;
         for (; ok && item_at(n_it, mt, nb0, nb1); ++n_it) {
             const int tok = mt * 128 + row;
@@ -659,13 +671,16 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 // they were staged once before the first item; otherwise this block's table is refilled here:
                 // wait until every epilogue warp has finished with the previous one, fill, publish.
                 const uint32_t dw_a0 = smem_base + L.dw_off + ((p.dw_tabs > 1 ? nb : 0) * p.nblk * 128 + cg * 32) * 4;
-                if (!dw_resident) {
+                if (!RESIDENT && !dw_resident) {
                     // The first column block of an item fills the table here; the later ones were filled at the end of the
-                    // block before them (loads issued before its result stores, table written after them).
-                    if (nb == nb0) {
-                        float wv[kMaxKT];
-                        dw_load(nb, wv);
-                        if (!dw_publish(wv)) { ok = false; break; }
+                    // block before them (loads issued before its result stores, table written between them) when the scales
+                    // can be read with 16-byte loads.
+                    const uint32_t free_par = (dwcnt & 1u) ^ 1u;
+                    if (!p.dw_vec) {
+                        if (!q8_dw_fill_scalar(p.Wd, p.Mout, p.nblk, nb, dw_s, etid, lane, dw_free, dw_full, free_par, cta_abort, p.err)) { ok = false; break; }
+                    } else if (nb == nb0) {
+                        const uint4 raw = q8_dw_load_vec(p.Wd, p.Mout, p.nblk, nb, etid);
+                        if (!q8_dw_publish_vec(raw, dw_s, p.nblk, etid, lane, dw_free, dw_full, free_par, cta_abort, p.err)) { ok = false; break; }
                     }
                     if (!mbar_wait(dw_full, dwcnt & 1u, cta_abort, p.err, 0x1403)) { ok = false; break; }
                 }
@@ -827,10 +842,13 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     }
                 }
                 if (!ok) break;
-                float wv_next[kMaxKT];
-                const bool refill_next = !dw_resident && nb + 1 < nb1;
-                if (!dw_resident) { __syncwarp(); if (lane == 0) mbar_arrive(dw_free); ++dwcnt; }
-                if (refill_next) dw_load(nb + 1, wv_next);       // in flight during the result stores
+                uint4 raw_next = make_uint4(0u, 0u, 0u, 0u);
+                bool refill_next = false;
+                if constexpr (!RESIDENT) {
+                    refill_next = !dw_resident && p.dw_vec && nb + 1 < nb1;
+                    if (!dw_resident) { __syncwarp(); if (lane == 0) mbar_arrive(dw_free); ++dwcnt; }
+                    if (refill_next) raw_next = q8_dw_load_vec(p.Wd, p.Mout, p.nblk, nb + 1, etid);       // in flight during the result stores
+                }
                 const int mo0 = nb * 128 + cg * 32;
                 if (p.bias != nullptr) {
                     if (mo0 + 32 <= p.Mout && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0) {
@@ -844,7 +862,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                         for (int j = 0; j < 32; ++j) if (mo0 + j < p.Mout) acc[j] += p.bias[mo0 + j];
                     }
                 }
-                if (p.c_trans && p.staged) {
+                if (STAGED || (p.c_trans && p.staged)) {
                     // Asynchronous stores, `staged` columns at a time: thread = row writes its 16-byte chunks into the warp's
                     // buffer (rows of 32, 64 or 128 bytes in the TMA swizzle of that width: address bits 4.. XOR address bits
                     // 7.., which also keeps the banks apart), then one lane hands the 32-row box to the TMA unit, which writes
@@ -871,14 +889,21 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                                 tma_store_3d(&tmC, stage, mo0 + c0, mt * 128 + q * 32, 0);
                                 bulk_commit_group();
                             }
+                            // the next table is written while the TMA unit reads the buffer
+                            if constexpr (!RESIDENT) {
+                                if (c0 == 0 && refill_next) {
+                                    refill_next = false;
+                                    if (!q8_dw_publish_vec(raw_next, dw_s, p.nblk, etid, lane, dw_free, dw_full, (dwcnt & 1u) ^ 1u, cta_abort, p.err)) ok = false;
+                                }
+                            }
                         }
                     };
                     using std::integral_constant;
-                    if (p.st_box == 8 && p.staged == 16) store_cols(integral_constant<int, 8>{}, integral_constant<int, 2>{});
-                    else if (p.st_box == 16) store_cols(integral_constant<int, 16>{}, integral_constant<int, 1>{});
-                    else if (p.st_box == 8) store_cols(integral_constant<int, 8>{}, integral_constant<int, 1>{});
-                    else store_cols(integral_constant<int, 32>{}, integral_constant<int, 1>{});
-                } else if (p.vec32_ok && mo0 + 32 <= p.Mout) {
+                    // one buffer of 16 columns per warp.  (The template also takes 8 or 32 columns and two buffers used in
+                    // turn; every further instance costs the block loop instruction-cache room: 89 against 86 us at
+                    // 65536 x 128 x 1024 with four instances.)
+                    store_cols(integral_constant<int, 16>{}, integral_constant<int, 1>{});
+                } else if (!STAGED && p.vec32_ok && mo0 + 32 <= p.Mout) {
                     // No room for store buffers (K = 1024: the resident A tile).  A thread holds 32 consecutive floats of
                     // its row; stored as they lie, every store instruction would touch 32 different lines with 16 bytes each
                     // and the load/store unit takes one line per cycle.  Two exchange steps over the lane bits 3-4 regroup
@@ -911,7 +936,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                                          "f"(acc[8 * s4 + 4]), "f"(acc[8 * s4 + 5]), "f"(acc[8 * s4 + 6]), "f"(acc[8 * s4 + 7]) : "memory");
                         }
                     }
-                } else if (tok < p.Ntok) {
+                } else if (!STAGED && tok < p.Ntok) {
                     if (p.c_trans) {
                         float* dst = p.C + static_cast<size_t>(tok) * p.Mout + mo0;
                         if (p.vec_ok && mo0 + 32 <= p.Mout) {
@@ -928,7 +953,10 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                             if (mo0 + j < p.Mout) p.C[static_cast<size_t>(mo0 + j) * p.Ntok + tok] = acc[j];
                     }
                 }
-                if (refill_next && !dw_publish(wv_next)) { ok = false; break; }
+                if constexpr (!RESIDENT) {
+                    if (refill_next && !q8_dw_publish_vec(raw_next, dw_s, p.nblk, etid, lane, dw_free, dw_full, (dwcnt & 1u) ^ 1u, cta_abort, p.err)) ok = false;
+                }
+                if (!ok) break;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(epi_done(n_it & 1u));
@@ -1045,33 +1073,42 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     if (!make_tmap_3d(&tmW, TmaType::U8, W, K, M, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
     tmC = tmW;                                   // only read by the kernel when the results leave through TMA stores
     // box = staged columns x 32 rows; swizzle of the box width (32, 64 or 128 bytes)
-    // (one buffer of 16 columns: its second store of a column block waits about 1 200 cycles for the first one to be read,
-    // but the same 2 KB used as two halves of 8 columns in turn was slower, 93 against 81 us at 65536 x 128 x 1024: stores
-    // of 32-byte rows cost the TMA unit more than the wait)
-    p.st_box = p.staged;
-    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, p.st_box, 32,
-                                  p.st_box == 32 ? 1 : (p.st_box == 16 ? 3 : 4))) p.staged = 0;
+    // (one buffer of 16 columns: its second store of a column block waits about 1 200 cycles for the first one to be read)
+    if (p.staged && !make_tmap_3d(&tmC, TmaType::F32, C, M, N, 1, static_cast<uint64_t>(M) * 4, 0, p.staged, 32, 3)) p.staged = 0;
 
     const int smem = static_cast<int>(q8_layout(p.AR, p.nblk, p.RS, p.BS, p.dw_tabs, p.staged).total);
     static int configured_smem[64] = {0};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && configured_smem[dev] < smem) {
-        if (cudaFuncSetAttribute(umma_q8_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(umma_q8_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(umma_q8_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
-            cudaGetLastError();
-            return ST_LAUNCH;
-        }
+        const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        bool ok_attr = true;
+        auto set = [&](auto kernel) { if (cudaFuncSetAttribute(kernel, attr, 227 * 1024) != cudaSuccess) ok_attr = false; };
+        set(umma_q8_kernel<false, 2, true, true>); set(umma_q8_kernel<false, 2, false, true>);
+        set(umma_q8_kernel<false, 4, true, true>); set(umma_q8_kernel<false, 4, false, true>);
+        set(umma_q8_kernel<false, 2, false, false>); set(umma_q8_kernel<false, 4, false, false>);
+        set(umma_q8_kernel<true, 2, false, false>);
+        if (!ok_attr) { cudaGetLastError(); return ST_LAUNCH; }
         configured_smem[dev] = 227 * 1024;
     }
     const int grid = total_items < sms ? total_items : sms;
-    if (sumi_out != nullptr) umma_q8_kernel<true, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
+    const bool resident = p.dw_tabs == p.n_blocks;
     // four quantizer warps where the quantizer sets the pace: items with one column block, and K = 1024 with up to four
     // (the A tile is not double-buffered there, so every item starts by waiting for its first blocks; measured 177 against
     // 194 us at 65536 x 1024 x 256, 317 against 324 at N = 512, but 584 against 547 at N = 1024)
-    else if (p.blocks_per_group == 1 || (!p.preq && p.KT == kMaxKT && p.blocks_per_group <= 4))
-        umma_q8_kernel<false, 4><<<grid, Roles<4>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
-    else umma_q8_kernel<false, 2><<<grid, Roles<2>::kThreads, smem, st>>>(tmX, tmW, tmC, p);
+    const bool four = p.blocks_per_group == 1 || (!p.preq && p.KT == kMaxKT && p.blocks_per_group <= 4);
+    const bool staged = p.staged != 0 && c_trans;
+    const int th2 = Roles<2>::kThreads, th4 = Roles<4>::kThreads;
+    if (sumi_out != nullptr) umma_q8_kernel<true, 2, false, false><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+    else if (!staged) {
+        if (four) umma_q8_kernel<false, 4, false, false><<<grid, th4, smem, st>>>(tmX, tmW, tmC, p);
+        else umma_q8_kernel<false, 2, false, false><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+    } else if (four) {
+        if (resident) umma_q8_kernel<false, 4, true, true><<<grid, th4, smem, st>>>(tmX, tmW, tmC, p);
+        else umma_q8_kernel<false, 4, false, true><<<grid, th4, smem, st>>>(tmX, tmW, tmC, p);
+    } else {
+        if (resident) umma_q8_kernel<false, 2, true, true><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+        else umma_q8_kernel<false, 2, false, true><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+    }
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
