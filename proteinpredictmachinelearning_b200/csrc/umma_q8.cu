@@ -16,6 +16,7 @@
 // per thread), warps 4-19 = epilogue (four warps per TMEM lane quarter, 32 columns each).
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "kernels.h"
@@ -749,7 +750,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                     rescale(vb, 1, kb, da, dc);
                     return true;
                 };
-                if (!SUMI && (p.nblk & 3) == 0) {
+                if (!SUMI && (STAGED || (p.nblk & 3) == 0)) {      // (the STAGED instances are only launched with K % 128 == 0)
                     // Fast path (every K that is a multiple of 128): groups of four blocks on slots 0..3, handed over in
                     // pairs.  Slot numbers, TMEM offsets and table offsets are compile-time constants; the two table
                     // pointers advance once per group.  Per block: the two 16-column halves are software-pipelined (the
@@ -825,6 +826,7 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                         half16(vb, integral_constant<int, 1536 + 64>{}, da, dc, dwp, 1);
                     }
                     bcnt += static_cast<uint32_t>(p.nblk);
+                } else if (STAGED) {
                 } else if ((p.nblk & 3) == 0) {
                     // the same schedule with run-time slot numbers (the instance that also writes the int32 sums)
                     for (int kb0 = 0; kb0 < p.nblk && ok; kb0 += 4, bcnt += 4) {
@@ -1096,7 +1098,7 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     // (the A tile is not double-buffered there, so every item starts by waiting for its first blocks; measured 177 against
     // 194 us at 65536 x 1024 x 256, 317 against 324 at N = 512, but 584 against 547 at N = 1024)
     const bool four = p.blocks_per_group == 1 || (!p.preq && p.KT == kMaxKT && p.blocks_per_group <= 4);
-    const bool staged = p.staged != 0 && c_trans;
+    const bool staged = p.staged != 0 && c_trans && (p.nblk & 3) == 0;
     const int th2 = Roles<2>::kThreads, th4 = Roles<4>::kThreads;
     if (sumi_out != nullptr) umma_q8_kernel<true, 2, false, false><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
     else if (!staged) {
