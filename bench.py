@@ -675,10 +675,10 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one pass of the sweep (36 launches of umma_q8_kernel) from one ncu
-# capture on a B200, divided by 36; the capture command and the per-launch figures are in
-# profiles/q8_sweep_launches_and_dram.md.  Below the algorithmic bytes: part of each result is still in L2 at kernel end.
-Q8_SWEEP_DRAM_BYTES_PER_LAUNCH = 76.4e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one pass of the sweep (36 launches of umma_q8_kernel and the 11
+# activation-quantizer launches of its two-pass shapes, as in the timed region) from one ncu capture on a B200, divided
+# by 36; the capture command and the per-kernel figures are in profiles/q8_sweep_launches_and_dram.md.
+Q8_SWEEP_DRAM_BYTES_PER_LAUNCH = 82.9e6
 
 
 def single_kernel(args):
