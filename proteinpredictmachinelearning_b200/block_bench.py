@@ -21,6 +21,13 @@ this path: they are not run here, so the figure is the sum of the path's kernels
 Every op takes its input from a tensor generated from a seed common to all ranks (the op chains that need no glue
 between them -- projections -> attention -> output Linear, left / right -> outer-product-mean -- are connected).
 
+Fused form (default; PPML_B200_BLOCK_FUSED=0 gives the op-by-op form above): projections of one input that feed one
+consumer are one Linear over the concatenated weights -- Q, K, V and the gate of an attention call (4 x 256 -> one
+N = 1024 product), the three gate projections of a triangle multiplication (N = 384) -- and the attention call reads
+Q, K, V as column ranges of that product's output (token-major operands, row stride 1024), applies sigmoid(gate) to its
+output in the store and writes it token-major for the output Linear.  44 Linears become 28, and the permute / gate passes
+of the reference around attention (src/model/PPML.cpp:1386-1520) have no counterpart at all.
+
 Sharding over G ranks follows the reference's flat-buffer semantics: every activation is cut into G contiguous
 flat chunks (token rows; attention batches; tri_mul channel slabs; outer-product-mean d1 slabs).  Exchanges per
 block, all through NCCL into local memory before any kernel reads them: all-gather of each pair bias ([L*L, 8],
@@ -50,8 +57,9 @@ class Block:
 
     SITES = {"mr_bias": 0, "col_t": 1, "right": 2, "pr_bias": 3, "row_t": 4, "pc_bias": 5}
 
-    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None):
+    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None, fused=True):
         self.torch, self.dist, self.ops = torch, dist, ops
+        self.fused = fused
         self.inp, self.weights, self.G, self.rank, self.dev = inputs, weights, G, rank, dev
         self.peers = peers if G > 1 else None      # shard.PeerBuffers: exchanges as single kernels over peer memory
         self.peer_ptrs = {}
@@ -148,6 +156,20 @@ class Block:
     def attention(self, src, batch, bias, scale, tag):
         """Projections, fused attention over this rank's batches (with the gathered pair bias, if any), output Linear."""
         d_in = src.shape[1]
+        if self.fused:
+            hd = HEADS * HEAD_DIM
+            with self.timed("linear_q8"):
+                qkvg = self.linear(src, 4 * hd, True, tag + "qkvg")
+            seq = qkvg.shape[0] // batch
+            t = qkvg.view(batch, seq, 4 * hd)
+            o = self.buf("att_" + tag, (batch, seq, hd))
+            with self.timed("attention"):
+                self.ops.flash_attn_tokens(t[:, :, 0:hd], t[:, :, hd:2 * hd], t[:, :, 2 * hd:3 * hd], HEADS, bias=bias,
+                                           gate=t[:, :, 3 * hd:4 * hd], act="sigmoid", scale=scale,
+                                           bias_bcast=bias is not None, out=o)
+            self.out["att_" + tag] = o
+            with self.timed("linear_q8"):
+                return self.linear(o.view(-1, hd), d_in, True, tag + "o")
         with self.timed("linear_q8"):
             q = self.linear(src, HEADS * HEAD_DIM, True, tag + "q")
             k = self.linear(src, HEADS * HEAD_DIM, True, tag + "k")
@@ -206,8 +228,11 @@ class Block:
             with self.timed("linear_tf32"):
                 a = self.linear(x, TRI_D, False, "tl" + d)
                 b = self.linear(x, TRI_D, False, "tr" + d)
-                for t in ("tlg", "trg", "tg"):
-                    self.linear(x, TRI_D, False, t + d)
+                if self.fused:
+                    self.linear(x, 3 * TRI_D, False, "tgates" + d)
+                else:
+                    for t in ("tlg", "trg", "tg"):
+                        self.linear(x, TRI_D, False, t + d)
             with self.timed("tri_mul"):
                 tm = self.ops.tri_mul_cuda(a.view(TRI_D // G, L, L, 1), b.view(TRI_D // G, L, L, 1), float(L), direction)
             self.out["tri_" + d] = tm
@@ -294,11 +319,19 @@ def make_inputs_and_weights(torch, ops, dev):
              ("oo", OPM_D * OPM_D, D_PAIR, True), ("pf1", D_PAIR, 2 * D_PAIR, False), ("pf2", 2 * D_PAIR, D_PAIR, False)]
     for d in ("out", "in"):
         spec += [(t + d, D_PAIR, TRI_D, False) for t in ("tl", "tr", "tlg", "trg", "tg")] + [("to" + d, TRI_D, D_PAIR, False)]
-    weights = {}
+    weights, raw = {}, {}
     for (tag, k, n_out, q8) in spec:
         w = rnd(n_out, k) * 0.02
         b = rnd(n_out) * 0.1
+        raw[tag] = (w, b)
         weights[(tag, k, n_out, q8)] = (ops.quantize_q8_0r(w) if q8 else w, b)
+    # concatenated weights of the fused form
+    cat = lambda tags: (torch.cat([raw[t][0] for t in tags], 0).contiguous(), torch.cat([raw[t][1] for t in tags], 0).contiguous())
+    for tag, d_in in (("mr", D_MSA), ("mc", D_MSA), ("pr", D_PAIR), ("pc", D_PAIR)):
+        w, b = cat([tag + t for t in "qkvg"])
+        weights[(tag + "qkvg", d_in, 4 * HEADS * HEAD_DIM, True)] = (ops.quantize_q8_0r(w), b)
+    for d in ("out", "in"):
+        weights[("tgates" + d, D_PAIR, 3 * TRI_D, False)] = cat([t + d for t in ("tlg", "trg", "tg")])
     return inputs, weights
 
 
@@ -358,7 +391,8 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
                 peers = None
             else:
                 exchange_mode = "one kernel per exchange: stores into the peers' buffers between two flag rounds"
-    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev, peers=peers)
+    fused = os.environ.get("PPML_B200_BLOCK_FUSED", "1") != "0"
+    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev, peers=peers, fused=fused)
 
     def barrier():
         if G > 1:
@@ -375,7 +409,7 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
     n_checked, bad = 0, []
     if check:
         if G > 1:
-            full = Block(torch, dist, ops, inputs, weights, 1, 0, dev)
+            full = Block(torch, dist, ops, inputs, weights, 1, 0, dev, fused=fused)
             full.run()
             torch.cuda.synchronize()
             n_checked, bad = verify(torch, blk, full, G, rank)
@@ -473,8 +507,12 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
             "launch": ("cuda graphs" + (" (" + graph_note + ")" if graph_note else " for the compute segments, collectives from the host"))
                       if graph_ms is not None else "eager",
             "exchange": exchange_mode,
-            "workload": "one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads; 26 Q8 Linears, 18 fp32 Linears, "
-                        "4 attention calls, 2 tri_mul, 1 outer-product-mean",
+            "workload": "one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads; "
+                        + ("14 Q8 Linears (Q, K, V and gate of an attention call as one), 14 fp32 Linears (the gates of a triangle "
+                           "multiplication as one), 4 attention calls on token-major operands with the gate applied in the store, "
+                           if fused else "26 Q8 Linears, 18 fp32 Linears, 4 attention calls, ")
+                        + "2 tri_mul, 1 outer-product-mean",
+            "fused_projections": fused,
             "split_ms_rank0": {k: round(v, 4) for k, v in sorted(split.items())},
             "exchange_share": round(split.get("exchange", 0.0) / total_split, 4),
             "exchange_bytes_per_rank": exchange_bytes(G),

@@ -315,6 +315,28 @@ __device__ __forceinline__ uint16_t lds_u16(uint32_t saddr) {
     return v;
 }
 
+// Regroups a 32 x 32 fp32 tile held one row per lane (lane r holds v[j] = element j of row r) for row-contiguous
+// global accesses: afterwards lane l holds in v[8 s .. 8 s + 7] (s = 0..3) the elements 8 (l >> 3) .. 8 (l >> 3) + 7 of
+// row (l & 7) + 8 s, so that an access with one 32-byte piece per lane covers eight whole 128-byte rows instead of
+// touching 32 rows with 32 bytes each.  Two exchange steps: lane bit 3 + st pairs with the piece bit st (8 or 16 floats).
+// All 32 lanes must call it.
+__device__ __forceinline__ void rows_to_line_pieces(float (&v)[32], int lane) {
+#pragma unroll
+    for (int st = 0; st < 2; ++st) {
+        const int bit = 8 << st;
+        const bool up = (lane & bit) != 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if ((j & bit) == 0) {
+                // the lane with the bit clear keeps piece j and sends j + bit; its partner the reverse
+                const float send = up ? v[j] : v[j + bit];
+                const float got = __shfl_xor_sync(0xffffffffu, send, bit);
+                if (up) v[j] = got; else v[j + bit] = got;
+            }
+        }
+    }
+}
+
 // ---- packed fp32 pairs (one issue slot for two lanes of add / mul / fma) ------------------------
 __device__ __forceinline__ uint64_t pack2(float a, float b) {
     uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r;

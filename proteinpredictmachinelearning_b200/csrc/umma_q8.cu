@@ -908,23 +908,10 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 } else if (!STAGED && p.vec32_ok && mo0 + 32 <= p.Mout) {
                     // No room for store buffers (K = 1024: the resident A tile).  A thread holds 32 consecutive floats of
                     // its row; stored as they lie, every store instruction would touch 32 different lines with 16 bytes each
-                    // and the load/store unit takes one line per cycle.  Two exchange steps over the lane bits 3-4 regroup
-                    // the data so that lane l holds, for s = 0..3, the 32-byte piece (l >> 3) of row 8 s + (l & 7): a store
-                    // instruction then writes eight whole 128-byte lines.
-#pragma unroll
-                    for (int st = 0; st < 2; ++st) {
-                        const int lbit = 8 << st, pbit = 8 << st;          // lane bit 3 + st pairs with piece bit st (8 or 16 floats)
-                        const bool up = (lane & lbit) != 0;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if ((j & pbit) == 0) {
-                                // the lane with the bit clear keeps piece j and sends j + pbit; its partner the reverse
-                                const float send = up ? acc[j] : acc[j + pbit];
-                                const float got = __shfl_xor_sync(0xffffffffu, send, lbit);
-                                if (up) acc[j] = got; else acc[j + pbit] = got;
-                            }
-                        }
-                    }
+                    // and the load/store unit takes one line per cycle.  Regrouped (two exchange steps over the lane bits 3-4),
+                    // lane l holds, for s = 0..3, the 32-byte piece (l >> 3) of row 8 s + (l & 7): a store instruction then
+                    // writes eight whole 128-byte lines.
+                    rows_to_line_pieces(acc, lane);
                     const int piece = lane >> 3;
 #pragma unroll
                     for (int s4 = 0; s4 < 4; ++s4) {
