@@ -354,6 +354,47 @@ def kernel_records(torch, dev, peaks, oracle):
                          "us": us, "tflops": fl / us / 1e6, "gbs": by / us / 1e3, "roofline": roofline(fl, by, us, peaks, ts), "checked": bool(ok)})
         del Q, K, V, O
 
+    # ---- the same attention on token-major operands (Q, K, V as column ranges of one fused projection output) with the
+    # sigmoid gate applied in the store, and the backward (exact fp32 CUDA-core kernels) on the forward's O and LSE ----
+    B, h, L, hd = 256, 8, 256, 256
+    t = rnd(B, L, 4 * hd) / 32 ** 0.5
+    bias = rnd(h, L, L)
+    Ot = torch.empty((B, L, hd), device=dev)
+    f = lambda: ops.flash_attn_tokens(t[:, :, 0:hd], t[:, :, hd:2 * hd], t[:, :, 2 * hd:3 * hd], h, bias=bias, gate=t[:, :, 3 * hd:],
+                                      act="sigmoid", scale=32 ** -0.5, bias_bcast=True, path=PATH_UMMA, out=Ot)
+    us = graph_time_us(torch, lambda: [f() for _ in range(4)], 4)
+    fl = 4.0 * B * h * L * L * 32
+    by = 5 * 4.0 * B * L * hd + 4.0 * h * L * L                       # Q, K, V, gate read, O written, shared bias
+    b0 = B // 3
+    heads = lambda x: host(x[b0:b0 + 1]).reshape(1, L, h, 32).transpose(0, 2, 1, 3)
+    rO, _ = oracle.flash_attn(heads(t[:, :, 0:hd]), heads(t[:, :, hd:2 * hd]), heads(t[:, :, 2 * hd:3 * hd]), host(bias),
+                              scale=32 ** -0.5, bias_bcast=True)
+    rO = rO * (1.0 / (1.0 + np.exp(-heads(t[:, :, 3 * hd:]).astype(np.float64))))
+    ok = rel(host(Ot[b0:b0 + 1]).reshape(1, L, h, 32).transpose(0, 2, 1, 3), rO) <= 1e-3
+    recs.append({"kernel": "umma_attn_kernel", "op": "flash_attn_forward on token-major operands, sigmoid(gate) * O in the store",
+                 "workload": f"MSA row, shared pair bias: B'={B} h={h} L={L} d=32, row stride 1024", "us": us, "tflops": fl / us / 1e6,
+                 "gbs": by / us / 1e3, "roofline": roofline(fl, by, us, peaks, 0.5), "checked": bool(ok)})
+    del t, Ot
+    B = 64
+    Q, K, V, dO = (rnd(B, h, L, 32) / 32 ** 0.5 for _ in range(4))
+    O, LSE = ops.flash_attn_forward_cuda(Q, K, V, bias, scale=32 ** -0.5, bias_bcast=True, path=PATH_UMMA)
+    grads = {"dQ": torch.empty_like(Q), "dK": torch.empty_like(Q), "dV": torch.empty_like(Q), "dbias": torch.empty((B, h, L, L), device=dev)}
+    def issue_bwd():
+        ops.flash_attn_backward_cuda(Q, K, V, O, dO, LSE, bias, scale=32 ** -0.5, bias_bcast=True, out=grads)
+    us = graph_time_us(torch, issue_bwd, 1, reps=5)
+    fl = 2 * 5 * 2.0 * B * h * L * L * 32                              # five products, each computed by both kernels' tiles
+    by = 4.0 * (8 * B * h * L * 32 + h * L * L + B * h * L * L)        # Q, K, V, O, dO read; dQ, dK, dV, dbias written
+    b0 = B // 3
+    rO, rL = oracle.flash_attn(host(Q[b0:b0 + 1]), host(K[b0:b0 + 1]), host(V[b0:b0 + 1]), host(bias), scale=32 ** -0.5, bias_bcast=True)
+    ref = oracle.flash_attn_backward(host(Q[b0:b0 + 1]), host(K[b0:b0 + 1]), host(V[b0:b0 + 1]), rO, host(dO[b0:b0 + 1]), rL, host(bias),
+                                     scale=32 ** -0.5, bias_bcast=True)
+    ok = all(rel(host(grads[n][b0:b0 + 1]), ref[n]) <= 2e-3 for n in ("dQ", "dK", "dV", "dbias"))      # the forward ran in tf32
+    recs.append({"kernel": "attn_bwd_dq_kernel + attn_bwd_dkv_kernel", "op": "flash_attn_backward (dQ, dK, dV, dbias), exact fp32 on CUDA cores",
+                 "workload": f"MSA row, shared pair bias: B'={B} h={h} L={L} d=32", "us": us, "tflops": fl / us / 1e6, "gbs": by / us / 1e3,
+                 "roofline": {"bound": "fp32 CUDA cores", "achieved": fl / us / 1e6, "peak": None, "unit": "TFLOP/s", "frac": None},
+                 "checked": bool(ok)})
+    del Q, K, V, dO, O, LSE, grads
+
     # ---- pair-track contractions (configs[3]) ----
     D = 128
     for L in (128, 256, 384):

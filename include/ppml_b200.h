@@ -188,6 +188,20 @@ typedef struct ppml_b200_flash_cfg {
 int ppml_b200_flash_attn_forward(const ppml_b200_flash_cfg* cfg, const float* Q, const float* K, const float* V,
                                  const float* bias, float* O, float* LSE, int path, void* stream);
 
+/* Flash-attention backward: replaces flash_attn_backward_cuda (src/backend/CUDAKernels.cpp:176, :920;
+ * include/ppml/FlashAttn.h:85-88; device code src/cuda/FlashAttnKernel.cu:538-1670), same math as
+ * flash_attn_backward_cpu (src/ops/FlashAttn.cpp:144-216):
+ *   P = exp(S - LSE), D_i = sum_d dO O, dS = P (dO V^T - D), dQ = scale dS K, dK = scale dS^T Q, dV = P^T dO, dbias = dS.
+ * Q, K, V, O, dO and the gradients [B, h, L, d]; LSE [B, h, L] as the forward wrote it (a row with LSE = -inf gets zero
+ * gradients); bias [B, h, L, L], or one [h, L, L] for every batch with bias_batch_stride = 0 (the reference passes
+ * h * L * L); dbias always [B, h, L, L] (masked positions 0).  Any of dQ / dK / dV / dbias may be NULL and is then not
+ * computed.  Differences from the reference's launcher: no zero-fill pass and no atomic adds (every output element is
+ * written once, results do not depend on scheduling), head dims up to 64 (the reference stops at 32).  Exact fp32 on CUDA
+ * cores.  Returns 0, or 7 when the shape is not supported (d > 64). */
+int ppml_b200_flash_attn_backward(const ppml_b200_flash_cfg* cfg, int64_t bias_batch_stride, const float* Q, const float* K,
+                                  const float* V, const float* bias, const float* O, const float* dO, const float* LSE,
+                                  float* dQ, float* dK, float* dV, float* dbias, void* stream);
+
 /* Extended form (no counterpart in the reference, whose config has a single L): Lk keys per query row
  * (K/V [B][h][Lk][d], bias rows of Lk), and bias_batch_stride in elements between batches
  * (h*L*Lk for a full bias tensor, 0 to share one [h][L][Lk] bias across the batch). */

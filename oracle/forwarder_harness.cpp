@@ -29,6 +29,9 @@ extern int mul_mat_q8_cuda(const void* W, const float* X, float* C, int M, int N
                            int* path_out);                                                                     // :169
 extern int flash_attn_forward_cuda(const FlashAttnConfig& cfg, const float* Q, const float* K, const float* V,
                                    const float* bias, float* O, float* LSE);                                   // :174
+extern int flash_attn_backward_cuda(const FlashAttnConfig& cfg, const float* Q, const float* K, const float* V,
+                                    const float* bias, const float* O, const float* dO, const float* LSE,
+                                    float* dQ, float* dK, float* dV, float* dbias);                              // :176
 extern void mul_mat_cuda_f16(const void* A, const void* B, float* C, int M, int K, int N);                     // :182
 extern int mul_mat_mma_tf32_smem(const void* A, const void* B, float* C, int M, int K, int N);                 // :187
 extern void mulmat_stats_cuda_begin(int M, int K, int N);                                                      // :190
@@ -89,6 +92,13 @@ int fh_flash_attn_forward(int B, int h, int L, int d, int causal, float scale, f
     FlashAttnConfig cfg;
     cfg.B = B; cfg.h = h; cfg.L = L; cfg.d = d; cfg.causal = causal != 0; cfg.scale = scale; cfg.softmax_eps = eps;
     return flash_attn_forward_cuda(cfg, Q, K, V, bias, O, LSE);
+}
+int fh_flash_attn_backward(int B, int h, int L, int d, int causal, float scale, const float* Q, const float* K, const float* V,
+                           const float* bias, const float* O, const float* dO, const float* LSE,
+                           float* dQ, float* dK, float* dV, float* dbias) {
+    FlashAttnConfig cfg;
+    cfg.B = B; cfg.h = h; cfg.L = L; cfg.d = d; cfg.causal = causal != 0; cfg.scale = scale;
+    return flash_attn_backward_cuda(cfg, Q, K, V, bias, O, dO, LSE, dQ, dK, dV, dbias);
 }
 int fh_sizeof_flash_cfg(void) { return static_cast<int>(sizeof(FlashAttnConfig)); }
 void fh_out_prod(const float* s0, const float* s1, float* dst, const int64_t* ne0x, const int64_t* ne1x, const int64_t* nex) {

@@ -292,6 +292,67 @@ int oracle_flash_attn_forward(int B, int H, int L, int Lk, int d, int causal, fl
     return 1;
 }
 
+/* ------------------------------------------------------------------ */
+/* flash attention backward, row by row as the reference's CPU routine
+ * (src/ops/FlashAttn.cpp:144-216; formulas include/ppml/FlashAttn.h:66-75):
+ *   P_ij  = exp(S_ij - LSE_i)   (LSE holds the eps of the forward)
+ *   D_i   = sum_d dO_id O_id ;  dP_ij = sum_d dO_id V_jd ;  dS_ij = P_ij (dP_ij - D_i)
+ *   dQ_id = scale sum_j dS_ij K_jd ; dK_jd = scale sum_i dS_ij Q_id ; dV_jd = sum_i P_ij dO_id
+ *   dbias_ij = dS_ij (masked positions and fully masked rows: 0)
+ * Q/K/V/O/dO/dQ/dK/dV [d,L,h,B] (d innermost), bias read with a batch stride
+ * (0: one [h,L,L] bias for every batch), dbias always [B,h,L,L], LSE [L,h,B].
+ * Outputs are zeroed first; a null output is skipped.                  */
+/* ------------------------------------------------------------------ */
+int oracle_flash_attn_backward(int B, int H, int L, int d, int causal, float scale,
+                               const float* Q, const float* K, const float* V, const float* bias,
+                               int64_t bias_batch_stride, const float* O, const float* dO, const float* LSE,
+                               float* dQ, float* dK, float* dV, float* dbias) {
+    if (!Q || !K || !V || !O || !dO || !LSE) return 0;
+    if (B <= 0 || H <= 0 || L <= 0 || d <= 0) return 0;
+    if (!dQ && !dK && !dV && !dbias) return 0;
+    const float sc = (scale > 0.f) ? scale : 1.0f / sqrtf((float)d);
+    const size_t nq = (size_t)B * H * L * d, nb = (size_t)B * H * L * L;
+    if (dQ) memset(dQ, 0, nq * sizeof(float));
+    if (dK) memset(dK, 0, nq * sizeof(float));
+    if (dV) memset(dV, 0, nq * sizeof(float));
+    if (dbias) memset(dbias, 0, nb * sizeof(float));
+    for (int b = 0; b < B; ++b) {
+        for (int hh = 0; hh < H; ++hh) {
+            const size_t base = ((size_t)b * H + hh) * (size_t)L * d;
+            const float* Lb = LSE + ((size_t)b * H + hh) * (size_t)L;
+            const float* Bb = bias ? bias + (size_t)b * (size_t)bias_batch_stride + (size_t)hh * L * L : NULL;
+            float* dBb = dbias ? dbias + ((size_t)b * H + hh) * (size_t)L * L : NULL;
+            for (int i = 0; i < L; ++i) {
+                const float lse = Lb[i];
+                if (!(lse > -INFINITY)) continue;
+                const float* q = Q + base + (size_t)i * d;
+                const float* o_row = O + base + (size_t)i * d;
+                const float* do_row = dO + base + (size_t)i * d;
+                float D = 0.f;
+                for (int dd = 0; dd < d; ++dd) D += do_row[dd] * o_row[dd];
+                const int jmax = causal ? (i + 1) : L;
+                for (int j = 0; j < jmax; ++j) {
+                    const float* k = K + base + (size_t)j * d;
+                    const float* v = V + base + (size_t)j * d;
+                    float s = 0.f;
+                    for (int dd = 0; dd < d; ++dd) s += q[dd] * k[dd];
+                    s *= sc;
+                    if (Bb) s += Bb[(size_t)i * L + j];
+                    const float p = expf(s - lse);
+                    float dp = 0.f;
+                    for (int dd = 0; dd < d; ++dd) dp += do_row[dd] * v[dd];
+                    const float ds = p * (dp - D);
+                    if (dBb) dBb[(size_t)i * L + j] = ds;
+                    if (dQ) for (int dd = 0; dd < d; ++dd) dQ[base + (size_t)i * d + dd] += sc * ds * k[dd];
+                    if (dK) for (int dd = 0; dd < d; ++dd) dK[base + (size_t)j * d + dd] += sc * ds * q[dd];
+                    if (dV) for (int dd = 0; dd < d; ++dd) dV[base + (size_t)j * d + dd] += p * do_row[dd];
+                }
+            }
+        }
+    }
+    return 1;
+}
+
 /* The legacy unfused attention path, the semantic ground truth for Lq != Lk:
  *   scores[j,i] = sum_d K[j,d]*Q[i,d]      (out_prod, src/modules/Attention.cpp:267)
  *   scores *= scale ; scores += bias       (:269-272)

@@ -119,6 +119,17 @@ int ref_flash_attn_forward(int B, int h, int L, int d, int causal, float scale, 
     return ok ? 0 : 1;
 }
 
+// flash_attn_backward_cpu (src/ops/FlashAttn.cpp:144-216): bias and dbias [B,h,L,L]; null outputs are skipped.
+int ref_flash_attn_backward(int B, int h, int L, int d, int causal, float scale, float eps,
+                            const float* Q, const float* K, const float* V, const float* bias,
+                            const float* O, const float* dO, const float* LSE,
+                            float* dQ, float* dK, float* dV, float* dbias) {
+    FlashAttnConfig cfg;
+    cfg.B = B; cfg.h = h; cfg.L = L; cfg.d = d; cfg.causal = causal != 0;
+    cfg.scale = scale; cfg.softmax_eps = eps;
+    return flash_attn_backward_cpu(cfg, Q, K, V, bias, O, dO, LSE, dQ, dK, dV, dbias) ? 0 : 1;
+}
+
 // The unfused attention graph of SelfAttention::forward_graph (src/modules/Attention.cpp:267-283),
 // Q [Lq,D,H,B], K/V [Lk,D,H,B] (sequence innermost), bias [Lk,Lq,H,B] or null, out [Lq,D,H,B].
 int ref_attention_legacy(const float* Q, const float* K, const float* V, const float* bias, float* O,

@@ -53,6 +53,7 @@ SIGNATURES = {
     "ppml_b200_q8_file_layout_hash": (_i, [_vp, C.c_char_p]),
     "ppml_b200_q8_file_load": (_i, [_vp, _i, _vp, _vp, _vp]),
     "ppml_b200_flash_attn_forward": (_i, [C.POINTER(FlashCfg), _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "ppml_b200_flash_attn_backward": (_i, [C.POINTER(FlashCfg), _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ppml_b200_flash_attn_forward_ex": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ppml_b200_flash_attn_forward_16": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "ppml_b200_flash_attn_forward_tokens": (_i, [C.POINTER(FlashCfg), _i, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i, _vp, _i64, _vp, _i, _vp]),

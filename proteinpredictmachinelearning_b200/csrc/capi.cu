@@ -328,6 +328,17 @@ int ppml_b200_flash_attn_forward_tokens(const ppml_b200_flash_cfg* cfg, int Lk, 
     return flash_attn_any(cfg, Lk, bias_batch_stride, Q, K, V, 0, bias, O, LSE, path, stream, &lay);
 }
 
+int ppml_b200_flash_attn_backward(const ppml_b200_flash_cfg* cfg, int64_t bias_batch_stride, const float* Q, const float* K,
+                                  const float* V, const float* bias, const float* O, const float* dO, const float* LSE,
+                                  float* dQ, float* dK, float* dV, float* dbias, void* stream) {
+    if (!cfg || !Q || !K || !V || !O || !dO || !LSE) return ST_BAD_ARGS;
+    if (cfg->B <= 0 || cfg->h <= 0 || cfg->L <= 0 || cfg->d <= 0) return ST_BAD_ARGS;
+    if (!dQ && !dK && !dV && !dbias) return ST_BAD_ARGS;
+    const float scale = (cfg->scale > 0.f) ? cfg->scale : 1.0f / std::sqrt(static_cast<float>(cfg->d));
+    return launch_attn_backward(cfg->B, cfg->h, cfg->L, cfg->d, cfg->causal ? 1 : 0, scale, Q, K, V, bias, bias_batch_stride,
+                                O, dO, LSE, dQ, dK, dV, dbias, as_stream(stream));
+}
+
 int ppml_b200_flash_attn_forward(const ppml_b200_flash_cfg* cfg, const float* Q, const float* K, const float* V,
                                  const float* bias, float* O, float* LSE, int path, void* stream) {
     if (!cfg) return ST_BAD_ARGS;

@@ -63,6 +63,11 @@ struct AttnLayout {
 };
 // ft: keys of the reference's first softmax tile (its Bc); a row whose first ft scores are all -inf gives O = 0, LSE = -inf
 // as the reference's CPU kernel does; 0 switches that off
+// Flash-attention backward, exact fp32 on CUDA cores (attn_backward.cu): Q, K, V, O, dO, dQ, dK, dV [B, h, L, d];
+// bias [.., h, L, L] with a batch stride (0: shared); dbias [B, h, L, L]; LSE [B, h, L]; null outputs are skipped.
+int launch_attn_backward(int B, int H, int L, int d, int causal, float scale, const float* Q, const float* K, const float* V,
+                         const float* bias, long long bias_batch_stride, const float* O, const float* dO, const float* LSE,
+                         float* dQ, float* dK, float* dV, float* dbias, cudaStream_t st);
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                         long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st);

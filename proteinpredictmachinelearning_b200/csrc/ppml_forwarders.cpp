@@ -124,6 +124,17 @@ int flash_attn_forward_cuda(const FlashAttnConfig& cfg, const float* Q, const fl
     return ppml_b200_flash_attn_forward(&c, Q, K, V, bias, O, LSE, batched_path(), nullptr) == 0 ? 0 : 1;
 }
 
+// src/backend/CUDAKernels.cpp:176 -- 0 = done, 1 = unsupported (the caller then falls back to the CPU routine)
+int flash_attn_backward_cuda(const FlashAttnConfig& cfg, const float* Q, const float* K, const float* V,
+                             const float* bias, const float* O, const float* dO, const float* LSE,
+                             float* dQ, float* dK, float* dV, float* dbias) {
+    ppml_b200_flash_cfg c;
+    c.B = cfg.B; c.h = cfg.h; c.L = cfg.L; c.d = cfg.d; c.causal = cfg.causal ? 1 : 0;
+    c.scale = cfg.scale; c.softmax_eps = cfg.softmax_eps; c.Br = cfg.Br; c.Bc = cfg.Bc;
+    return ppml_b200_flash_attn_backward(&c, static_cast<int64_t>(cfg.h) * cfg.L * cfg.L, Q, K, V, bias, O, dO, LSE,
+                                         dQ, dK, dV, dbias, nullptr) == 0 ? 0 : 1;
+}
+
 // src/backend/CUDAKernels.cpp:201
 void out_prod_cuda(const float* src0, const float* src1, float* dst,
                    int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03,

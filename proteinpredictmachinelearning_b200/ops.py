@@ -245,6 +245,29 @@ def flash_attn_tokens(Q, K, V, heads, bias=None, gate=None, act="sigmoid", scale
     return O, LSE
 
 
+def flash_attn_backward_cuda(Q, K, V, O, dO, LSE, bias=None, scale=0.0, causal=False, bias_bcast=False,
+                             want=("dQ", "dK", "dV", "dbias"), out=None):
+    """Gradients of the fused attention: Q, K, V, O, dO [B, h, L, d], LSE [B, h, L], bias [B, h, L, L] (or [h, L, L] with
+    bias_bcast).  Returns a dict with the requested ones of dQ, dK, dV [B, h, L, d] and dbias [B, h, L, L] (`out`: a dict
+    of tensors to write into instead of new ones)."""
+    Q, K, V, O, dO, LSE = (_f32c(t) for t in (Q, K, V, O, dO, LSE))
+    B, h, L, d = Q.shape
+    if bias is not None:
+        bias = _f32c(bias)
+    if out is None:
+        out = {}
+        for name in want:
+            shape = (B, h, L, L) if name == "dbias" else (B, h, L, d)
+            out[name] = torch.full(shape, float("nan"), device=Q.device, dtype=torch.float32)
+    cfg = FlashCfg(B, h, L, d, int(causal), float(scale), 1e-9, 64, 64)
+    stride = 0 if (bias is None or bias_bcast) else h * L * L
+    rc = _lib.load().ppml_b200_flash_attn_backward(C.byref(cfg), stride, _p(Q), _p(K), _p(V), _p(bias), _p(O), _p(dO), _p(LSE),
+                                                   _p(out.get("dQ")), _p(out.get("dK")), _p(out.get("dV")), _p(out.get("dbias")),
+                                                   _stream())
+    _check(rc, "flash_attn_backward")
+    return out
+
+
 def out_prod_cuda(s0, s1, path=PATH_AUTO):
     """s0 [ne03,ne02,K,ne00], s1 [ne13,ne12,K,ne10] (torch order = reversed graph dims) -> [ne3,ne2,ne10,ne00]."""
     s0, s1 = _f32c(s0), _f32c(s1)

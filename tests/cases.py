@@ -38,6 +38,16 @@ def attn_case(B, h, L, d, Lk=None, seed=3, bias=True, bias_bcast=False):
     return Q, K, V, bi
 
 
+def attn_backward_case(B, h, L, d, seed=7, bias=True, bias_bcast=False, masked_rows=()):
+    """Inputs of the attention backward: the forward's operands, an upstream gradient dO, and optionally query rows
+    whose bias is -inf everywhere (fully masked: LSE = -inf, all their gradients are 0)."""
+    Q, K, V, bi = attn_case(B, h, L, d, seed=seed, bias=bias or bool(masked_rows), bias_bcast=bias_bcast)
+    for r in masked_rows:
+        bi[..., r, :] = -np.inf
+    dO = rng(seed + 100).standard_normal((B, h, L, d)).astype(np.float32)
+    return Q, K, V, bi, dO
+
+
 def attn_masked_first_tile_case(d=8, L=100, Lk=200, seed=13):
     """Rows whose leading scores are -inf: row 3 has the reference's whole first key tile (64 keys) masked and later
     keys visible, row 4 has 63 of them masked, row 2 two whole tiles."""

@@ -58,6 +58,7 @@ class Oracle:
         L.oracle_f32_to_bf16.argtypes = [C.c_float]
         L.oracle_mul_mat_q8.restype = C.c_int
         L.oracle_flash_attn_forward.restype = C.c_int
+        L.oracle_flash_attn_backward.restype = C.c_int
 
     def mul_mat_f32(self, a, b, bias=None):
         a, b, bias = _f32(a), _f32(b), _f32(bias)
@@ -127,6 +128,19 @@ class Oracle:
                                                 _ptr(O), _ptr(LSE))
         assert ok
         return O, LSE
+
+    def flash_attn_backward(self, Q, K, V, O, dO, LSE, bias=None, scale=0.0, causal=False, bias_bcast=False,
+                            want=("dQ", "dK", "dV", "dbias")):
+        """Q, K, V, O, dO [B,h,L,d], LSE [B,h,L], bias [B,h,L,L] (or [h,L,L] with bias_bcast) -> dict of gradients."""
+        Q, K, V, O, dO, LSE, bias = (_f32(t) for t in (Q, K, V, O, dO, LSE, bias))
+        B, h, L, d = Q.shape
+        out = {n: np.full((B, h, L, L) if n == "dbias" else (B, h, L, d), np.nan, np.float32) for n in want}
+        stride = 0 if (bias is None or bias_bcast) else h * L * L
+        ok = self.lib.oracle_flash_attn_backward(B, h, L, d, int(causal), C.c_float(scale), _ptr(Q), _ptr(K), _ptr(V), _ptr(bias),
+                                                 _i64(stride), _ptr(O), _ptr(dO), _ptr(LSE), _ptr(out.get("dQ")),
+                                                 _ptr(out.get("dK")), _ptr(out.get("dV")), _ptr(out.get("dbias")))
+        assert ok
+        return out
 
     def attention_legacy(self, Q, K, V, bias, scale, bias_bcast=False):
         Q, K, V, bias = _f32(Q), _f32(K), _f32(V), _f32(bias)
@@ -270,6 +284,16 @@ class Ref:
                                              _ptr(Q), _ptr(K), _ptr(V), _ptr(bias), _ptr(O), _ptr(LSE), int(naive))
         assert rc == 0
         return O, LSE
+
+    def flash_attn_backward(self, Q, K, V, O, dO, LSE, bias=None, scale=0.0, causal=False):
+        Q, K, V, O, dO, LSE, bias = (_f32(t) for t in (Q, K, V, O, dO, LSE, bias))
+        B, h, L, d = Q.shape
+        out = {n: np.empty((B, h, L, L) if n == "dbias" else (B, h, L, d), np.float32) for n in ("dQ", "dK", "dV", "dbias")}
+        rc = self.lib.ref_flash_attn_backward(B, h, L, d, int(causal), C.c_float(scale), C.c_float(1e-9), _ptr(Q), _ptr(K), _ptr(V),
+                                              _ptr(bias), _ptr(O), _ptr(dO), _ptr(LSE), _ptr(out["dQ"]), _ptr(out["dK"]),
+                                              _ptr(out["dV"]), _ptr(out["dbias"]))
+        assert rc == 0
+        return out
 
     def attention_legacy(self, Q, K, V, bias, scale):
         """Q [B,h,Lq,d] etc. in the fused op's layout; transposed here into the unfused graph's

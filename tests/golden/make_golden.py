@@ -20,7 +20,7 @@ os.environ["PPML_CPU_F16C"] = "0"      # the scalar fp16 dot, the loop the resta
 
 
 HOT_LAUNCHERS = ("mul_mat_cuda", "mul_mat_mma_tf32_smem", "mul_mat_mma_f16", "mul_mat_cuda_f16", "mul_mat_q8_cuda",
-                 "quantize_rows_q8_1_cuda", "dequantize_q8_", "flash_attn_forward_cuda", "out_prod_cuda",
+                 "quantize_rows_q8_1_cuda", "dequantize_q8_", "flash_attn_forward_cuda", "flash_attn_backward_cuda", "out_prod_cuda",
                  "tri_mul_cuda", "outer_prod_mean_cuda", "mulmat_stats_cuda", "cutlass_hw_supported")
 
 
@@ -41,7 +41,7 @@ def launcher_symbols(reference=None):
                                "-I/usr/local/cuda/include", "-c", f"{reference}/src/backend/CUDAKernels.cpp", "-o", obj])
         names = subprocess.check_output(["nm", "-u", obj], text=True).split()
     want = sorted(n for n in names if n.startswith("_ZN4ppml") and any(h in n for h in HOT_LAUNCHERS)
-                  and "back" not in n)
+                  and ("back" not in n or "flash_attn_backward_cuda" in n))
     with open(os.path.join(HERE, "reference_launcher_symbols.txt"), "w") as f:
         f.write("\n".join(want) + "\n")
     print("wrote", len(want), "launcher symbols")
@@ -87,6 +87,17 @@ def main():
     bp = np.zeros((2, 2, 200, 200), np.float32); bp[:, :, :100] = bi
     o, l_ = ref.flash_attn(Qp, K, V, bp, scale=1 / np.sqrt(32.0))
     out["fa_masked_O"], out["fa_masked_LSE"] = o[:, :, :100].copy(), l_[:, :, :100].copy()
+
+    # attention backward (flash_attn_backward_cpu) on the forward's own O and LSE; rows 5 and 17 fully masked
+    Q, K, V, bi, dO = cases.attn_backward_case(2, 3, 45, 32, seed=7, masked_rows=(5, 17))
+    O, LSE = ref.flash_attn(Q, K, V, bi, scale=1 / np.sqrt(32.0))
+    g = ref.flash_attn_backward(Q, K, V, O, dO, LSE, bi, scale=1 / np.sqrt(32.0))
+    for n in ("dQ", "dK", "dV", "dbias"):
+        out["fab_" + n] = g[n]
+    g = ref.flash_attn_backward(Q, K, V, *ref.flash_attn(Q, K, V, None, causal=True)[:1], dO,
+                                ref.flash_attn(Q, K, V, None, causal=True)[1], None, causal=True)
+    for n in ("dQ", "dK", "dV", "dbias"):
+        out["fab_causal_" + n] = g[n]
 
     # pair-track contractions
     l, r = cases.tri_case(6, 20, 24, 28, outgoing=True)

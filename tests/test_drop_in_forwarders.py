@@ -35,6 +35,7 @@ def fh():
     lib.fh_quantize_rows_q8_1.argtypes = [vp, vp, i64]
     lib.fh_dequantize_q8.argtypes = [i, vp, vp, i64]
     lib.fh_flash_attn_forward.argtypes = [i, i, i, i, i, f, f, vp, vp, vp, vp, vp, vp]
+    lib.fh_flash_attn_backward.argtypes = [i, i, i, i, i, f] + [vp] * 11
     lib.fh_out_prod.argtypes = [vp, vp, vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]
     lib.fh_out_prod.restype = None
     lib.fh_tri_mul.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, f, i]
@@ -159,6 +160,28 @@ def test_flash_attn_forwarder_takes_the_reference_struct(fh, oracle, math_mode, 
     rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, causal=causal, eps=eps)
     assert cases.rel_err(host(O), rO) <= tol
     assert np.abs(host(LSE) - rL).max() <= ltol
+
+
+def test_flash_attn_backward_forwarder(fh, oracle):
+    """flash_attn_backward_cuda as the reference's dispatcher declares it (src/backend/CUDAKernels.cpp:176): full bias
+    [B, h, L, L], every gradient, then with dbias and dK left out (null pointers are skipped)."""
+    B, h, L, d = 2, 3, 77, 32
+    Q, K, V, bi, dO = cases.attn_backward_case(B, h, L, d, seed=12, masked_rows=(4,))
+    scale = 0.19
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale)
+    ref = oracle.flash_attn_backward(Q, K, V, rO, dO, rL, bi, scale=scale)
+    t = [dev(x) for x in (Q, K, V, bi, rO, dO, rL)]
+    g = {n: torch.full((B, h, L, L) if n == "dbias" else (B, h, L, d), float("nan"), device="cuda") for n in ("dQ", "dK", "dV", "dbias")}
+    torch.cuda.synchronize()
+    rc = fh.fh_flash_attn_backward(B, h, L, d, 0, scale, *[p(x) for x in t], p(g["dQ"]), p(g["dK"]), p(g["dV"]), p(g["dbias"]))
+    assert rc == 0
+    for n in g:
+        assert cases.rel_err(host(g[n]), ref[n]) <= TOL_FP32, n
+    keep = g["dK"].clone()
+    g["dK"].fill_(7.0)
+    rc = fh.fh_flash_attn_backward(B, h, L, d, 0, scale, *[p(x) for x in t], p(g["dQ"]), None, p(g["dV"]), None)
+    assert rc == 0 and bool((g["dK"] == 7.0).all()) and cases.rel_err(host(g["dV"]), ref["dV"]) <= TOL_FP32
+    del keep
 
 
 @pytest.mark.parametrize("mode,tol", [(None, TOL_FP32), ("tc", TOL_TF32)])

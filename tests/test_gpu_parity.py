@@ -498,6 +498,76 @@ def test_attention_first_key_tile_masked(oracle, d, L, Lk, path):
     assert float((LSE2 - torch.logsumexp(s, dim=-1)).abs().max()) <= max(tol_l, 1e-4)
 
 
+@pytest.mark.parametrize("B,h,L,d,causal,bias,bcast,masked", [
+    (2, 3, 45, 32, False, True, False, (5, 17)),     # the golden case: two fully masked rows
+    (2, 3, 45, 32, True, False, False, ()),          # causal, no bias (golden)
+    (2, 8, 51, 32, False, True, True, ()),           # dev size, one bias for every batch
+    (3, 8, 100, 8, False, True, False, (0,)),        # extra-MSA heads
+    (2, 2, 70, 64, True, True, False, ()),           # d = 64 (two channels per lane), causal with bias
+    (1, 4, 256, 32, False, True, True, ()),          # main-track size of one batch
+    (2, 2, 33, 20, False, False, False, ()),         # a head dim that is no power of two, one row past a tile
+])
+def test_attention_backward(oracle, B, h, L, d, causal, bias, bcast, masked):
+    """flash_attn_backward against the restated CPU routine of the reference (src/ops/FlashAttn.cpp:144-216) on the
+    forward's own O and LSE; exact fp32 kernels, 1e-5 of the largest gradient entry."""
+    Q, K, V, bi, dO = cases.attn_backward_case(B, h, L, d, seed=7, bias=bias, bias_bcast=bcast, masked_rows=masked)
+    scale = 1 / np.sqrt(32.0)
+    O, LSE = oracle.flash_attn(Q, K, V, bi, scale=scale, causal=causal, bias_bcast=bcast)
+    ref = oracle.flash_attn_backward(Q, K, V, O, dO, LSE, bi, scale=scale, causal=causal, bias_bcast=bcast)
+    got = ops.flash_attn_backward_cuda(dev(Q), dev(K), dev(V), dev(O), dev(dO), dev(LSE), (dev(bi) if bi is not None else None), scale=scale, causal=causal,
+                                       bias_bcast=bcast)
+    for n in ("dQ", "dK", "dV", "dbias"):
+        g = host(got[n])
+        assert np.isfinite(g).all(), n
+        assert cases.rel_err(g, ref[n]) <= TOL_FP32, (n, cases.rel_err(g, ref[n]))
+    for r in masked:
+        assert np.all(host(got["dQ"])[:, :, r] == 0) and np.all(host(got["dbias"])[:, :, r] == 0)
+    if causal:
+        assert np.all(np.triu(host(got["dbias"])[0, 0], 1) == 0)
+    if (B, h, L, d) == (2, 3, 45, 32):
+        tag = "fab_causal_" if causal else "fab_"
+        for n in ("dQ", "dK", "dV", "dbias"):
+            assert cases.rel_err(host(got[n]), GOLD[tag + n]) <= TOL_FP32       # produced by the reference's own CPU code
+    # only some gradients wanted: the others are not touched, the wanted ones do not change
+    part = ops.flash_attn_backward_cuda(dev(Q), dev(K), dev(V), dev(O), dev(dO), dev(LSE), (dev(bi) if bi is not None else None), scale=scale, causal=causal,
+                                        bias_bcast=bcast, want=("dV", "dQ"))
+    assert sorted(part) == ["dQ", "dV"]
+    assert torch.equal(part["dV"], got["dV"]) and torch.equal(part["dQ"], got["dQ"])
+
+
+def test_attention_backward_from_the_cuda_forward(oracle):
+    """Forward on the tensor cores, backward on its O and LSE: the chain a training step runs (1e-3: the forward is tf32)."""
+    Q, K, V, bi, dO = cases.attn_backward_case(2, 8, 128, 32, seed=9, bias_bcast=True)
+    scale = 1 / np.sqrt(32.0)
+    O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), (dev(bi) if bi is not None else None), scale=scale, bias_bcast=True)
+    got = ops.flash_attn_backward_cuda(dev(Q), dev(K), dev(V), O, dev(dO), LSE, (dev(bi) if bi is not None else None), scale=scale, bias_bcast=True)
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=True)
+    ref = oracle.flash_attn_backward(Q, K, V, rO, dO, rL, bi, scale=scale, bias_bcast=True)
+    for n in ("dQ", "dK", "dV", "dbias"):
+        assert cases.rel_err(host(got[n]), ref[n]) <= 2 * TOL_TF32, n
+
+
+def test_backward_shapes_of_a_linear(oracle):
+    """The two products a Linear's backward sends through the same entries (src/backend/CUDAKernels.cpp:823): the input
+    gradient dX = dY W is a mul_mat against the transposed weight, the weight gradient dW = dY^T X is an out_prod whose
+    contraction runs over the tokens."""
+    M, K, N = 2601, 128, 256                          # tokens, in features, out features (a dev-size pair Linear)
+    r = cases.rng(17)
+    X = r.standard_normal((M, K)).astype(np.float32)
+    W = (r.standard_normal((N, K)) * 0.02).astype(np.float32)
+    dY = r.standard_normal((M, N)).astype(np.float32)
+    dX = host(ops.mul_mat_cuda(dev(dY), dev(np.ascontiguousarray(W.T)), path=PATH_SIMT))          # [M, N] x [K, N]^T
+    assert cases.rel_err(dX, oracle.mul_mat_f32(dY, np.ascontiguousarray(W.T))) <= TOL_FP32
+    dXt = host(ops.mul_mat_cuda(dev(dY), dev(np.ascontiguousarray(W.T)), path=PATH_UMMA))
+    assert cases.rel_err(dXt, dX) <= TOL_TF32
+    # dW[n][k] = sum_m dY[m][n] X[m][k]: out_prod of the planes [tokens][N] and [tokens][K]
+    s0 = np.ascontiguousarray(X.reshape(1, 1, M, K)); s1 = np.ascontiguousarray(dY.reshape(1, 1, M, N))
+    dW = host(ops.out_prod_cuda(dev(s0), dev(s1)))[0, 0]
+    ref = oracle.out_prod(s0, s1)[0, 0]
+    assert dW.shape == (N, K) and cases.rel_err(dW, ref) <= TOL_TF32
+    assert cases.rel_err(dW, dY.T.astype(np.float64) @ X.astype(np.float64)) <= TOL_TF32
+
+
 @pytest.mark.parametrize("B,h,L,d,Lk,bias,path,tol,ltol", [
     (3, 8, 256, 32, None, True, PATH_UMMA, TOL_TF32, 2e-3),      # main-track heads on the tensor cores
     (2, 8, 51, 32, None, True, PATH_AUTO, TOL_FP32, 1e-5),       # dev size: 51 keys with a bias -> CUDA cores

@@ -127,6 +127,52 @@ def test_attention_golden(oracle):
     assert cases.rel_err(GOLD["fa_O"], GOLD["fa_legacy_O"]) < 1e-5
 
 
+def test_attention_backward_golden(oracle):
+    """The restated backward against gradients produced by the reference's flash_attn_backward_cpu, bit for bit; rows 5
+    and 17 are fully masked (LSE = -inf): all their gradients are zero."""
+    Q, K, V, bi, dO = cases.attn_backward_case(2, 3, 45, 32, seed=7, masked_rows=(5, 17))
+    O, LSE = oracle.flash_attn(Q, K, V, bi, scale=1 / np.sqrt(32.0))
+    assert np.all(LSE[:, :, 5] == -np.inf) and np.all(LSE[:, :, 17] == -np.inf)
+    g = oracle.flash_attn_backward(Q, K, V, O, dO, LSE, bi, scale=1 / np.sqrt(32.0))
+    for n in ("dQ", "dK", "dV", "dbias"):
+        assert np.array_equal(g[n], GOLD["fab_" + n]), n
+    assert np.all(g["dQ"][:, :, 5] == 0) and np.all(g["dbias"][:, :, 17] == 0)
+    O, LSE = oracle.flash_attn(Q, K, V, None, causal=True)
+    g = oracle.flash_attn_backward(Q, K, V, O, dO, LSE, None, causal=True)
+    for n in ("dQ", "dK", "dV", "dbias"):
+        assert np.array_equal(g[n], GOLD["fab_causal_" + n]), n
+    assert np.all(np.triu(g["dbias"][0, 0], 1) == 0)
+    # a null output is skipped, the others are unchanged
+    g2 = oracle.flash_attn_backward(Q, K, V, O, dO, LSE, None, causal=True, want=("dK",))
+    assert list(g2) == ["dK"] and np.array_equal(g2["dK"], g["dK"])
+
+
+def test_attention_backward_is_the_gradient(oracle):
+    """Finite differences of sum(O * dO) in float64 against dQ, dK, dV and dbias (small case, eps of the forward = 0)."""
+    Q, K, V, bi, dO = cases.attn_backward_case(1, 2, 9, 4, seed=21)
+    sc = 0.5
+    def fwd(q, k, v, b):
+        s = np.einsum("bhid,bhjd->bhij", q, k) * sc + b
+        p = np.exp(s - s.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+        return np.einsum("bhij,bhjd->bhid", p, v)
+    q64, k64, v64, b64, g64 = (t.astype(np.float64) for t in (Q, K, V, bi, dO))
+    O = fwd(q64, k64, v64, b64)
+    s = np.einsum("bhid,bhjd->bhij", q64, k64) * sc + b64
+    LSE = np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)
+    g = oracle.flash_attn_backward(Q, K, V, O.astype(np.float32), dO, LSE.astype(np.float32), bi, scale=sc)
+    for name, arr in (("dQ", q64), ("dK", k64), ("dV", v64), ("dbias", b64)):
+        num = np.zeros_like(arr)
+        it = np.nditer(arr, flags=["multi_index"])
+        for _ in it:
+            idx = it.multi_index
+            old = arr[idx]
+            arr[idx] = old + 1e-5; up = (fwd(q64, k64, v64, b64) * g64).sum()
+            arr[idx] = old - 1e-5; dn = (fwd(q64, k64, v64, b64) * g64).sum()
+            arr[idx] = old
+            num[idx] = (up - dn) / 2e-5
+        assert cases.rel_err(g[name], num) < 2e-4, name
+
+
 def test_attention_lq_ne_lk_matches_unfused_graph(oracle):
     Q, K, V, bi = cases.attn_case(3, 2, 1, 8, Lk=40, seed=33)
     assert np.array_equal(oracle.attention_legacy(Q, K, V, bi, 1 / np.sqrt(32.0)), GOLD["fa_legacy_q1_O"])
