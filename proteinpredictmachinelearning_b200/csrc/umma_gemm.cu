@@ -1,5 +1,6 @@
 // umma_gemm.cu -- host side of the tcgen05 contraction engine: eligibility checks, tensor maps,
 // tile shape selection and the launch.
+#include <cstdlib>
 #include "kernels.h"
 #include "tma_host.h"
 #include "umma_gemm.cuh"
@@ -39,6 +40,12 @@ int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, cud
     const long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * p.batch;
     if (total <= 0 || total > 0x7fffffffLL) return ST_BAD_ARGS;
     const int grid = static_cast<int>(total < num_sms() ? total : num_sms());
+    // equal row ranges per CTA instead of whole tiles dealt round robin, when the tiles do not divide evenly
+    static const int flat_env = [] { const char* e = std::getenv("PPML_B200_GEMM_FLAT"); return e ? (e[0] != '0' ? 1 : 0) : 1; }();
+    // (one column tile only: with several, a partial row tile costs every one of them and the round robin balances better;
+    // measured at M = 65536: 36.5 -> 35.0 us at 256 x 256 tf32, 31.9 -> 31.3 at 128 x 256, but 57 -> 63 at 256 x 512)
+    p.flat_rows = (flat_env && p.batch == 1 && !MNMAJOR && EPI == Epi::ROW_MAJOR && p.n_tiles == 1 && p.m_tiles > grid &&
+                   p.m_tiles % grid != 0) ? 1 : 0;
     kern<<<grid, CONVERT ? 320 : 192, smem, st>>>(tmA, tmB, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }

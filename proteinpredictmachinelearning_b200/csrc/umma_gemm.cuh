@@ -21,6 +21,10 @@ struct GemmParams {
     int M, N, K;            // per-batch extents: rows of A, rows of B, contraction length
     int batch;
     int m_tiles, n_tiles;
+    int flat_rows;          // 1 (batch 1, more row tiles than CTAs): every CTA takes an equal contiguous range of rows and walks
+                            // it in tiles of 128, the last one partial (its other rows belong to the next CTA, which computes
+                            // them again from its own start): no CTA has a whole tile more than another (3.46 tiles per CTA
+                            // ran as 4 at M = 65536)
     int k_steps;            // ceil(K / elements per 128 bytes)
     float* C;
     long long ldc;          // row stride of C (elements)
@@ -130,16 +134,36 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     const int tiles_per_batch = p.m_tiles * p.n_tiles;
     const int total_tiles = tiles_per_batch * p.batch;
+    // the k-th tile of this CTA: batch b, rows [row0, row_end) (row0 + 128 rows are loaded and multiplied), column tile nt
+    const int flat_r0 = static_cast<int>(static_cast<long long>(p.M) * blockIdx.x / gridDim.x);
+    const int flat_r1 = static_cast<int>(static_cast<long long>(p.M) * (blockIdx.x + 1) / gridDim.x);
+    auto tile_at = [&](uint32_t k, int& b, int& row0, int& row_end, int& nt) -> bool {
+        if (p.flat_rows) {
+            const int im = static_cast<int>(k) / p.n_tiles;
+            nt = static_cast<int>(k) - im * p.n_tiles;
+            b = 0;
+            row0 = flat_r0 + im * 128;
+            row_end = min(flat_r1, row0 + 128);
+            return row0 < flat_r1;
+        }
+        const long long t = blockIdx.x + static_cast<long long>(k) * gridDim.x;
+        if (t >= total_tiles) return false;
+        b = static_cast<int>(t / tiles_per_batch);
+        const int r = static_cast<int>(t - static_cast<long long>(b) * tiles_per_batch);
+        const int mt = r / p.n_tiles;
+        nt = r - mt * p.n_tiles;
+        row0 = mt * 128;
+        row_end = min(p.M, row0 + 128);
+        return true;
+    };
 
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int b = t / tiles_per_batch;
-                const int r = t - b * tiles_per_batch;
-                const int mt = r / p.n_tiles, nt = r - mt * p.n_tiles;
+            int b, row0, row_end, nt;
+            for (uint32_t tk = 0; ok && tile_at(tk, b, row0, row_end, nt); ++tk) {
                 for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -147,14 +171,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
                     mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
                     if constexpr (!MNMAJOR) {
-                        tma_load_3d(sa, &tmA, full_bar(s), ks * BK, mt * 128, b);
+                        tma_load_3d(sa, &tmA, full_bar(s), ks * BK, row0, b);
                         tma_load_3d(sa + kGemmStageA, &tmB, full_bar(s), ks * BK, nt * BN, b);
                     } else {
                         // boxes of BK rows (inner, contiguous: 128 bytes) x BK k, one after the other
                         constexpr int kBox = BK * 128;
                         static_assert(BN % BK == 0, "row-contiguous operands: BN must be a multiple of the box width");
 #pragma unroll
-                        for (int i = 0; i < 128 / BK; ++i) tma_load_3d(sa + i * kBox, &tmA, full_bar(s), mt * 128 + i * BK, ks * BK, b);
+                        for (int i = 0; i < 128 / BK; ++i) tma_load_3d(sa + i * kBox, &tmA, full_bar(s), row0 + i * BK, ks * BK, b);
 #pragma unroll
                         for (int i = 0; i < BN / BK; ++i) tma_load_3d(sa + kGemmStageA + i * kBox, &tmB, full_bar(s), nt * BN + i * BK, ks * BK, b);
                     }
@@ -171,7 +195,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             else idesc = make_idesc(1, p.ab_fmt, p.ab_fmt, MNMAJOR ? 1 : 0, MNMAJOR ? 1 : 0, 128, BN);
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+            int b_, row0_, row_end_, nt_;
+            for (; ok && tile_at(tile_i, b_, row0_, row_end_, nt_); ++tile_i) {
                 const int acc = tile_i & 1;
                 const uint32_t acc_ph = (tile_i >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, cta_abort, p.err, 0x201)) { ok = false; break; }
@@ -223,10 +248,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         float* bias_s = reinterpret_cast<float*>(stage + kEpiStageBytes);
         uint32_t tile_i = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
-            const int b = t / tiles_per_batch;
-            const int r = t - b * tiles_per_batch;
-            const int mt = r / p.n_tiles, nt = r - mt * p.n_tiles;
+        int b, trow0, row_end, nt;
+        for (; ok && tile_at(tile_i, b, trow0, row_end, nt); ++tile_i) {
             const int acc = tile_i & 1;
             const uint32_t acc_ph = (tile_i >> 1) & 1u;
             const int col0 = nt * BN;
@@ -239,7 +262,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             float ln_mean = 0.0f, ln_rstd = 1.0f;
             if (p.ln_stats != nullptr) {
                 for (int j = lane; j < BN; j += 32) bias_s[256 + j] = (col0 + j < p.N) ? p.ln_u[col0 + j] : 0.0f;
-                const int rown = mt * 128 + q * 32 + lane;
+                const int rown = trow0 + q * 32 + lane;
                 if (rown < p.M) {
                     const float2 st2 = *reinterpret_cast<const float2*>(p.ln_stats + 2 * (static_cast<long long>(b) * p.M + rown));
                     ln_mean = st2.x; ln_rstd = st2.y;
@@ -248,7 +271,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __syncwarp();
             if (!mbar_wait(tfull_bar(acc), acc_ph, cta_abort, p.err, 0x301)) { ok = false; break; }
             tc_fence_after();
-            const int row0 = mt * 128 + q * 32;
+            const int row0 = trow0 + q * 32;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int cbase = col0 + c * 32;
@@ -298,7 +321,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         const int rr = (lane >> 3) + 4 * i;
                         const int row = row0 + rr;
                         float4 val = *reinterpret_cast<const float4*>(stage + rr * kEpiStagePitch + cc * 16);
-                        if (row < p.M && col < p.N) {    // vec_ok: N, ldc (or L) are multiples of 4
+                        if (row < row_end && col < p.N) {    // vec_ok: N, ldc (or L) are multiples of 4
                             if constexpr (EPI == Epi::ROW_MAJOR) {
                                 if (p.gate != nullptr) {         // read with the same coalesced pattern as the store
                                     const float4 g4 = *reinterpret_cast<const float4*>(p.gate + static_cast<long long>(b) * p.c_batch +
@@ -319,7 +342,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     __syncwarp();
                 } else {
                     const int row = row0 + lane;
-                    if (row < p.M) {
+                    if (row < row_end) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int col = cbase + j;
@@ -348,7 +371,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int ctid = threadIdx.x - 6 * 32;       // 0..127
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int b_, row0_, row_end_, nt_;
+            for (uint32_t tk = 0; ok && tile_at(tk, b_, row0_, row_end_, nt_); ++tk) {
                 for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
