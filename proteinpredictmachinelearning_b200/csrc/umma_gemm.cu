@@ -44,8 +44,10 @@ int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, cud
     static const int flat_env = [] { const char* e = std::getenv("PPML_B200_GEMM_FLAT"); return e ? (e[0] != '0' ? 1 : 0) : 1; }();
     // (one column tile only: with several, a partial row tile costs every one of them and the round robin balances better;
     // measured at M = 65536: 36.5 -> 35.0 us at 256 x 256 tf32, 31.9 -> 31.3 at 128 x 256, but 57 -> 63 at 256 x 512)
-    p.flat_rows = (flat_env && p.batch == 1 && !MNMAJOR && EPI == Epi::ROW_MAJOR && p.n_tiles == 1 && p.m_tiles > grid &&
-                   p.m_tiles % grid != 0) ? 1 : 0;
+    // (and short contractions only: at K = 1024 the partial tile costs more tensor and L2 time than the balance gains,
+    // 75 -> 80 us at 65536 x 1024 x 256)
+    p.flat_rows = (flat_env && p.batch == 1 && !MNMAJOR && EPI != Epi::OPM_BLOCKED && p.n_tiles == 1 && p.k_steps <= 8 &&
+                   p.m_tiles > grid && p.m_tiles % grid != 0) ? 1 : 0;
     kern<<<grid, CONVERT ? 320 : 192, smem, st>>>(tmA, tmB, p);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
@@ -145,6 +147,12 @@ int launch_umma_gemm(const UmmaGemmArgs& a, cudaStream_t st) {
     else p.vec_ok = c_al && (a.ldc % 4 == 0) && (a.c_batch % 4 == 0) && (a.N % 4 == 0);
 
     const bool opm = a.opm_L > 0;
+    const bool fused = a.ln_stats != nullptr || a.gate != nullptr || a.act != 0;
+    if (fused) {                                   // fp32 operands, row-major result only
+        if (opm || a.elem != 0) return ST_UNSUPPORTED_PATH;
+        return (a.tf32_mode == 0) ? launch_bn<MmaKind::TF32, Epi::ROW_MAJOR_FUSED, true>(BN, tmA, tmB, p, st)
+                                  : launch_bn<MmaKind::TF32, Epi::ROW_MAJOR_FUSED, false>(BN, tmA, tmB, p, st);
+    }
     if (a.elem == 0) {
         const bool conv = (a.tf32_mode == 0);
         if (opm) return conv ? launch_bn<MmaKind::TF32, Epi::OPM_BLOCKED, true>(BN, tmA, tmB, p, st)

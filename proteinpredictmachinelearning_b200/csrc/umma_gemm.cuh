@@ -15,7 +15,10 @@
 
 namespace ppml_b200 {
 
-enum class Epi { ROW_MAJOR, OPM_BLOCKED };
+// ROW_MAJOR_FUSED: row-major store with the fused neighbours of a Linear (LayerNorm algebra, activation, gate).  An epilogue
+// of its own: compiled into the plain instance, that code slowed every HBM-bound product although it never ran there
+// (24.2 -> 31.5 us at 65536 x 128 x 256 tf32, 69.9 -> 96.8 at 65536 x 128 x 1024).
+enum class Epi { ROW_MAJOR, OPM_BLOCKED, ROW_MAJOR_FUSED };
 
 struct GemmParams {
     int M, N, K;            // per-batch extents: rows of A, rows of B, contraction length
@@ -95,6 +98,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int BK = 128 / ESIZE;                       // elements of K per stage
     constexpr uint32_t TMEM_COLS = 2 * BN;
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "UMMA N");
+
+    constexpr bool kFused = EPI == Epi::ROW_MAJOR_FUSED;
+    constexpr bool kRowMajor = EPI != Epi::OPM_BLOCKED;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -260,7 +266,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int j = lane; j < BN; j += 32) bias_s[j] = 0.0f;
             }
             float ln_mean = 0.0f, ln_rstd = 1.0f;
-            if (p.ln_stats != nullptr) {
+            if (kFused && p.ln_stats != nullptr) {
                 for (int j = lane; j < BN; j += 32) bias_s[256 + j] = (col0 + j < p.N) ? p.ln_u[col0 + j] : 0.0f;
                 const int rown = trow0 + q * 32 + lane;
                 if (rown < p.M) {
@@ -288,7 +294,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     f[j4 * 4 + 2] = fmaf(__uint_as_float(v[j4 * 4 + 2]), p.alpha, b4.z);
                     f[j4 * 4 + 3] = fmaf(__uint_as_float(v[j4 * 4 + 3]), p.alpha, b4.w);
                 }
-                if (p.ln_stats != nullptr) {
+                if (kFused && p.ln_stats != nullptr) {
                     // f = alpha * acc + bias so far; the LayerNorm form is rstd * (alpha * acc - mean * u) + bias
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -304,7 +310,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         f[j] = x;
                     }
                 }
-                if (p.act != 0 && p.gate == nullptr) {
+                if (kFused && p.act != 0 && p.gate == nullptr) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = act_apply(p.act, f[j]);
                 }
@@ -322,8 +328,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         const int row = row0 + rr;
                         float4 val = *reinterpret_cast<const float4*>(stage + rr * kEpiStagePitch + cc * 16);
                         if (row < row_end && col < p.N) {    // vec_ok: N, ldc (or L) are multiples of 4
-                            if constexpr (EPI == Epi::ROW_MAJOR) {
-                                if (p.gate != nullptr) {         // read with the same coalesced pattern as the store
+                            if constexpr (kRowMajor) {
+                                if (kFused && p.gate != nullptr) {         // read with the same coalesced pattern as the store
                                     const float4 g4 = *reinterpret_cast<const float4*>(p.gate + static_cast<long long>(b) * p.c_batch +
                                                                                         static_cast<long long>(row) * p.ldc + col);
                                     val.x = act_apply(p.act, val.x) * g4.x; val.y = act_apply(p.act, val.y) * g4.y;
@@ -347,9 +353,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         for (int j = 0; j < 32; ++j) {
                             const int col = cbase + j;
                             if (col < p.N) {
-                                if constexpr (EPI == Epi::ROW_MAJOR) {
+                                if constexpr (kRowMajor) {
                                     const long long off = static_cast<long long>(b) * p.c_batch + static_cast<long long>(row) * p.ldc + col;
-                                    p.C[off] = (p.gate != nullptr) ? act_apply(p.act, f[j]) * p.gate[off] : f[j];
+                                    p.C[off] = (kFused && p.gate != nullptr) ? act_apply(p.act, f[j]) * p.gate[off] : f[j];
                                 } else {
                                     const int L = p.opm_L, D = p.opm_D;
                                     const int d1 = row / L, ii = row - d1 * L;
