@@ -37,6 +37,14 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with launch_pdl() may start (its CTAs become resident and run their prologue) while the kernel before it
+// in the stream is still running; pdl_wait() blocks until that kernel has completed and its memory operations are visible,
+// so everything after it keeps the stream's ordering.  Every kernel that is launched this way calls pdl_wait() before its
+// first access to global memory.  pdl_launch_dependents() lets the next kernel of the stream begin launching early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier -------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -363,4 +371,24 @@ __device__ __forceinline__ float tf32_round(float x) {
     return __uint_as_float(u);
 }
 
+}  // namespace ppml_b200
+
+// ---- host: launch with programmatic stream serialization (PPML_B200_PDL=0 switches it off) -----------------------------
+#include <cstdlib>
+#include <utility>
+namespace ppml_b200 {
+inline bool pdl_enabled() {
+    static const bool on = [] { const char* e = std::getenv("PPML_B200_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 }  // namespace ppml_b200

@@ -222,6 +222,8 @@ __device__ __forceinline__ void quantize_rows2(const uint8_t* raw, uint8_t* at, 
 __global__ void __launch_bounds__(256)
 quantize_q8_planar_kernel(const float* __restrict__ X, int8_t* __restrict__ Aq, __half* __restrict__ da_t,
                           int Ntok, int K, int nblk, long long nthreads) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long g = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
     if (g >= nthreads) return;                    // nthreads is a multiple of 8: whole 8-thread groups leave together
     const int sub = static_cast<int>(g & 7);
@@ -273,6 +275,8 @@ quantize_q8_planar_tile_kernel(const float* __restrict__ X, int8_t* __restrict__
     constexpr int PIECES = 128 * KW / 8;          // 32-byte pieces in the tile
     constexpr int ITERS = PIECES / 256;
     __shared__ __half sc[NB][128];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tile_row0 = blockIdx.y * 128, k0 = blockIdx.x * KW;
 #pragma unroll 4
     for (int it = 0; it < ITERS; ++it) {
@@ -394,7 +398,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     uint8_t* sg = smem_raw;
-    if ((smem_base & 1023u) != 0u) {             // the swizzled tiles need a 1024-byte aligned base: refuse to run otherwise
+    pdl_launch_dependents();        // the next kernel of the stream may set itself up while this one runs (see pdl_wait below)
+    if ((smem_base & 1023u) != 0u) {
+        pdl_wait();             // the swizzled tiles need a 1024-byte aligned base: refuse to run otherwise
         if (threadIdx.x == 0) { p.err[0] = ST_DEVICE_ABORT; p.err[1] = 0x1001; }
         return;
     }
@@ -447,6 +453,9 @@ umma_q8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers, TMEM and descriptors are set up: from here on global memory is touched, which needs the kernels before this
+    // one in the stream to be complete
+    pdl_wait();
 
     const int total_items = p.m_tiles * p.groups;
     // The k-th work item of this CTA: token tile `mt`, weight column blocks [nb0, nb1).  Two schedules:
@@ -1050,11 +1059,11 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
         // (the tile kernels want a few CTAs per SM; with few token tiles the one-piece-per-thread kernel spreads wider)
         const bool wide = static_cast<long long>(p.m_tiles) * (K / 128) >= 4LL * sms;
         if (wide && x_aligned && K % 256 == 0 && p.m_tiles <= 65535)
-            quantize_q8_planar_tile_kernel<256><<<dim3(K / 256, p.m_tiles), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk);
+            launch_pdl(quantize_q8_planar_tile_kernel<256>, dim3(K / 256, p.m_tiles), dim3(256), 0, st, X, aq, da_t, N, K, p.nblk);
         else if (wide && x_aligned && K % 128 == 0 && p.m_tiles <= 65535)
-            quantize_q8_planar_tile_kernel<128><<<dim3(K / 128, p.m_tiles), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk);
+            launch_pdl(quantize_q8_planar_tile_kernel<128>, dim3(K / 128, p.m_tiles), dim3(256), 0, st, X, aq, da_t, N, K, p.nblk);
         else
-            quantize_q8_planar_kernel<<<static_cast<unsigned>(qgrid), 256, 0, st>>>(X, aq, da_t, N, K, p.nblk, nthreads);
+            launch_pdl(quantize_q8_planar_kernel, dim3(static_cast<unsigned>(qgrid)), dim3(256), 0, st, X, aq, da_t, N, K, p.nblk, nthreads);
         if (cudaGetLastError() != cudaSuccess) return ST_QUANT;
         if (!make_tmap_3d(&tmX, TmaType::U8, aq, K, N, 1, static_cast<uint64_t>(K), 0, 128, 128, 1)) return ST_UNSUPPORTED_PATH;
     } else
@@ -1087,16 +1096,16 @@ int launch_umma_q8(const void* W, const float* X, float* C, int M, int N, int K,
     const bool four = p.blocks_per_group == 1 || (!p.preq && p.KT == kMaxKT && p.blocks_per_group <= 4);
     const bool staged = p.staged != 0 && c_trans && (p.nblk & 3) == 0;
     const int th2 = Roles<2>::kThreads, th4 = Roles<4>::kThreads;
-    if (sumi_out != nullptr) umma_q8_kernel<true, 2, false, false><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+    if (sumi_out != nullptr) launch_pdl(umma_q8_kernel<true, 2, false, false>, dim3(grid), dim3(th2), smem, st, tmX, tmW, tmC, p);
     else if (!staged) {
-        if (four) umma_q8_kernel<false, 4, false, false><<<grid, th4, smem, st>>>(tmX, tmW, tmC, p);
-        else umma_q8_kernel<false, 2, false, false><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+        if (four) launch_pdl(umma_q8_kernel<false, 4, false, false>, dim3(grid), dim3(th4), smem, st, tmX, tmW, tmC, p);
+        else launch_pdl(umma_q8_kernel<false, 2, false, false>, dim3(grid), dim3(th2), smem, st, tmX, tmW, tmC, p);
     } else if (four) {
-        if (resident) umma_q8_kernel<false, 4, true, true><<<grid, th4, smem, st>>>(tmX, tmW, tmC, p);
-        else umma_q8_kernel<false, 4, false, true><<<grid, th4, smem, st>>>(tmX, tmW, tmC, p);
+        if (resident) launch_pdl(umma_q8_kernel<false, 4, true, true>, dim3(grid), dim3(th4), smem, st, tmX, tmW, tmC, p);
+        else launch_pdl(umma_q8_kernel<false, 4, false, true>, dim3(grid), dim3(th4), smem, st, tmX, tmW, tmC, p);
     } else {
-        if (resident) umma_q8_kernel<false, 2, true, true><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
-        else umma_q8_kernel<false, 2, false, true><<<grid, th2, smem, st>>>(tmX, tmW, tmC, p);
+        if (resident) launch_pdl(umma_q8_kernel<false, 2, true, true>, dim3(grid), dim3(th2), smem, st, tmX, tmW, tmC, p);
+        else launch_pdl(umma_q8_kernel<false, 2, false, true>, dim3(grid), dim3(th2), smem, st, tmX, tmW, tmC, p);
     }
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
