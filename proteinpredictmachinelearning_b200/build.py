@@ -13,7 +13,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
-SOURCES = ["simt_kernels.cu", "umma_gemm.cu", "umma_q8.cu", "umma_attn.cu", "attn_backward.cu", "noalloc.cu", "peer_exchange.cu", "capi.cu",
+SOURCES = ["simt_kernels.cu", "umma_gemm.cu", "umma_q8.cu", "umma_attn.cu", "attn_backward.cu", "attn_mma8.cu", "noalloc.cu", "peer_exchange.cu", "capi.cu",
            "tma_host.cpp", "host_quant.cpp", "q8_file.cpp", "ppml_forwarders.cpp"]
 
 

@@ -293,7 +293,14 @@ int flash_attn_any(const ppml_b200_flash_cfg* cfg, int Lk, int64_t bias_batch_st
     if (path != PPML_B200_PATH_SIMT) {
         const int rc = launch_umma_attn(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0,
                                         scale, cfg->softmax_eps, bias_batch_stride, ft, lay, as_stream(stream));
-        if (rc != ST_UNSUPPORTED_PATH || path == PPML_B200_PATH_UMMA) return rc;
+        if (rc != ST_UNSUPPORTED_PATH) return rc;
+        if (elem == 0) {
+            const int rc8 = launch_attn_d8_mma(static_cast<const float*>(Q), static_cast<const float*>(K), static_cast<const float*>(V),
+                                               bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
+                                               cfg->softmax_eps, bias_batch_stride, ft, lay, as_stream(stream));
+            if (rc8 != ST_UNSUPPORTED_PATH) return rc8;
+        }
+        if (path == PPML_B200_PATH_UMMA) return rc;
     }
     return launch_attn_rowwarp(Q, K, V, elem, bias, O, LSE, cfg->B, cfg->h, cfg->L, Lk, cfg->d, cfg->causal ? 1 : 0, scale,
                                cfg->softmax_eps, bias_batch_stride, ft, lay, as_stream(stream));

@@ -345,6 +345,18 @@ __device__ __forceinline__ void rows_to_line_pieces(float (&v)[32], int lane) {
     }
 }
 
+// the activations of the reference's act_fwd_scalar (src/backend/CPUKernels.cpp:1903-1916), same formulas
+__device__ __forceinline__ float act_scalar(int kind, float x) {
+    switch (kind) {
+        case 1: return 1.0f / (1.0f + expf(-x));
+        case 2: return x / (1.0f + expf(-x));
+        case 3: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        case 4: return tanhf(x);
+        case 5: return x > 0.0f ? x : 0.0f;
+        default: return x;
+    }
+}
+
 // ---- packed fp32 pairs (one issue slot for two lanes of add / mul / fma) ------------------------
 __device__ __forceinline__ uint64_t pack2(float a, float b) {
     uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r;

@@ -68,6 +68,11 @@ struct AttnLayout {
 int launch_attn_backward(int B, int H, int L, int d, int causal, float scale, const float* Q, const float* K, const float* V,
                          const float* bias, long long bias_batch_stride, const float* O, const float* dO, const float* LSE,
                          float* dQ, float* dK, float* dV, float* dbias, cudaStream_t st);
+// head dim 8, fp32 operands with 16-byte aligned K / V rows, at least 16 query rows: warp-level tensor-core kernel (tf32
+// products); ST_UNSUPPORTED_PATH otherwise
+int launch_attn_d8_mma(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE, int B, int H,
+                       int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft,
+                       const AttnLayout& lay, cudaStream_t st);
 int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, const float* bias, float* O, float* LSE,
                         int B, int H, int L, int Lk, int d, int causal, float scale, float eps,
                         long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st);

@@ -33,18 +33,6 @@ template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; 
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// the activations of the reference's act_fwd_scalar (src/backend/CPUKernels.cpp:1903-1916), same formulas
-__device__ __forceinline__ float act_scalar(int kind, float x) {
-    switch (kind) {
-        case 1: return 1.0f / (1.0f + expf(-x));
-        case 2: return x / (1.0f + expf(-x));
-        case 3: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-        case 4: return tanhf(x);
-        case 5: return x > 0.0f ? x : 0.0f;
-        default: return x;
-    }
-}
-
 template <typename T, bool A_KFAST, bool B_KFAST>
 __global__ void __launch_bounds__(256)
 simt_contract_kernel(const T* __restrict__ A, const T* __restrict__ B, float* __restrict__ C, SimtContract p) {
@@ -516,78 +504,106 @@ attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* _
 }
 
 // =============================================================================================
-// Small head dims (4, 8, 16: the extra-MSA blocks use 8): one thread per query row, 128 rows per CTA.  Keys are
-// walked in tiles of 32; the K and V tiles are staged in shared memory as fp32 (every thread reads the same key, so
-// the reads are broadcasts), the 32 scores of a tile stay in registers, and the running maximum / sum / output
-// accumulator are per-thread scalars: no shuffles and no cross-lane reductions.  Same arithmetic contract as the
-// kernel above; exp is 2^((s - m) log2 e) on the transcendental unit.
+// Small head dims (4, 8, 16: the extra-MSA blocks use 8): one thread per R query rows, R * NT rows per CTA.  Keys are
+// walked in tiles of 16; the K and V tiles are staged in shared memory as fp32 and every thread reads the same key,
+// so the reads are broadcasts -- and they are what the load/store pipe spends its time on, which is why a thread owns
+// R rows: one 16-byte read of K or V serves R rows.  The arithmetic is packed fp32 pairs (one issue slot for two
+// FMAs): the score is summed over channel pairs (even and odd channels apart, one add at the end, the bias as the
+// start value), the P V product over key pairs (V is staged with the two keys of a pair interleaved, the
+// accumulators of even and odd keys are added at the end).  Running maximum / sum / accumulators are per-thread
+// scalars: no shuffles and no cross-lane reductions.  Same arithmetic contract as the kernel above; exp is
+// 2^((s - m) log2 e) on the transcendental unit.
 // =============================================================================================
 // 2^x on the transcendental unit (about 2 ulp); results below the normal range flush to 0, 2^-inf = 0
 __device__ __forceinline__ float ex2_fast(float x) {
     float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(128)
+template <typename T, int D, int R, int NT>
+__global__ void __launch_bounds__(NT)
 attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                       const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
                       int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft,
-                      const AttnLayout lay) {
-    constexpr int kTile = 32;
+                      int bias_vec, const AttnLayout lay) {
+    constexpr int kTile = 16;
+    constexpr int kRows = R * NT;
     constexpr float kLog2e = 1.4426950408889634f;
-    constexpr int kPer = (kTile * D + 127) / 128;               // K (and V) elements each thread moves per tile
-    constexpr int kPitch = 36;
+    constexpr int kPer = (kTile * D + NT - 1) / NT;             // K (and V) elements each thread moves per tile
+    constexpr int kPitch = kTile + 4;                           // 80-byte bias rows: 16-byte reads of 8 lanes hit 8 bank groups
+    constexpr int D2 = D / 2, D4 = D / 4;
     // two stages of everything: the next tile's K / V travel through registers and its bias through cp.async while
     // the current tile is consumed
-    __shared__ __align__(16) float ks_all[2][kTile * D];
-    __shared__ __align__(16) float vs_all[2][kTile * D];
-    __shared__ __align__(16) float bs_all[2][128 * kPitch];
-    const int i = blockIdx.x * 128 + threadIdx.x;
+    __shared__ __align__(16) float ks_all[2][kTile * D];        // [key][channel]
+    __shared__ __align__(16) float vs_all[2][kTile * D];        // [key pair][channel][key of the pair]
+    __shared__ __align__(16) float bs_all[2][kRows * kPitch];   // [row of the CTA][key]
     const int hh = blockIdx.y, b = blockIdx.z;
     const size_t bh = static_cast<size_t>(b) * H + hh;
     const T* Kb = K + b * lay.k_b + hh * lay.k_h;
     const T* Vb = V + b * lay.v_b + hh * lay.v_h;
-    const bool row_ok = i < L;
-    float q[D];
-#pragma unroll
-    for (int dd = 0; dd < D; ++dd) q[dd] = row_ok ? attn_ld(Q + b * lay.q_b + hh * lay.q_h + static_cast<long long>(i) * lay.q_l + dd) * scale : 0.0f;
-    // bias: every warp brings the 32 x 32 tile of its own rows through shared memory (row by row, 128 contiguous bytes
-    // per request) and each thread then reads its row back with 16-byte loads; the pitch of 36 floats keeps both sides
-    // free of bank conflicts
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wrow0 = blockIdx.x * 128 + warp * 32;              // first query row of this warp
-    const float* Bw = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
-                                 (static_cast<size_t>(hh) * L + wrow0) * static_cast<size_t>(Lk) : nullptr;
-    const int jmax = row_ok ? (causal ? min(i + 1, Lk) : Lk) : 0;
-    // keys needed by any row of this CTA
-    const int last_row = min(blockIdx.x * 128 + 127, L - 1);
-    const int jend = causal ? min(last_row + 1, Lk) : Lk;
-    float m = -CUDART_INF_F, l = 0.0f;
-    float mfirst = -CUDART_INF_F;                    // maximum over the first `ft` keys
-    float acc[D];
+    const int row0 = blockIdx.x * kRows;
+    // row k of this thread: row0 + k * NT + threadIdx.x (a warp's rows of one k are consecutive)
+    int jmax[R];
+    uint64_t q2[R][D2];
 #pragma unroll
-    for (int dd = 0; dd < D; ++dd) acc[dd] = 0.0f;
+    for (int k = 0; k < R; ++k) {
+        const int i = row0 + k * NT + threadIdx.x;
+        const bool ok = i < L;
+        jmax[k] = ok ? (causal ? min(i + 1, Lk) : Lk) : 0;
+        const T* qp = Q + b * lay.q_b + hh * lay.q_h + static_cast<long long>(ok ? i : 0) * lay.q_l;
+#pragma unroll
+        for (int c = 0; c < D2; ++c)
+            q2[k][c] = ok ? pack2(attn_ld(qp + 2 * c) * scale, attn_ld(qp + 2 * c + 1) * scale) : 0ull;
+    }
+    const float* Bh = bias ? bias + static_cast<size_t>(b) * bias_batch_stride + static_cast<size_t>(hh) * L * static_cast<size_t>(Lk)
+                           : nullptr;
+    // keys needed by any row of this CTA
+    const int last_row = min(row0 + kRows - 1, L - 1);
+    const int jend = causal ? min(last_row + 1, Lk) : Lk;
+    float m[R], mfirst[R];
+    uint64_t l2[R], acc2[R][D];                      // sums over even and odd keys apart
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+        m[k] = -CUDART_INF_F; mfirst[k] = -CUDART_INF_F; l2[k] = 0ull;
+#pragma unroll
+        for (int dd = 0; dd < D; ++dd) acc2[k][dd] = 0ull;
+    }
     float kreg[kPer], vreg[kPer];
     auto fetch_kv = [&](int j0) {
 #pragma unroll
         for (int c = 0; c < kPer; ++c) {
-            const int e = threadIdx.x + c * 128;
+            const int e = threadIdx.x + c * NT;
             const bool ok = e < kTile * D && j0 + e / D < Lk;
             kreg[c] = ok ? attn_ld(Kb + static_cast<long long>(j0 + e / D) * lay.k_l + e % D) : 0.0f;
             vreg[c] = ok ? attn_ld(Vb + static_cast<long long>(j0 + e / D) * lay.v_l + e % D) : 0.0f;
         }
     };
+    // bias: every warp brings the 32 x 16 tiles of its own rows through shared memory (coalesced on the global side)
+    // and each thread then reads its rows back with 16-byte loads
     auto fetch_bias = [&](int j0, int buf) {
-        if (Bw) {
-            const bool col_ok = j0 + lane < Lk;
-#pragma unroll 8
-            for (int rr = 0; rr < 32; ++rr) {
-                float* dst = &bs_all[buf][(warp * 32 + rr) * kPitch + lane];
-                if (col_ok && wrow0 + rr < L) {
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
-                                 "l"(Bw + static_cast<size_t>(rr) * Lk + j0 + lane) : "memory");
+        if (Bh) {
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const int rl0 = k * NT + warp * 32;                      // first row (within the CTA) of this 32-row tile
+                if (bias_vec) {
+                    // 16 bytes per lane: four lanes per row, eight rows per instruction
+#pragma unroll
+                    for (int it = 0; it < 4; ++it) {
+                        const int rl = rl0 + it * 8 + (lane >> 2), c = (lane & 3) * 4;
+                        const bool ok = row0 + rl < L && j0 + c < Lk;    // Lk is a multiple of 4 here
+                        const float* src = ok ? Bh + static_cast<size_t>(row0 + rl) * Lk + j0 + c : Bh;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(
+                                         __cvta_generic_to_shared(&bs_all[buf][rl * kPitch + c]))), "l"(src), "r"(ok ? 16 : 0) : "memory");
+                    }
                 } else {
-                    *dst = 0.0f;
+#pragma unroll
+                    for (int it = 0; it < 16; ++it) {
+                        const int rl = rl0 + it * 2 + (lane >> 4), c = lane & 15;
+                        const bool ok = row0 + rl < L && j0 + c < Lk;
+                        const float* src = ok ? Bh + static_cast<size_t>(row0 + rl) * Lk + j0 + c : Bh;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(static_cast<uint32_t>(
+                                         __cvta_generic_to_shared(&bs_all[buf][rl * kPitch + c]))), "l"(src), "r"(ok ? 4 : 0) : "memory");
+                    }
                 }
             }
         }
@@ -595,6 +611,7 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
     };
     fetch_kv(0);
     fetch_bias(0, 0);
+    const uint64_t log2e2 = pack2(kLog2e, kLog2e);
     for (int j0 = 0, tile = 0; j0 < jend; j0 += kTile, ++tile) {
         const int buf = tile & 1;
         float* ks = ks_all[buf];
@@ -603,68 +620,132 @@ attn_rowthread_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T*
         // this stage was last read two tiles ago, and every thread has passed the barrier of the tile in between
 #pragma unroll
         for (int c = 0; c < kPer; ++c) {
-            const int e = threadIdx.x + c * 128;
-            if (e < kTile * D) { ks[e] = kreg[c]; vs[e] = vreg[c]; }
+            const int e = threadIdx.x + c * NT;
+            if (e < kTile * D) {
+                const int key = e / D, dd = e % D;
+                ks[e] = kreg[c];
+                vs[((key >> 1) * D + dd) * 2 + (key & 1)] = vreg[c];
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         if (j0 + kTile < jend) { fetch_kv(j0 + kTile); fetch_bias(j0 + kTile, buf ^ 1); }
-        if (j0 >= jmax) continue;                    // nothing visible to this row in the tile (still joins the barriers)
-        float x[kTile];
-        float mt = -CUDART_INF_F;
+        // scores: x[k][t] starts as the bias and becomes q . k_t + bias
+        float x[R][kTile];
 #pragma unroll
-        for (int t = 0; t < kTile; ++t) {
-            float dot = 0.0f;
+        for (int k = 0; k < R; ++k) {
+            if (Bh) {
 #pragma unroll
-            for (int dd = 0; dd < D; ++dd) dot = fmaf(q[dd], ks[t * D + dd], dot);
-            x[t] = dot;
-        }
-        if (Bw) {
+                for (int t4 = 0; t4 < kTile / 4; ++t4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bs + (k * NT + threadIdx.x) * kPitch + t4 * 4);
+                    x[k][t4 * 4] = b4.x; x[k][t4 * 4 + 1] = b4.y; x[k][t4 * 4 + 2] = b4.z; x[k][t4 * 4 + 3] = b4.w;
+                }
+            } else {
 #pragma unroll
-            for (int t4 = 0; t4 < kTile / 4; ++t4) {
-                const float4 b4 = *reinterpret_cast<const float4*>(bs + threadIdx.x * kPitch + t4 * 4);
-                x[t4 * 4] += b4.x; x[t4 * 4 + 1] += b4.y; x[t4 * 4 + 2] += b4.z; x[t4 * 4 + 3] += b4.w;
+                for (int t = 0; t < kTile; ++t) x[k][t] = 0.0f;
             }
         }
 #pragma unroll
         for (int t = 0; t < kTile; ++t) {
-            if (j0 + t >= jmax) x[t] = -CUDART_INF_F;
-            mt = fmaxf(mt, x[t]);
-        }
-        if (j0 < ft) {
-            if (j0 + kTile <= ft) mfirst = fmaxf(mfirst, mt);
-            else {
+            uint64_t kk[D2];
 #pragma unroll
-                for (int t = 0; t < kTile; ++t) if (j0 + t < ft) mfirst = fmaxf(mfirst, x[t]);
+            for (int c4 = 0; c4 < D4; ++c4) {
+                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(ks + t * D + c4 * 4);
+                kk[2 * c4] = v.x; kk[2 * c4 + 1] = v.y;
+            }
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                uint64_t s = pack2(x[k][t], 0.0f);
+#pragma unroll
+                for (int c = 0; c < D2; ++c) s = ffma2(q2[k][c], kk[c], s);
+                float se, so; unpack2(s, se, so);
+                x[k][t] = se + so;
             }
         }
-        const float m_new = fmaxf(m, mt);
-        if (m_new == -CUDART_INF_F) continue;        // every key so far is masked for this row
-        const float alpha = (m == -CUDART_INF_F) ? 0.0f : ex2_fast((m - m_new) * kLog2e);
-        const float ml2 = m_new * kLog2e;
-        float lt = 0.0f;
+        // per row: mask, maximum, rescale factor, probabilities (in place of the scores)
+        uint64_t alpha2[R];
 #pragma unroll
-        for (int dd = 0; dd < D; ++dd) acc[dd] *= alpha;
+        for (int k = 0; k < R; ++k) {
+            if (j0 + kTile > jmax[k]) {
 #pragma unroll
-        for (int t = 0; t < kTile; ++t) {
-            const float pj = ex2_fast(fmaf(x[t], kLog2e, -ml2));      // 2^-inf = 0 for masked keys
-            lt += pj;
+                for (int t = 0; t < kTile; ++t) if (j0 + t >= jmax[k]) x[k][t] = -CUDART_INF_F;
+            }
+            float mt = -CUDART_INF_F;
 #pragma unroll
-            for (int dd = 0; dd < D; ++dd) acc[dd] = fmaf(pj, vs[t * D + dd], acc[dd]);
+            for (int t = 0; t < kTile; ++t) mt = fmaxf(mt, x[k][t]);
+            if (j0 < ft) {
+                if (j0 + kTile <= ft) mfirst[k] = fmaxf(mfirst[k], mt);
+                else {
+#pragma unroll
+                    for (int t = 0; t < kTile; ++t) if (j0 + t < ft) mfirst[k] = fmaxf(mfirst[k], x[k][t]);
+                }
+            }
+            const float m_new = fmaxf(m[k], mt);
+            // nothing visible so far: alpha = 0 and every probability 2^-inf = 0, the state stays empty
+            const float alpha = (m[k] == -CUDART_INF_F) ? 0.0f : ex2_fast((m[k] - m_new) * kLog2e);
+            const float ml2 = (m_new == -CUDART_INF_F) ? 0.0f : m_new * kLog2e;
+            const uint64_t nml2 = pack2(-ml2, -ml2);
+            alpha2[k] = pack2(alpha, alpha);
+            uint64_t lt = 0ull;
+#pragma unroll
+            for (int tp = 0; tp < kTile / 2; ++tp) {
+                float e0, e1;
+                unpack2(ffma2(pack2(x[k][2 * tp], x[k][2 * tp + 1]), log2e2, nml2), e0, e1);
+                x[k][2 * tp] = ex2_fast(e0);
+                x[k][2 * tp + 1] = ex2_fast(e1);
+                lt = fadd2(lt, pack2(x[k][2 * tp], x[k][2 * tp + 1]));
+            }
+            l2[k] = ffma2(l2[k], alpha2[k], lt);
+            m[k] = m_new;
+#pragma unroll
+            for (int dd = 0; dd < D; ++dd) acc2[k][dd] = fmul2(acc2[k][dd], alpha2[k]);
         }
-        l = fmaf(l, alpha, lt);
-        m = m_new;
+        // P V over key pairs
+#pragma unroll
+        for (int tp = 0; tp < kTile / 2; ++tp) {
+            uint64_t vv[D];
+#pragma unroll
+            for (int c2 = 0; c2 < D2; ++c2) {
+                const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(vs + tp * 2 * D + c2 * 4);
+                vv[2 * c2] = v.x; vv[2 * c2 + 1] = v.y;
+            }
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const uint64_t p2 = pack2(x[k][2 * tp], x[k][2 * tp + 1]);
+#pragma unroll
+                for (int dd = 0; dd < D; ++dd) acc2[k][dd] = ffma2(p2, vv[dd], acc2[k][dd]);
+            }
+        }
     }
-    if (!row_ok) return;
-    if (ft > 0 && mfirst == -CUDART_INF_F) l = 0.0f; // the reference's first key tile is fully masked: O = 0, LSE = -inf
-    const long long ooff = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l;
-    const long long goff = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l;
-    float* o = O + ooff;
-    float inv = 0.0f, lse = -CUDART_INF_F;
-    if (l > 0.0f) { inv = 1.0f / (l + eps); lse = m + logf(l + eps); }
 #pragma unroll
-    for (int dd = 0; dd < D; ++dd) o[dd] = lay.gate ? act_scalar(lay.act, lay.gate[goff + dd]) * (acc[dd] * inv) : acc[dd] * inv;
-    if (LSE) LSE[bh * L + i] = lse;
+    for (int k = 0; k < R; ++k) {
+        const int i = row0 + k * NT + threadIdx.x;
+        if (i >= L) continue;
+        float le, lo; unpack2(l2[k], le, lo);
+        float l = le + lo;
+        if (ft > 0 && mfirst[k] == -CUDART_INF_F) l = 0.0f;  // the reference's first key tile is fully masked: O = 0, LSE = -inf
+        const long long ooff = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l;
+        const long long goff = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l;
+        float* o = O + ooff;
+        float inv = 0.0f, lse = -CUDART_INF_F;
+        if (l > 0.0f) { inv = 1.0f / (l + eps); lse = m[k] + logf(l + eps); }
+        float r[D];
+#pragma unroll
+        for (int dd = 0; dd < D; ++dd) {
+            float ae, ao; unpack2(acc2[k][dd], ae, ao);
+            const float v = (ae + ao) * inv;
+            r[dd] = lay.gate ? act_scalar(lay.act, lay.gate[goff + dd]) * v : v;
+        }
+        if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+            for (int c4 = 0; c4 < D4; ++c4)
+                *reinterpret_cast<float4*>(o + c4 * 4) = make_float4(r[c4 * 4], r[c4 * 4 + 1], r[c4 * 4 + 2], r[c4 * 4 + 3]);
+        } else {
+#pragma unroll
+            for (int dd = 0; dd < D; ++dd) o[dd] = r[dd];
+        }
+        if (LSE) LSE[bh * L + i] = lse;
+    }
 }
 
 // Small head dims with few query rows (global column attention: one query over all keys): one warp per query row,
@@ -754,13 +835,31 @@ bool launch_attn_keylanes(const T* Q, const T* K, const T* V, const float* bias,
     return true;
 }
 
+template <typename T, int D>
+void launch_attn_rowthread_d(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
+                             int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft, int bias_vec,
+                             const AttnLayout& lay, cudaStream_t st) {
+    // two rows per thread; the CTA shrinks with the number of query rows so that short sequences still fill their CTAs
+    if (L > 128) {
+        dim3 grid((L + 255) / 256, H, B);
+        attn_rowthread_kernel<T, D, 2, 128><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay);
+    } else if (L > 64) {
+        dim3 grid((L + 127) / 128, H, B);
+        attn_rowthread_kernel<T, D, 2, 64><<<grid, 64, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay);
+    } else {
+        dim3 grid((L + 63) / 64, H, B);
+        attn_rowthread_kernel<T, D, 2, 32><<<grid, 32, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay);
+    }
+}
+
 template <typename T>
 bool launch_attn_rowthread(const T* Q, const T* K, const T* V, const float* bias, float* O, float* LSE, int B, int H, int L,
                            int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft, const AttnLayout& lay, cudaStream_t st) {
-    dim3 grid((L + 127) / 128, H, B);
-    if (d == 4) attn_rowthread_kernel<T, 4><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, lay);
-    else if (d == 8) attn_rowthread_kernel<T, 8><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, lay);
-    else if (d == 16) attn_rowthread_kernel<T, 16><<<grid, 128, 0, st>>>(Q, K, V, bias, O, LSE, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, lay);
+    // 16-byte bias copies need whole 16-byte pieces in every row
+    const int bias_vec = bias != nullptr && (Lk & 3) == 0 && (bias_batch_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
+    if (d == 4) launch_attn_rowthread_d<T, 4>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
+    else if (d == 8) launch_attn_rowthread_d<T, 8>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
+    else if (d == 16) launch_attn_rowthread_d<T, 16>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
     else return false;
     return true;
 }

@@ -379,20 +379,56 @@ def test_attention_shapes(oracle, B, h, L, d, Lk, bias, bcast):
     (4, 2, 1, 8, 1024, False, False, False),    # global column attention at full key count
     (2, 2, 20, 16, None, False, False, True),   # few rows, causal (lanes without any visible key)
 ])
-def test_attention_small_head_dims(oracle, B, h, L, d, Lk, bias, bcast, causal):
+@pytest.mark.parametrize("path", [PATH_SIMT, PATH_AUTO])
+def test_attention_small_head_dims(oracle, B, h, L, d, Lk, bias, bcast, causal, path):
+    """The exact CUDA-core kernels (PATH_SIMT), and whatever PATH_AUTO picks: for d = 8 with 16 or more query rows that
+    is the warp-level tensor-core kernel with tf32 products."""
+    tensor = path == PATH_AUTO and d == 8 and L >= 16
+    tol_o, tol_l = (TOL_TF32, 2e-3) if tensor else (TOL_FP32, 1e-5)
     Q, K, V, bi = cases.attn_case(B, h, L, d, Lk=Lk, seed=9, bias=bias, bias_bcast=bcast)
     if bi is not None:
         bi[..., 1, :] = -np.inf                  # one fully masked query row per head
         bi[..., 0, ::3] = -np.inf                # and a partly masked one
     scale = 1 / np.sqrt(32.0)
     O, LSE = ops.flash_attn_forward_cuda(dev(Q), dev(K), dev(V), None if bi is None else dev(bi), scale=scale, bias_bcast=bcast,
-                                         causal=causal)
+                                         causal=causal, path=path)
     rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast, causal=causal)
     O, LSE = host(O), host(LSE)
     assert np.isfinite(O).all()
-    assert cases.rel_err(O, rO) <= TOL_FP32
+    assert cases.rel_err(O, rO) <= tol_o
     fin = np.isfinite(rL)
-    assert np.array_equal(np.isfinite(LSE), fin) and np.abs(LSE[fin] - rL[fin]).max() <= 1e-5
+    assert np.array_equal(np.isfinite(LSE), fin) and np.abs(LSE[fin] - rL[fin]).max() <= tol_l
+
+
+@pytest.mark.parametrize("B,h,L,Lk,bias,bcast,causal", [
+    (1024 // 64, 8, 256, None, True, True, False),   # extra-MSA rows (fewer batch elements): four batch elements per CTA
+    (6, 3, 100, None, True, True, False),       # batch not a multiple of 4, rows not a multiple of 32, ragged key tile
+    (5, 2, 130, 70, True, False, False),        # a bias per batch element: 128 rows of one batch element per CTA
+    (4, 2, 200, 203, True, True, False),        # key count not a multiple of 4: the bias tile comes in 4-byte pieces
+    (3, 2, 90, None, True, True, False),        # fewer than four batch elements
+    (4, 2, 150, None, False, False, True),      # causal without bias
+    (4, 2, 33, 130, True, True, True),          # causal with Lk > L
+    (8, 4, 16, 300, False, False, False),       # a single m tile of rows, five key tiles
+])
+def test_attention_head_dim_8_tensor_cores(oracle, B, h, L, Lk, bias, bcast, causal):
+    """Head dim 8 on the warp-level tensor-core kernel (tf32 products, fp32 softmax) against the oracle, with a fully
+    masked and a partly masked query row, and against the exact CUDA-core kernel."""
+    Q, K, V, bi = cases.attn_case(B, h, L, 8, Lk=Lk, seed=21, bias=bias, bias_bcast=bcast)
+    if bi is not None:
+        bi[..., 1, :] = -np.inf
+        bi[..., 0, ::3] = -np.inf
+    scale = 1 / np.sqrt(8.0)
+    args = (dev(Q), dev(K), dev(V), None if bi is None else dev(bi))
+    O, LSE = ops.flash_attn_forward_cuda(*args, scale=scale, bias_bcast=bcast, causal=causal, path=PATH_UMMA)
+    rO, rL = oracle.flash_attn(Q, K, V, bi, scale=scale, bias_bcast=bcast, causal=causal)
+    O, LSE = host(O), host(LSE)
+    assert np.isfinite(O).all() and cases.rel_err(O, rO) <= TOL_TF32
+    fin = np.isfinite(rL)
+    assert np.array_equal(np.isfinite(LSE), fin) and np.abs(LSE[fin] - rL[fin]).max() <= 2e-3
+    if bi is not None:
+        assert np.all(O[:, :, 1] == 0) and np.all(LSE[:, :, 1] == -np.inf)
+    Oe, _ = ops.flash_attn_forward_cuda(*args, scale=scale, bias_bcast=bcast, causal=causal, path=PATH_SIMT)
+    assert cases.rel_err(O, host(Oe)) <= TOL_TF32
 
 
 @pytest.mark.parametrize("B,h,L,Lk,bias,bcast,causal", [
@@ -469,8 +505,8 @@ def test_attention_output_at_16_byte_offset(oracle):
     assert float(buf[:4].abs().max()) == 0 and float(buf[-4:].abs().max()) == 0
 
 
-@pytest.mark.parametrize("d,L,Lk,path", [(32, 100, 200, PATH_UMMA), (32, 100, 200, PATH_SIMT), (8, 100, 200, PATH_AUTO),
-                                         (8, 5, 200, PATH_AUTO), (64, 40, 136, PATH_AUTO)])
+@pytest.mark.parametrize("d,L,Lk,path", [(32, 100, 200, PATH_UMMA), (32, 100, 200, PATH_SIMT), (8, 100, 200, PATH_SIMT),
+                                         (8, 100, 200, PATH_UMMA), (8, 5, 200, PATH_AUTO), (64, 40, 136, PATH_AUTO)])
 def test_attention_first_key_tile_masked(oracle, d, L, Lk, path):
     """A query row whose first 64 scores (the reference's first key tile) are all -inf: the reference's CPU kernel turns
     it into O = 0, LSE = -inf although later keys are visible (src/ops/FlashAttn.cpp:94-121); every kernel here does the
@@ -571,7 +607,8 @@ def test_backward_shapes_of_a_linear(oracle):
 @pytest.mark.parametrize("B,h,L,d,Lk,bias,path,tol,ltol", [
     (3, 8, 256, 32, None, True, PATH_UMMA, TOL_TF32, 2e-3),      # main-track heads on the tensor cores
     (2, 8, 51, 32, None, True, PATH_AUTO, TOL_FP32, 1e-5),       # dev size: 51 keys with a bias -> CUDA cores
-    (4, 8, 100, 8, None, True, PATH_AUTO, TOL_FP32, 1e-5),       # extra-MSA heads (d = 8): thread-per-row kernel
+    (4, 8, 100, 8, None, True, PATH_SIMT, TOL_FP32, 1e-5),       # extra-MSA heads (d = 8): thread-per-row kernel
+    (5, 8, 100, 8, None, True, PATH_AUTO, TOL_TF32, 2e-3),       # extra-MSA heads (d = 8): warp-level tensor-core kernel
     (5, 8, 1, 8, 64, False, PATH_AUTO, TOL_FP32, 1e-5),          # global column attention: one query, keys over lanes
     (2, 4, 70, 64, 44, True, PATH_AUTO, TOL_FP32, 1e-5),         # generic kernel
 ])
