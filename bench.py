@@ -395,6 +395,23 @@ def kernel_records(torch, dev, peaks, oracle):
                  "checked": bool(ok)})
     del Q, K, V, dO, O, LSE, grads
 
+    # ---- extra-MSA row attention (head dim 8, shared pair bias): the warp-level tensor-core kernel ----
+    B, h, L = 1024, 8, 256
+    Q, K, V = (rnd(B, h, L, 8) / 8 ** 0.5 for _ in range(3))
+    bias = rnd(h, L, L)
+    O = torch.empty((B, h, L, 8), device=dev)
+    f = lambda: ops.flash_attn_forward_cuda(Q, K, V, bias, scale=8 ** -0.5, bias_bcast=True, path=PATH_UMMA, out=O)
+    us = graph_time_us(torch, lambda: [f() for _ in range(2)], 2)
+    fl = 4.0 * B * h * L * L * 8
+    by = 16.0 * B * h * L * 8 + 4.0 * h * L * L + 4.0 * B * h * L
+    b0 = B // 3
+    rO, _ = oracle.flash_attn(host(Q[b0:b0 + 1]), host(K[b0:b0 + 1]), host(V[b0:b0 + 1]), host(bias), scale=8 ** -0.5, bias_bcast=True)
+    ok = rel(host(O[b0:b0 + 1]), rO) <= 1e-3
+    recs.append({"kernel": "attn_d8_mma_kernel", "op": "flash_attn_forward, fp32 operands (tf32 products, mma.sync)",
+                 "workload": f"extra-MSA row, shared pair bias: B'={B} h={h} L={L} d=8", "us": us, "tflops": fl / us / 1e6,
+                 "gbs": by / us / 1e3, "roofline": roofline(fl, by, us, peaks, 0.5), "checked": bool(ok)})
+    del Q, K, V, O
+
     # ---- pair-track contractions (configs[3]) ----
     D = 128
     for L in (128, 256, 384):

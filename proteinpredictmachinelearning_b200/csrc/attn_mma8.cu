@@ -49,26 +49,26 @@ constexpr int kPitch = 72;       // floats per staged bias row: 8-byte reads of 
 constexpr int kKV = kTile * 8;   // floats of one K (or V) tile
 
 // NW warps per CTA, GB batch elements per CTA: 32 NW / GB query rows per CTA
-template <int GB, int NW>
+template <int GB, int NW, int MT>
 struct Shape {
-    static constexpr int rows = 32 * NW / GB;
+    static constexpr int rows = 16 * MT * NW / GB;
     static constexpr int stage = rows * kPitch + 2 * GB * kKV;       // floats of one stage: bias rows, K tiles, V tiles
-    static constexpr int qtile = 32 * NW * 8;                        // floats of the Q rows of one row block
+    static constexpr int qtile = 16 * MT * NW * 8;                        // floats of the Q rows of one row block
     static constexpr int smem_bytes = (2 * stage + qtile) * static_cast<int>(sizeof(float));
 };
 
 // GB: batch elements per CTA (4: warp w works on batch element w % 4 and the 32-row group w / 4; 1: the warps take
 // 32-row groups of one batch element)
-template <int GB, int NW>
-__global__ void __launch_bounds__(32 * NW, GB == 4 ? 512 / (32 * NW) : 2)
+template <int GB, int NW, int MT>
+__global__ void __launch_bounds__(32 * NW, GB == 4 ? (MT == 2 ? 16 : 24) / NW : 2)
 attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                    const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
                    int B, int H, int L, int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft,
                    int bias_vec, int blocks_per_cta, const AttnLayout lay) {
     constexpr int NT = 32 * NW;
-    constexpr int kRows = Shape<GB, NW>::rows;                  // query rows per CTA
+    constexpr int kRows = Shape<GB, NW, MT>::rows;                  // query rows per CTA
     constexpr int kBias = kRows * kPitch;
-    constexpr int kStage = Shape<GB, NW>::stage;
+    constexpr int kStage = Shape<GB, NW, MT>::stage;
     constexpr float kLog2e = 1.4426950408889634f;
     extern __shared__ __align__(16) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -84,27 +84,27 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
     const float* Bh = bias ? bias + static_cast<size_t>(GB == 1 ? b0 : 0) * bias_batch_stride +
                                  static_cast<size_t>(hh) * L * static_cast<size_t>(Lk) : nullptr;
 
-    // rows of this thread in row block rb: index r = mi * 2 + hr -> row rb * kRows + rg * 32 + mi * 16 + hr * 8 + g
-    int jmax[4];
-    uint32_t qa[2][4];
-    float m[4], mfirst[4];
-    float o[2][4], lacc[2][4];                       // lacc: row sums of P (every column of the fragment holds the sum)
+    // rows of this thread in row block rb: index r = mi * 2 + hr -> row rb * kRows + rg * (16 * MT) + mi * 16 + hr * 8 + g
+    int jmax[2 * MT];
+    uint32_t qa[MT][4];
+    float m[2 * MT], mfirst[2 * MT];
+    float o[MT][4], lacc[MT][4];                       // lacc: row sums of P (every column of the fragment holds the sum)
     auto begin_block = [&](int rb) {
 #pragma unroll
-        for (int mi = 0; mi < 2; ++mi)
+        for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
             for (int hr = 0; hr < 2; ++hr) {
-                const int i = rb * kRows + rg * 32 + mi * 16 + hr * 8 + g;
+                const int i = rb * kRows + rg * (16 * MT) + mi * 16 + hr * 8 + g;
                 const bool ok = b_ok && i < L;
                 jmax[mi * 2 + hr] = ok ? (causal ? min(i + 1, Lk) : Lk) : 0;
-                const float* qp = smem + 2 * kStage + (bl * kRows + rg * 32 + mi * 16 + hr * 8 + g) * 8;     // staged, zero-filled
+                const float* qp = smem + 2 * kStage + (bl * kRows + rg * (16 * MT) + mi * 16 + hr * 8 + g) * 8;     // staged, zero-filled
                 qa[mi][hr] = tf32_bits(qp[t] * scale);                      // a0 / a1: channel t
                 qa[mi][hr + 2] = tf32_bits(qp[t + 4] * scale);              // a2 / a3: channel t + 4
             }
 #pragma unroll
-        for (int r = 0; r < 4; ++r) { m[r] = -CUDART_INF_F; mfirst[r] = -CUDART_INF_F; }
+        for (int r = 0; r < 2 * MT; ++r) { m[r] = -CUDART_INF_F; mfirst[r] = -CUDART_INF_F; }
 #pragma unroll
-        for (int mi = 0; mi < 2; ++mi)
+        for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
             for (int e = 0; e < 4; ++e) { o[mi][e] = 0.0f; lacc[mi][e] = 0.0f; }
     };
@@ -160,7 +160,7 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
         if (j0 == 0) {
             // the Q rows of the block: nobody reads the previous block's any more (they are in registers since its start)
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < MT; ++i) {
                 const int p = threadIdx.x + i * NT, idx = p >> 1, half = p & 1, bb = idx / kRows, r = idx % kRows;
                 const bool ok = b0 + bb < B && row0 + r < L;
                 cp_async16(smem + 2 * kStage + idx * 8 + half * 4,
@@ -172,10 +172,10 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
 
     auto end_block = [&](int rb) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < 2 * MT; ++r) {
             const int mi = r >> 1, hr = r & 1;
             float l = lacc[mi][hr * 2];
-            const int i = rb * kRows + rg * 32 + mi * 16 + hr * 8 + g;
+            const int i = rb * kRows + rg * (16 * MT) + mi * 16 + hr * 8 + g;
             if (!b_ok || i >= L) continue;
             if (ft > 0 && mfirst[r] == -CUDART_INF_F) l = 0.0f;     // the reference's first key tile is fully masked: O = 0, LSE = -inf
             float inv = 0.0f, lse = -CUDART_INF_F;
@@ -198,7 +198,7 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
         const bool last_tile = j0 + kTile >= keys_of(rb);
         const int rb_next = last_tile ? rb + 1 : rb, j0_next = last_tile ? 0 : j0 + kTile;
         const float* st = smem + buf * kStage;
-        const float* bs = st + (rg * 32 + g) * kPitch + 2 * t;
+        const float* bs = st + (rg * (16 * MT) + g) * kPitch + 2 * t;
         const float* ks = st + kBias + bl * kKV + lane;
         const float* vs = st + kBias + (GB + bl) * kKV + t * 8 + g;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -207,9 +207,9 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
         if (j0 == 0) begin_block(rb);
         if (rb_next < rb_end) stage_in(rb_next, j0_next, buf ^ 1);
 
-        float s[2][8][4];
+        float s[MT][8][4];
 #pragma unroll
-        for (int mi = 0; mi < 2; ++mi)
+        for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 if (Bh) {
@@ -224,22 +224,24 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
         for (int n = 0; n < 8; ++n) {
             const uint32_t kb0 = tf32_bits(ks[(n * 2) * 32]), kb1 = tf32_bits(ks[(n * 2 + 1) * 32]);
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi) mma_tf32(s[mi][n], qa[mi], kb0, kb1);
+            for (int mi = 0; mi < MT; ++mi) mma_tf32(s[mi][n], qa[mi], kb0, kb1);
         }
         // keys past the end (or past the diagonal) of a row; element e of an n tile: key j0 + n * 8 + 2 t + (e & 1)
-        const int jlow = min(min(jmax[0], jmax[1]), min(jmax[2], jmax[3]));
+        int jlow = jmax[0];
+#pragma unroll
+        for (int r = 1; r < 2 * MT; ++r) jlow = min(jlow, jmax[r]);
         if (j0 + kTile > jlow) {
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi)
+            for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
                 for (int n = 0; n < 8; ++n)
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
                         if (j0 + n * 8 + 2 * t + (e & 1) >= jmax[mi * 2 + (e >> 1)]) s[mi][n][e] = -CUDART_INF_F;
         }
-        float alpha[4], nml2[4];
+        float alpha[2 * MT], nml2[2 * MT];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < 2 * MT; ++r) {
             const int mi = r >> 1, e0 = (r & 1) * 2;
             float mt = -CUDART_INF_F;
 #pragma unroll
@@ -268,14 +270,14 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
             m[r] = m_new;
         }
 #pragma unroll
-        for (int mi = 0; mi < 2; ++mi)
+        for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
             for (int n = 0; n < 8; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     s[mi][n][e] = ex2_approx(fmaf(s[mi][n][e], kLog2e, nml2[mi * 2 + (e >> 1)]));
 #pragma unroll
-        for (int mi = 0; mi < 2; ++mi) {
+        for (int mi = 0; mi < MT; ++mi) {
             o[mi][0] *= alpha[mi * 2]; o[mi][1] *= alpha[mi * 2];
             o[mi][2] *= alpha[mi * 2 + 1]; o[mi][3] *= alpha[mi * 2 + 1];
             lacc[mi][0] *= alpha[mi * 2]; lacc[mi][2] *= alpha[mi * 2 + 1];
@@ -284,7 +286,7 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
         for (int n = 0; n < 8; ++n) {
             const uint32_t vb0 = tf32_bits(vs[(n * 2) * 32]), vb1 = tf32_bits(vs[(n * 2 + 1) * 32]);
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi) {
+            for (int mi = 0; mi < MT; ++mi) {
                 // A fragment of P: (row g, key 2t), (row g + 8, key 2t), (row g, key 2t + 1), (row g + 8, key 2t + 1).  The
                 // tensor core drops the low 13 bits of P; the row sum is taken from the same operand (a product with
                 // ones), so numerator and denominator see the same P
@@ -302,29 +304,29 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
     }
 }
 
-template <int GB, int NW>
+template <int GB, int NW, int MT>
 int launch_shape(const float* Q, const float* K, const float* V, const float* bias, float* O, float* LSE, int B, int H, int L,
                  int Lk, int causal, float scale, float eps, long long bias_batch_stride, int ft, int bias_vec, const AttnLayout& lay,
                  cudaStream_t st) {
-    using S = Shape<GB, NW>;
+    using S = Shape<GB, NW, MT>;
     static bool configured[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ST_LAUNCH;
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(attn_d8_mma_kernel<GB, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(attn_d8_mma_kernel<GB, NW, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::smem_bytes) != cudaSuccess)
             return ST_LAUNCH;
         configured[dev] = true;
     }
     // a CTA takes several consecutive row blocks (its copies run ahead across them) as long as the grid keeps about eight
     // waves of CTAs
     const int n_blocks = (L + S::rows - 1) / S::rows, groups = (B + GB - 1) / GB;
-    const long long ctas_wanted = 8LL * num_sms() * (GB == 4 ? 512 / (32 * NW) : 2);
+    const long long ctas_wanted = 8LL * num_sms() * (GB == 4 ? (MT == 2 ? 16 : 24) / NW : 2);
     long long split = (ctas_wanted + static_cast<long long>(H) * groups - 1) / (static_cast<long long>(H) * groups);
     if (split > n_blocks) split = n_blocks;
     if (split < 1) split = 1;
     const int per_cta = static_cast<int>((n_blocks + split - 1) / split);
     dim3 grid((n_blocks + per_cta - 1) / per_cta, H, groups);
-    attn_d8_mma_kernel<GB, NW><<<grid, 32 * NW, S::smem_bytes, st>>>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps,
+    attn_d8_mma_kernel<GB, NW, MT><<<grid, 32 * NW, S::smem_bytes, st>>>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps,
                                                                     bias_batch_stride, ft, bias_vec, per_cta, lay);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
@@ -344,11 +346,11 @@ int launch_attn_d8_mma(const float* Q, const float* K, const float* V, const flo
     if (shared && B >= 4) {
         if ((B + 3) / 4 > 65535) return ST_UNSUPPORTED_PATH;
         if (L > 32)
-            return launch_shape<4, 8>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
-        return launch_shape<4, 4>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
+            return launch_shape<4, 8, 2>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
+        return launch_shape<4, 4, 2>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
     }
     if (B > 65535) return ST_UNSUPPORTED_PATH;
-    return launch_shape<1, 4>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
+    return launch_shape<1, 4, 2>(Q, K, V, bias, O, LSE, B, H, L, Lk, causal, scale, eps, bias_batch_stride, ft, bias_vec, lay, st);
 }
 
 }  // namespace ppml_b200
