@@ -20,6 +20,8 @@ Beside the headline the line carries
                    (min(tensor peak, intensity x HBM bandwidth), peaks from MEASURED_PEAKS.json);
   `sharded_block`  the hot-path op sequence of one main IterBlock at full size cut over the N ranks (strong scaling,
                    ms per block, per-class split, exchanged bytes, every op's shard checked against the unsharded op);
+  `sharded_extra_block`  the same for one extra-MSA FullBlock (1024 MSA rows of 64 channels, 8 heads x 8, global column
+                   attention);
   `cpu_baseline`   the host-core figures: the Q8 arithmetic restated on the CPU (the reference has no CPU Q8 kernel,
                    include/ppml/QuantBlocks.h:56) and, where the reference's own CPU kernels were compiled
                    (oracle/_ref), those kernels on bounded samples.
@@ -688,10 +690,11 @@ def run_ours(args):
         from checkers import Oracle
         kernels = kernel_records(torch, dev, peaks, Oracle())
     barrier()
-    block = None
+    block = extra_block = None
     if not args.no_block:
         from proteinpredictmachinelearning_b200 import block_bench
         block = block_bench.measure(steps=max(5, min(args.steps, 20)), warmup=3)
+        extra_block = block_bench.measure(steps=max(5, min(args.steps, 20)), warmup=3, kind="extra")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -723,6 +726,7 @@ def run_ours(args):
         line["checked_kernels"] = all(k.get("checked", True) for k in kernels)
     if block is not None:
         line["sharded_block"] = block
+        line["sharded_extra_block"] = extra_block
     # CPU baseline on rank 0, N = 1 only
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_record()
@@ -795,12 +799,13 @@ def main():
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs); B,h,L with --kernel attn")
     ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn", "attn_bf16"],
                     help="profiling runs: one launch kind on one workload, launched directly")
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "block"],
-                    help="block: only the sharded IterBlock record (proteinpredictmachinelearning_b200/block_bench.py)")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "block", "extra_block"],
+                    help="block / extra_block: only the sharded IterBlock / extra-MSA FullBlock record "
+                         "(proteinpredictmachinelearning_b200/block_bench.py)")
     args = ap.parse_args()
-    if args.workload == "block":
+    if args.workload in ("block", "extra_block"):
         from proteinpredictmachinelearning_b200 import block_bench
-        return block_bench.run(args.gpus, args.steps, args.warmup)
+        return block_bench.run(args.gpus, args.steps, args.warmup, kind="main" if args.workload == "block" else "extra")
     if args.kernel != "q8":
         return single_kernel(args)
     if args.impl == "reference":

@@ -39,6 +39,14 @@ Parity: the same block code runs a second time on the rank's own GPU with G = 1 
 weights), and every op's sharded result must equal the matching contiguous part of the unsharded result bit for bit
 (token rows, batches and slabs are independent and go through the same tiles in the same order).
 
+Extra-MSA block (`kind="extra"`, src/model/PPML.cpp:1526-1590, layer shapes :2243-2273): the same pair track, and an MSA
+track on the 1024-row extra MSA with 64 channels and 8 heads x 8: row attention with the pair bias (projections Q8, the
+head-dim-8 attention kernel), global column attention (src/modules/Attention.cpp:582-641: fp32 projections 64 -> 64 of
+every token, one query per chunk of N flat positions -- the mean over the MSA rows, elementwise glue, here a common
+input -- over the chunk's 1024 keys, no (n, l) transpose; the mean's partial sums [L, 64] per rank are gathered where the
+reference would all-reduce them), feed-forward 64 -> 256 -> 64, left / right 64 -> 16 and the outer-product-mean over
+1024 rows.
+
 Timing: the block is timed launched op by op from the host ("eager_ms", with a per-class split from events around
 every op), and with the compute segments between the exchanges captured as CUDA graphs and replayed, the collectives
 still launched from the host ("ms_per_block").  Collectives are never captured.  Times are CUDA-event times, maximum
@@ -49,15 +57,17 @@ import json
 import os
 
 L_RES, N_MSA, D_MSA, D_PAIR, HEADS, HEAD_DIM, OPM_D, TRI_D = 256, 256, 256, 128, 8, 32, 16, 128
+# MSA track of the two block kinds: rows, channels, head dim
+KINDS = {"main": (N_MSA, D_MSA, HEAD_DIM), "extra": (1024, 64, 8)}
 
 
 class Block:
     """The op sequence for one rank of a G-way partition (G = 1: the unsharded block).  Inputs and weights are shared
     between instances; every instance owns its outputs."""
 
-    SITES = {"mr_bias": 0, "col_t": 1, "right": 2, "pr_bias": 3, "row_t": 4, "pc_bias": 5}
+    SITES = {"mr_bias": 0, "col_t": 1, "qsum": 1, "right": 2, "pr_bias": 3, "row_t": 4, "pc_bias": 5}
 
-    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None, fused=True):
+    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None, fused=True, kind="main"):
         self.torch, self.dist, self.ops = torch, dist, ops
         self.fused = fused
         self.inp, self.weights, self.G, self.rank, self.dev = inputs, weights, G, rank, dev
@@ -68,7 +78,9 @@ class Block:
         self.timers = {}
         self.capturing = False
         self.ctx = {}
-        L, N = L_RES, N_MSA
+        self.kind = kind
+        self.N, self.D, self.hd_msa = KINDS[kind]
+        L, N = L_RES, self.N
         self.tok_msa, self.tok_pair = N * L // G, L * L // G
 
     # ---- helpers -----------------------------------------------------------------------------------------------
@@ -153,11 +165,11 @@ class Block:
         out.view(l_loc, G, n_loc, C).copy_(recv.permute(2, 0, 1, 3))         # [l][from rank][n][c]
         return out.view(l_loc * G * n_loc, C)
 
-    def attention(self, src, batch, bias, scale, tag):
+    def attention(self, src, batch, bias, scale, tag, head_dim=HEAD_DIM):
         """Projections, fused attention over this rank's batches (with the gathered pair bias, if any), output Linear."""
         d_in = src.shape[1]
+        hd = HEADS * head_dim
         if self.fused:
-            hd = HEADS * HEAD_DIM
             with self.timed("linear_q8"):
                 qkvg = self.linear(src, 4 * hd, True, tag + "qkvg")
             seq = qkvg.shape[0] // batch
@@ -171,19 +183,41 @@ class Block:
             with self.timed("linear_q8"):
                 return self.linear(o.view(-1, hd), d_in, True, tag + "o")
         with self.timed("linear_q8"):
-            q = self.linear(src, HEADS * HEAD_DIM, True, tag + "q")
-            k = self.linear(src, HEADS * HEAD_DIM, True, tag + "k")
-            v = self.linear(src, HEADS * HEAD_DIM, True, tag + "v")
-            self.linear(src, HEADS * HEAD_DIM, True, tag + "g")
+            q = self.linear(src, hd, True, tag + "q")
+            k = self.linear(src, hd, True, tag + "k")
+            v = self.linear(src, hd, True, tag + "v")
+            self.linear(src, hd, True, tag + "g")
         seq = q.shape[0] // batch
-        shape = (batch, HEADS, seq, HEAD_DIM)                                  # flat reinterpretation, as the reference's views
+        shape = (batch, HEADS, seq, head_dim)                                  # flat reinterpretation, as the reference's views
         o = self.buf("att_" + tag, shape)
         with self.timed("attention"):
             self.ops.flash_attn_forward_cuda(q.view(shape), k.view(shape), v.view(shape), bias, scale=scale,
                                              bias_bcast=bias is not None, out=o)
         self.out["att_" + tag] = o
         with self.timed("linear_q8"):
-            return self.linear(o.view(-1, HEADS * HEAD_DIM), d_in, True, tag + "o")
+            return self.linear(o.view(-1, hd), d_in, True, tag + "o")
+
+    def global_column_attention(self, x):
+        """Extra-MSA block: projections of every token (fp32 Linears: not on the reference's Q8 list), one query per chunk
+        of N flat positions over the chunk's N keys, output Linear.  The query (mean over the MSA rows of the Q
+        projection) and the broadcast of the result over the rows times sigmoid(gate) are elementwise glue: common inputs."""
+        N, hd = self.N, HEADS * self.hd_msa
+        chunks = x.shape[0] // N
+        with self.timed("linear_tf32"):
+            if self.fused:
+                t = self.linear(x, 4 * hd, False, "gcqkvg").view(chunks, N, 4 * hd)
+                k, v = t[:, :, hd:2 * hd], t[:, :, 2 * hd:3 * hd]
+            else:
+                self.linear(x, hd, False, "gcq")
+                k, v = self.linear(x, hd, False, "gck").view(chunks, N, hd), self.linear(x, hd, False, "gcv").view(chunks, N, hd)
+                self.linear(x, hd, False, "gcg")
+        q = self.rows("x_qmean").view(chunks, 1, hd)
+        o = self.buf("att_gc", (chunks, 1, hd))
+        with self.timed("attention"):
+            self.ops.flash_attn_tokens(q, k, v, HEADS, scale=1.0 / self.hd_msa ** 0.5, out=o)
+        self.out["att_gc"] = o
+        with self.timed("linear_tf32"):
+            return self.linear(self.rows("x_gc"), self.D, False, "gco")
 
     def pair_bias(self, tag):
         with self.timed("linear_q8"):
@@ -202,20 +236,24 @@ class Block:
 
     def seg_b(self):
         x = self.rows("x_msa")
-        self.attention(x, N_MSA // self.G, self.ctx["mr_bias"], 1.0 / 32 ** 0.5, "mr")
-        self.ctx["col"] = self.attention(x, N_MSA // self.G, None, 1.0 / 32 ** 0.5, "mc")
+        self.attention(x, self.N // self.G, self.ctx["mr_bias"], 1.0 / self.hd_msa ** 0.5, "mr", self.hd_msa)
+        if self.kind == "main":
+            self.ctx["col"] = self.attention(x, self.N // self.G, None, 1.0 / 32 ** 0.5, "mc")
+        else:
+            self.global_column_attention(x)
+            self.ctx["qsum"] = self.rows("x_qsum")
 
     def seg_c(self):
         x = self.rows("x_msa")
         with self.timed("linear_tf32"):
-            self.linear(x, 4 * D_MSA, False, "ff1")
-            self.linear(self.rows("x_ff"), D_MSA, False, "ff2")
+            self.linear(x, 4 * self.D, False, "ff1")
+            self.linear(self.rows("x_ff"), self.D, False, "ff2")
         with self.timed("linear_q8"):
             self.ctx["left"] = self.linear(x, OPM_D, True, "ol")
             self.ctx["right"] = self.linear(x, OPM_D, True, "or")
 
     def seg_d(self):
-        G, L, N = self.G, L_RES, N_MSA
+        G, L, N = self.G, L_RES, self.N
         opm = self.buf("opm", (OPM_D // G * OPM_D, L, L, 1))
         with self.timed("outer_prod_mean"):
             self.ops.outer_prod_mean_slabs_cuda(self.ctx["left"].view(OPM_D // G, L, N, 1), self.ctx["right_all"].view(OPM_D, L, N, 1), out=opm)
@@ -265,6 +303,10 @@ class Block:
             self.ctx["right_all"] = self.gather_rows(self.ctx["right"], "right")          # [N*L, 16] flat = [16][L][N]
             self.out["right_all"] = self.ctx["right_all"]
 
+    def ex_qsum(self):
+        with self.timed("exchange"):
+            self.out["qsum_all"] = self.gather_rows(self.ctx["qsum"], "qsum")               # [G * L, 64] partial sums of the query mean
+
     def ex_transpose(self, src, n_total, dst):
         def step():
             with self.timed("exchange"):
@@ -275,7 +317,8 @@ class Block:
     def plan(self):
         segments = [self.seg_a, self.seg_b, self.seg_c, self.seg_d, self.seg_e, self.seg_f, self.seg_g]
         exchanges = [self.ex_bias("mr_b", "mr_bias"),                # pair bias of MSA row attention
-                     self.ex_transpose("col", N_MSA, "col_t"),       # (n, l) transpose closing column attention
+                     self.ex_transpose("col", self.N, "col_t") if self.kind == "main"       # (n, l) transpose closing column attention
+                     else self.ex_qsum,                                                  # partial sums of the global query
                      self.ex_right,
                      self.ex_bias("pr_b", "pr_bias"),
                      self.ex_transpose("row", L_RES, "row_t"),       # transpose closing pair row attention
@@ -294,28 +337,40 @@ class Block:
 
 
 # per rank and block: bytes received by each collective at G ranks (fp32)
-def exchange_bytes(G):
+def exchange_bytes(G, kind="main"):
     if G == 1:
         return {}
     frac = (G - 1) / G
-    return {"all_gather pair bias [L*L, 8] (x3)": int(L_RES * L_RES * HEADS * 4 * frac),
-            "all_gather outer-product-mean right [N*L, 16]": int(N_MSA * L_RES * OPM_D * 4 * frac),
-            "all_to_all MSA (n, l) transpose [N*L, 256] / G": int(N_MSA * L_RES * D_MSA * 4 / G * frac),
-            "all_to_all pair (row, col) transpose [L*L, 128] / G": int(L_RES * L_RES * D_PAIR * 4 / G * frac)}
+    N, D, _ = KINDS[kind]
+    out = {"all_gather pair bias [L*L, 8] (x3)": int(L_RES * L_RES * HEADS * 4 * frac),
+           "all_gather outer-product-mean right [N*L, 16]": int(N * L_RES * OPM_D * 4 * frac),
+           "all_to_all pair (row, col) transpose [L*L, 128] / G": int(L_RES * L_RES * D_PAIR * 4 / G * frac)}
+    if kind == "main":
+        out["all_to_all MSA (n, l) transpose [N*L, 256] / G"] = int(N * L_RES * D * 4 / G * frac)
+    else:
+        out["all_gather partial sums of the global query [L, 64] per rank"] = int(L_RES * D * 4 * (G - 1))
+    return out
 
 
-def make_inputs_and_weights(torch, ops, dev):
+def make_inputs_and_weights(torch, ops, dev, kind="main", G=1):
     """Inputs and weights from one seed, identical on every rank."""
     g = torch.Generator(device=dev).manual_seed(5)
     rnd = lambda *shape: torch.randn(shape, device=dev, generator=g)
-    L, N = L_RES, N_MSA
-    inputs = {"x_msa": rnd(N * L, D_MSA), "x_pair": rnd(L * L, D_PAIR), "x_ff": rnd(N * L, 4 * D_MSA),
+    N, D_M, hd_m = KINDS[kind]
+    L = L_RES
+    inputs = {"x_msa": rnd(N * L, D_M), "x_pair": rnd(L * L, D_PAIR), "x_ff": rnd(N * L, 4 * D_M),
               "x_pff": rnd(L * L, 2 * D_PAIR), "x_opm": rnd(L * L, OPM_D * OPM_D)}
+    attn = [("mr", D_M, hd_m), ("pr", D_PAIR, HEAD_DIM), ("pc", D_PAIR, HEAD_DIM)] + ([("mc", D_M, hd_m)] if kind == "main" else [])
     spec = []
-    for tag, d_in in (("mr", D_MSA), ("mc", D_MSA), ("pr", D_PAIR), ("pc", D_PAIR)):
-        spec += [(tag + t, d_in, HEADS * HEAD_DIM, True) for t in "qkvg"] + [(tag + "o", HEADS * HEAD_DIM, d_in, True)]
+    for tag, d_in, hd in attn:
+        spec += [(tag + t, d_in, HEADS * hd, True) for t in "qkvg"] + [(tag + "o", HEADS * hd, d_in, True)]
+    if kind == "extra":
+        # global column attention: the query per chunk of N flat positions (their number is L), the gated result per token,
+        # and every rank's partial sums of the query mean
+        inputs.update({"x_qmean": rnd(L, HEADS * hd_m) / hd_m ** 0.5, "x_gc": rnd(N * L, HEADS * hd_m), "x_qsum": rnd(G * L, D_M)})
+        spec += [("gc" + t, D_M, HEADS * hd_m, False) for t in "qkvg"] + [("gco", HEADS * hd_m, D_M, False)]
     spec += [(tag + "b", D_PAIR, HEADS, True) for tag in ("mr", "pr", "pc")]
-    spec += [("ff1", D_MSA, 4 * D_MSA, False), ("ff2", 4 * D_MSA, D_MSA, False), ("ol", D_MSA, OPM_D, True), ("or", D_MSA, OPM_D, True),
+    spec += [("ff1", D_M, 4 * D_M, False), ("ff2", 4 * D_M, D_M, False), ("ol", D_M, OPM_D, True), ("or", D_M, OPM_D, True),
              ("oo", OPM_D * OPM_D, D_PAIR, True), ("pf1", D_PAIR, 2 * D_PAIR, False), ("pf2", 2 * D_PAIR, D_PAIR, False)]
     for d in ("out", "in"):
         spec += [(t + d, D_PAIR, TRI_D, False) for t in ("tl", "tr", "tlg", "trg", "tg")] + [("to" + d, TRI_D, D_PAIR, False)]
@@ -327,9 +382,11 @@ def make_inputs_and_weights(torch, ops, dev):
         weights[(tag, k, n_out, q8)] = (ops.quantize_q8_0r(w) if q8 else w, b)
     # concatenated weights of the fused form
     cat = lambda tags: (torch.cat([raw[t][0] for t in tags], 0).contiguous(), torch.cat([raw[t][1] for t in tags], 0).contiguous())
-    for tag, d_in in (("mr", D_MSA), ("mc", D_MSA), ("pr", D_PAIR), ("pc", D_PAIR)):
+    for tag, d_in, hd in attn:
         w, b = cat([tag + t for t in "qkvg"])
-        weights[(tag + "qkvg", d_in, 4 * HEADS * HEAD_DIM, True)] = (ops.quantize_q8_0r(w), b)
+        weights[(tag + "qkvg", d_in, 4 * HEADS * hd, True)] = (ops.quantize_q8_0r(w), b)
+    if kind == "extra":
+        weights[("gcqkvg", D_M, 4 * HEADS * hd_m, False)] = cat(["gc" + t for t in "qkvg"])
     for d in ("out", "in"):
         weights[("tgates" + d, D_PAIR, 3 * TRI_D, False)] = cat([t + d for t in ("tlg", "trg", "tg")])
     return inputs, weights
@@ -340,7 +397,7 @@ def verify(torch, sharded, full, G, rank):
     bad, n = [], 0
     for name, got in sharded.out.items():
         ref = full.out[name]
-        if name.startswith("bias_") or name == "right_all":
+        if name.startswith("bias_") or name in ("right_all", "qsum_all"):
             part = ref                                           # gathered: the whole tensor on every rank
         else:
             flat = ref.reshape(-1)
@@ -352,7 +409,7 @@ def verify(torch, sharded, full, G, rank):
     return n, bad
 
 
-def measure(steps=5, warmup=3, use_graph=True, check=True):
+def measure(steps=5, warmup=3, use_graph=True, check=True, kind="main"):
     """Runs the block on this process's rank (torch.distributed already initialised when WORLD_SIZE > 1) and returns the
     record (identical on every rank as far as the timing goes; rank 0's split)."""
     import torch
@@ -368,11 +425,11 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     G = world
-    L, N = L_RES, N_MSA
+    L, N = L_RES, KINDS[kind][0]
     for total in (N * L, L * L, N, L, OPM_D, TRI_D):
         if total % G:
             return {"unavailable": f"{G} ranks do not divide the block's partitions"}
-    inputs, weights = make_inputs_and_weights(torch, ops, dev)
+    inputs, weights = make_inputs_and_weights(torch, ops, dev, kind, G)
     # exchanges: single kernels over peer memory (CUDA IPC) by default, NCCL collectives launched from the host when
     # that cannot be set up or PPML_B200_EXCHANGE=nccl asks for them
     peers, exchange_mode = None, "none (one rank)"
@@ -392,7 +449,7 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
             else:
                 exchange_mode = "one kernel per exchange: stores into the peers' buffers between two flag rounds"
     fused = os.environ.get("PPML_B200_BLOCK_FUSED", "1") != "0"
-    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev, peers=peers, fused=fused)
+    blk = Block(torch, dist, ops, inputs, weights, G, rank, dev, peers=peers, fused=fused, kind=kind)
 
     def barrier():
         if G > 1:
@@ -409,7 +466,7 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
     n_checked, bad = 0, []
     if check:
         if G > 1:
-            full = Block(torch, dist, ops, inputs, weights, 1, 0, dev, fused=fused)
+            full = Block(torch, dist, ops, inputs, weights, 1, 0, dev, fused=fused, kind=kind)
             full.run()
             torch.cuda.synchronize()
             n_checked, bad = verify(torch, blk, full, G, rank)
@@ -501,29 +558,37 @@ def measure(steps=5, warmup=3, use_graph=True, check=True):
             dist.barrier()
         blk.bufs.clear()
         peers.close()
-    return {"metric": "main IterBlock hot-path ops, ms per block", "ms_per_block": float(ms[0].item()), "unit": "ms",
-            "ms_per_32_blocks": float(ms[0].item()) * 32, "eager_ms": float(ms[1].item()), "n_gpus": G, "steps": steps,
+    n_blocks = 32 if kind == "main" else 4               # blocks of this kind in the full-size model
+    if kind == "main":
+        workload = ("one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads; "
+                    + ("14 Q8 Linears (Q, K, V and gate of an attention call as one), 14 fp32 Linears (the gates of a triangle "
+                       "multiplication as one), 4 attention calls on token-major operands with the gate applied in the store, "
+                       if fused else "26 Q8 Linears, 18 fp32 Linears, 4 attention calls, ")
+                    + "2 tri_mul, 1 outer-product-mean")
+    else:
+        workload = ("one extra-MSA FullBlock: L=256, extra MSA depth 1024, d_msa 64 with 8x8 heads (row attention with pair "
+                    "bias on the head-dim-8 kernel, global column attention: one query over 1024 keys per chunk), d_pair 128 "
+                    "with 8x32 heads; " + ("fused projections, " if fused else "") + "2 tri_mul, 1 outer-product-mean over 1024 rows")
+    return {"metric": ("main IterBlock" if kind == "main" else "extra-MSA FullBlock") + " hot-path ops, ms per block",
+            "ms_per_block": float(ms[0].item()), "unit": "ms",
+            f"ms_per_{n_blocks}_blocks": float(ms[0].item()) * n_blocks, "eager_ms": float(ms[1].item()), "n_gpus": G, "steps": steps,
             "scaling": "strong", "higher_is_better": False, "dtype": "q8 + tf32, fp32 accumulate", "data": "synthetic, seed 5",
             "launch": ("cuda graphs" + (" (" + graph_note + ")" if graph_note else " for the compute segments, collectives from the host"))
                       if graph_ms is not None else "eager",
             "exchange": exchange_mode,
-            "workload": "one main IterBlock: L=256, MSA depth 256, d_msa 256, d_pair 128, 8x32 heads; "
-                        + ("14 Q8 Linears (Q, K, V and gate of an attention call as one), 14 fp32 Linears (the gates of a triangle "
-                           "multiplication as one), 4 attention calls on token-major operands with the gate applied in the store, "
-                           if fused else "26 Q8 Linears, 18 fp32 Linears, 4 attention calls, ")
-                        + "2 tri_mul, 1 outer-product-mean",
+            "workload": workload,
             "fused_projections": fused,
             "split_ms_rank0": {k: round(v, 4) for k, v in sorted(split.items())},
             "exchange_share": round(split.get("exchange", 0.0) / total_split, 4),
-            "exchange_bytes_per_rank": exchange_bytes(G),
+            "exchange_bytes_per_rank": exchange_bytes(G, kind),
             "parity": {"ops_checked": n_checked, "mismatching_over_ranks": n_bad_all, "mismatching_here": bad,
                        "against": "the unsharded block on the same GPU, same inputs and weights, bit for bit" if G > 1
                                   else "a second run of the same block (one rank: sharded and unsharded coincide), bit for bit"}}
 
 
-def run(gpus, steps, warmup, use_graph=True):
+def run(gpus, steps, warmup, use_graph=True, kind="main"):
     import torch.distributed as dist
-    rec = measure(steps, warmup, use_graph)
+    rec = measure(steps, warmup, use_graph, kind=kind)
     if int(os.environ.get("RANK", "0")) == 0:
         rec["value"] = rec.get("ms_per_block")
         print(json.dumps(rec), flush=True)
@@ -538,8 +603,9 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only")
+    ap.add_argument("--kind", choices=sorted(KINDS), default="main", help="main IterBlock or extra-MSA FullBlock")
     a = ap.parse_args()
-    run(a.gpus, a.steps, a.warmup, use_graph=not a.no_graph)
+    run(a.gpus, a.steps, a.warmup, use_graph=not a.no_graph, kind=a.kind)
 
 
 if __name__ == "__main__":
