@@ -103,6 +103,14 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
             }
 #pragma unroll
         for (int r = 0; r < 2 * MT; ++r) { m[r] = -CUDART_INF_F; mfirst[r] = -CUDART_INF_F; }
+        if (lay.gate && t == 0 && b_ok) {
+            // the block's gate rows are read when it ends: bring them into L2 now
+#pragma unroll
+            for (int r = 0; r < 2 * MT; ++r) {
+                const int i = rb * kRows + rg * (16 * MT) + (r >> 1) * 16 + (r & 1) * 8 + g;
+                if (i < L) asm volatile("prefetch.global.L2 [%0];" ::"l"(lay.gate + b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l));
+            }
+        }
 #pragma unroll
         for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
@@ -171,6 +179,18 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
     };
 
     auto end_block = [&](int rb) {
+        // the gate values first, all loads in flight together (the stores below could alias them for the compiler)
+        float gv[2 * MT][2];
+#pragma unroll
+        for (int r = 0; r < 2 * MT; ++r) {
+            const int i = rb * kRows + rg * (16 * MT) + (r >> 1) * 16 + (r & 1) * 8 + g;
+            gv[r][0] = gv[r][1] = 0.0f;
+            if (lay.gate && b_ok && i < L) {
+                const float2* gp = reinterpret_cast<const float2*>(lay.gate + b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l + 2 * t);
+                if ((reinterpret_cast<uintptr_t>(gp) & 7) == 0) { const float2 v = __ldg(gp); gv[r][0] = v.x; gv[r][1] = v.y; }
+                else { gv[r][0] = __ldg(reinterpret_cast<const float*>(gp)); gv[r][1] = __ldg(reinterpret_cast<const float*>(gp) + 1); }
+            }
+        }
 #pragma unroll
         for (int r = 0; r < 2 * MT; ++r) {
             const int mi = r >> 1, hr = r & 1;
@@ -182,8 +202,12 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
             if (l > 0.0f) { inv = 1.0f / (l + eps); lse = m[r] + logf(l + eps); }
             float v0 = o[mi][hr * 2] * inv, v1 = o[mi][hr * 2 + 1] * inv;
             if (lay.gate) {
-                const float* gp = lay.gate + b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l + 2 * t;
-                v0 *= act_scalar(lay.act, gp[0]); v1 *= act_scalar(lay.act, gp[1]);
+                if (lay.act == 1) {                                 // sigmoid: 1 / (1 + 2^(-x log2 e)) on the fast units
+                    v0 *= __frcp_rn(1.0f + ex2_approx(-gv[r][0] * kLog2e));
+                    v1 *= __frcp_rn(1.0f + ex2_approx(-gv[r][1] * kLog2e));
+                } else {
+                    v0 *= act_scalar(lay.act, gv[r][0]); v1 *= act_scalar(lay.act, gv[r][1]);
+                }
             }
             float* op = O + b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l + 2 * t;
             if ((reinterpret_cast<uintptr_t>(op) & 7) == 0) *reinterpret_cast<float2*>(op) = make_float2(v0, v1);
