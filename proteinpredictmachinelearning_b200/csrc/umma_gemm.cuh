@@ -278,10 +278,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!mbar_wait(tfull_bar(acc), acc_ph, cta_abort, p.err, 0x301)) { ok = false; break; }
             tc_fence_after();
             const int row0 = trow0 + q * 32;
+            // blocked store: (slab, position) of the warp's first row and of every chunk's first column, one division each;
+            // the elements step from there (an integer division per stored element costs more than the store)
+            int opm_d1 = 0, opm_i = 0;
+            if constexpr (!kRowMajor) { opm_d1 = row0 / p.opm_L; opm_i = row0 - opm_d1 * p.opm_L; }
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int cbase = col0 + c * 32;
                 if (cbase >= p.N) break;                 // uniform across the warp
+                int opm_d2 = 0, opm_j = 0;
+                if constexpr (!kRowMajor) { opm_d2 = cbase / p.opm_L; opm_j = cbase - opm_d2 * p.opm_L; }
                 uint32_t v[32];
                 tmem_ld32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                 tmem_ld_wait();
@@ -322,6 +328,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     __syncwarp();
                     const int cc = lane & 7;             // 16-byte chunk inside the 128-byte row segment
                     const int col = cbase + cc * 4;
+                    // blocked store: the address of this lane's first row, stepped by four rows per round
+                    float* optr = nullptr;
+                    int o_ii = 0;
+                    if constexpr (!kRowMajor) {
+                        const int L = p.opm_L, D = p.opm_D;
+                        int d1 = opm_d1, d2 = opm_d2, jj = opm_j + cc * 4;
+                        o_ii = opm_i + (lane >> 3);
+                        while (o_ii >= L) { o_ii -= L; ++d1; }
+                        while (jj >= L) { jj -= L; ++d2; }
+                        optr = p.C + ((static_cast<long long>(d1) * D + d2) * L + o_ii) * L + jj;
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int rr = (lane >> 3) + 4 * i;
@@ -338,11 +355,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 *reinterpret_cast<float4*>(p.C + static_cast<long long>(b) * p.c_batch +
                                                            static_cast<long long>(row) * p.ldc + col) = val;
                             } else {
-                                const int L = p.opm_L, D = p.opm_D;
-                                const int d1 = row / L, ii = row - d1 * L;
-                                const int d2 = col / L, jj = col - d2 * L;
-                                *reinterpret_cast<float4*>(p.C + ((static_cast<long long>(d1) * D + d2) * L + ii) * L + jj) = val;
+                                *reinterpret_cast<float4*>(optr) = val;
                             }
+                        }
+                        if constexpr (!kRowMajor) {          // four rows on: L is a multiple of 4 here, so at most one slab boundary
+                            const int L = p.opm_L;
+                            optr += 4 * L; o_ii += 4;
+                            if (o_ii >= L) { o_ii -= L; optr += static_cast<long long>(p.opm_D - 1) * L * L; }
                         }
                     }
                     __syncwarp();
@@ -358,8 +377,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                     p.C[off] = (kFused && p.gate != nullptr) ? act_apply(p.act, f[j]) * p.gate[off] : f[j];
                                 } else {
                                     const int L = p.opm_L, D = p.opm_D;
-                                    const int d1 = row / L, ii = row - d1 * L;
-                                    const int d2 = col / L, jj = col - d2 * L;
+                                    int d1 = opm_d1, ii = opm_i + lane, d2 = opm_d2, jj = opm_j + j;
+                                    while (ii >= L) { ii -= L; ++d1; }
+                                    while (jj >= L) { jj -= L; ++d2; }
                                     p.C[((static_cast<long long>(d1) * D + d2) * L + ii) * L + jj] = f[j];
                                 }
                             }
