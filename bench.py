@@ -750,14 +750,15 @@ def single_kernel(args):
     from proteinpredictmachinelearning_b200 import PATH_UMMA, TF32_TMA, ops
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(3)
-    if args.kernel in ("attn", "attn_bf16"):
+    if args.kernel in ("attn", "attn_bf16", "attn8"):
         B, h, L = (int(v) for v in args.only.split(",")) if args.only else (64, 8, 256)
-        Q, K, V = (torch.randn(B, h, L, 32, device=dev, generator=g) / 32 ** 0.5 for _ in range(3))
+        d = 8 if args.kernel == "attn8" else 32                  # attn8: the extra-MSA head dim (warp-level tensor-core kernel)
+        Q, K, V = (torch.randn(B, h, L, d, device=dev, generator=g) / d ** 0.5 for _ in range(3))
         bias = torch.randn(h, L, L, device=dev, generator=g)
         if args.kernel == "attn_bf16":
             Q, K, V = Q.bfloat16(), K.bfloat16(), V.bfloat16()
-        f = lambda: ops.flash_attn_forward_cuda(Q, K, V, bias, scale=1 / 32 ** 0.5, bias_bcast=True, path=PATH_UMMA)
-        what = {"B": B, "h": h, "L": L}
+        f = lambda: ops.flash_attn_forward_cuda(Q, K, V, bias, scale=1 / d ** 0.5, bias_bcast=True, path=PATH_UMMA)
+        what = {"B": B, "h": h, "L": L, "d": d}
     else:
         m, k, n = (int(v) for v in args.only.split(",")) if args.only else (65536, 256, 256)
         A, Bw = torch.randn(m, k, device=dev, generator=g), torch.randn(n, k, device=dev, generator=g) * 0.02
@@ -797,7 +798,7 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the records of the other kernels")
     ap.add_argument("--no-block", action="store_true", help="skip the sharded IterBlock record")
     ap.add_argument("--only", default="", help="M,K,N: run a single shape of the sweep (profiling runs); B,h,L with --kernel attn")
-    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn", "attn_bf16"],
+    ap.add_argument("--kernel", default="q8", choices=["q8", "tf32", "bf16", "attn", "attn_bf16", "attn8"],
                     help="profiling runs: one launch kind on one workload, launched directly")
     ap.add_argument("--workload", default="sweep", choices=["sweep", "block", "extra_block"],
                     help="block / extra_block: only the sharded IterBlock / extra-MSA FullBlock record "
