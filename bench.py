@@ -18,6 +18,8 @@ Beside the headline the line carries
                    the three axial-attention cases in fp32 and bf16, triangle multiplication, outer-product-mean and the
                    Linear behind it), each timed from its own CUDA graph, each with its roofline
                    (min(tensor peak, intensity x HBM bandwidth), peaks from MEASURED_PEAKS.json);
+  `dev_forward_calls`  BASELINE config 0's shapes: every mul_mat / attention / pair-track call of the dev-size blocks
+                   (51 residues, MSA depth 8, fp32) timed and checked against the CPU checker, on both paths;
   `sharded_block`  the hot-path op sequence of one main IterBlock at full size cut over the N ranks (strong scaling,
                    ms per block, per-class split, exchanged bytes, every op's shard checked against the unsharded op);
   `sharded_extra_block`  the same for one extra-MSA FullBlock (1024 MSA rows of 64 channels, 8 heads x 8, global column
@@ -296,6 +298,35 @@ def graph_time_us(torch, issue, launches, reps=20, warm=3):
 def rotations(working_set_bytes):
     """Copies of a small workload to cycle through so that consecutive launches do not find their inputs in L2."""
     return int(min(48, max(1, math.ceil(1.5 * L2_BYTES / max(working_set_bytes, 1.0)))))
+
+
+def dev_forward_calls(torch, dev, oracle):
+    """BASELINE config 0's shapes: the blocks of the dev-size forward (51 residues, MSA depth 8, fp32 weights; one extra-MSA and
+    one main block are run, the forward has 1 + 2), every mul_mat / attention / tri_mul / outer-product-mean call timed by its
+    own CUDA events and checked against the CPU checker on the tensors it saw -- once on the exact CUDA-core kernels (the
+    forwarders' default) and once on the tensor-core path."""
+    from proteinpredictmachinelearning_b200 import PATH_AUTO, PATH_SIMT, block_bench, ops
+    from checkers import check_block_calls
+    rec = {"workload": "dev-size blocks: L=51, MSA depth 8, d_msa 256 (extra: 64), d_pair 128, fp32 weights, seed 1; op by op "
+                       "(no fused projections), one launch per call, eager", "paths": {}}
+    for name, path, tol in (("cuda cores, exact fp32", PATH_SIMT, 1e-5), ("tensor cores where a kernel exists, tf32 products", PATH_AUTO, 1e-3)):
+        blocks = block_bench.dev_blocks(torch, ops, dev, path=path, fused=False)
+        entry = {"tolerance": tol, "blocks": {}}
+        worst, total_us, n_calls = 0.0, 0.0, 0
+        for kind, blk in blocks.items():
+            calls = check_block_calls(blk.trace, oracle)
+            mult = 2 if kind == "main" else 1
+            us = sum(c["us"] for c in calls)
+            entry["blocks"][kind] = {"calls": [{**c, "us": round(c["us"], 2), "err": float(f"{c['err']:.3g}")} for c in calls],
+                                     "us_per_block": round(us, 1), "blocks_in_the_forward": mult}
+            worst = max(worst, max(c["err"] for c in calls))
+            total_us += mult * us
+            n_calls += len(calls)
+        entry.update({"calls_checked": n_calls, "worst_err": float(f"{worst:.3g}"), "checked": bool(worst <= tol),
+                      "us_per_forward_hot_path": round(total_us, 1)})
+        rec["paths"][name] = entry
+    rec["checked"] = all(e["checked"] for e in rec["paths"].values())
+    return rec
 
 
 def kernel_records(torch, dev, peaks, oracle):
@@ -684,11 +715,13 @@ def run_ours(args):
     del Xh, Ch, Xd, Cd
 
     # ---- the other kernels of the path (rank 0) and the sharded block (all ranks) -----------------------------------
-    kernels = None
+    kernels = dev_calls = None
     if rank == 0 and not args.no_kernels:
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         from checkers import Oracle
-        kernels = kernel_records(torch, dev, peaks, Oracle())
+        oracle = Oracle()
+        kernels = kernel_records(torch, dev, peaks, oracle)
+        dev_calls = dev_forward_calls(torch, dev, oracle)
     barrier()
     block = extra_block = None
     if not args.no_block:
@@ -724,6 +757,7 @@ def run_ours(args):
     if kernels is not None:
         line["kernels"] = kernels
         line["checked_kernels"] = all(k.get("checked", True) for k in kernels)
+        line["dev_forward_calls"] = dev_calls
     if block is not None:
         line["sharded_block"] = block
         line["sharded_extra_block"] = extra_block

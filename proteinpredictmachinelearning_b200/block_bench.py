@@ -59,6 +59,8 @@ import os
 L_RES, N_MSA, D_MSA, D_PAIR, HEADS, HEAD_DIM, OPM_D, TRI_D = 256, 256, 256, 128, 8, 32, 16, 128
 # MSA track of the two block kinds: rows, channels, head dim
 KINDS = {"main": (N_MSA, D_MSA, HEAD_DIM), "extra": (1024, 64, 8)}
+# dev size (BASELINE config 0): one chain of 51 residues, MSA depth 8, every Linear fp32
+DEV_L, DEV_N = 51, 8
 
 
 class Block:
@@ -67,7 +69,8 @@ class Block:
 
     SITES = {"mr_bias": 0, "col_t": 1, "qsum": 1, "right": 2, "pr_bias": 3, "row_t": 4, "pc_bias": 5}
 
-    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None, fused=True, kind="main"):
+    def __init__(self, torch, dist, ops, inputs, weights, G, rank, dev, peers=None, fused=True, kind="main", size="full",
+                 path=None, trace=False):
         self.torch, self.dist, self.ops = torch, dist, ops
         self.fused = fused
         self.inp, self.weights, self.G, self.rank, self.dev = inputs, weights, G, rank, dev
@@ -80,7 +83,13 @@ class Block:
         self.ctx = {}
         self.kind = kind
         self.N, self.D, self.hd_msa = KINDS[kind]
-        L, N = L_RES, self.N
+        self.L = L_RES
+        self.use_q8 = size == "full"             # the dev-size forward is fp32 throughout
+        if size == "dev":
+            self.L, self.N = DEV_L, DEV_N
+        self.path = path                         # None: PATH_AUTO
+        self.trace = [] if trace else None       # one entry per mul_mat / attention / pair-track call: what went in, what came out
+        L, N = self.L, self.N
         self.tok_msa, self.tok_pair = N * L // G, L * L // G
 
     # ---- helpers -----------------------------------------------------------------------------------------------
@@ -116,14 +125,32 @@ class Block:
     def linear(self, x, n_out, q8, tag):
         """One Linear with bias on this rank's token rows."""
         from proteinpredictmachinelearning_b200 import PATH_AUTO, TF32_TMA
+        q8 = q8 and self.use_q8
+        path = PATH_AUTO if self.path is None else self.path
         w, b = self.weights[(tag, x.shape[1], n_out, q8)]
         out = self.buf("lin_" + tag, (x.shape[0], n_out))
+        ev = self.call_begin()
         if q8:
-            self.ops.mul_mat_q8_cuda(w, x, n_out, wtype=2, c_trans=1, bias=b, path=PATH_AUTO, out=out)
+            self.ops.mul_mat_q8_cuda(w, x, n_out, wtype=2, c_trans=1, bias=b, path=path, out=out)
         else:
-            self.ops.mul_mat_cuda(x, w, bias=b, path=PATH_AUTO, tf32_mode=TF32_TMA, out=out)
+            self.ops.mul_mat_cuda(x, w, bias=b, path=path, tf32_mode=TF32_TMA, out=out)
+        self.call_end(ev, "mul_mat_q8" if q8 else "mul_mat", tag, x=x, w=w, bias=b, out=out)
         self.out["lin_" + tag] = out
         return out
+
+    def call_begin(self):
+        if self.trace is None or self.capturing:
+            return None
+        e0 = self.torch.cuda.Event(enable_timing=True)
+        e0.record()
+        return e0
+
+    def call_end(self, e0, op, tag, **tensors):
+        if e0 is None:
+            return
+        e1 = self.torch.cuda.Event(enable_timing=True)
+        e1.record()
+        self.trace.append(dict(op=op, tag=tag, events=(e0, e1), **tensors))
 
     def gather_rows(self, x, tag):
         """All-gather of the ranks' contiguous row ranges (rank order = row order)."""
@@ -176,9 +203,12 @@ class Block:
             t = qkvg.view(batch, seq, 4 * hd)
             o = self.buf("att_" + tag, (batch, seq, hd))
             with self.timed("attention"):
+                ev = self.call_begin()
                 self.ops.flash_attn_tokens(t[:, :, 0:hd], t[:, :, hd:2 * hd], t[:, :, 2 * hd:3 * hd], HEADS, bias=bias,
                                            gate=t[:, :, 3 * hd:4 * hd], act="sigmoid", scale=scale,
-                                           bias_bcast=bias is not None, out=o)
+                                           bias_bcast=bias is not None, out=o, **self.path_kw())
+                self.call_end(ev, "flash_attn_tokens", tag, q=t[:, :, 0:hd], k=t[:, :, hd:2 * hd], v=t[:, :, 2 * hd:3 * hd],
+                              gate=t[:, :, 3 * hd:4 * hd], bias=bias, scale=scale, out=o)
             self.out["att_" + tag] = o
             with self.timed("linear_q8"):
                 return self.linear(o.view(-1, hd), d_in, True, tag + "o")
@@ -191,11 +221,16 @@ class Block:
         shape = (batch, HEADS, seq, head_dim)                                  # flat reinterpretation, as the reference's views
         o = self.buf("att_" + tag, shape)
         with self.timed("attention"):
+            ev = self.call_begin()
             self.ops.flash_attn_forward_cuda(q.view(shape), k.view(shape), v.view(shape), bias, scale=scale,
-                                             bias_bcast=bias is not None, out=o)
+                                             bias_bcast=bias is not None, out=o, **self.path_kw())
+            self.call_end(ev, "flash_attn", tag, q=q.view(shape), k=k.view(shape), v=v.view(shape), bias=bias, scale=scale, out=o)
         self.out["att_" + tag] = o
         with self.timed("linear_q8"):
             return self.linear(o.view(-1, hd), d_in, True, tag + "o")
+
+    def path_kw(self):
+        return {} if self.path is None else {"path": self.path}
 
     def global_column_attention(self, x):
         """Extra-MSA block: projections of every token (fp32 Linears: not on the reference's Q8 list), one query per chunk
@@ -214,7 +249,9 @@ class Block:
         q = self.rows("x_qmean").view(chunks, 1, hd)
         o = self.buf("att_gc", (chunks, 1, hd))
         with self.timed("attention"):
-            self.ops.flash_attn_tokens(q, k, v, HEADS, scale=1.0 / self.hd_msa ** 0.5, out=o)
+            ev = self.call_begin()
+            self.ops.flash_attn_tokens(q, k, v, HEADS, scale=1.0 / self.hd_msa ** 0.5, out=o, **self.path_kw())
+            self.call_end(ev, "flash_attn_tokens", "gc", q=q, k=k, v=v, gate=None, bias=None, scale=1.0 / self.hd_msa ** 0.5, out=o)
         self.out["att_gc"] = o
         with self.timed("linear_tf32"):
             return self.linear(self.rows("x_gc"), self.D, False, "gco")
@@ -225,8 +262,8 @@ class Block:
 
     def bias_layout(self, gathered, tag):
         """[L*L, 8] token-major -> [8, L, L], shared by every batch (the reference's permute copy)."""
-        b = self.buf("bias_" + tag, (HEADS, L_RES, L_RES))
-        b.view(HEADS, L_RES * L_RES).copy_(gathered.t())
+        b = self.buf("bias_" + tag, (HEADS, self.L, self.L))
+        b.view(HEADS, self.L * self.L).copy_(gathered.t())
         self.out["bias_" + tag] = b
         return b
 
@@ -253,10 +290,14 @@ class Block:
             self.ctx["right"] = self.linear(x, OPM_D, True, "or")
 
     def seg_d(self):
-        G, L, N = self.G, L_RES, self.N
+        G, L, N = self.G, self.L, self.N
         opm = self.buf("opm", (OPM_D // G * OPM_D, L, L, 1))
         with self.timed("outer_prod_mean"):
-            self.ops.outer_prod_mean_slabs_cuda(self.ctx["left"].view(OPM_D // G, L, N, 1), self.ctx["right_all"].view(OPM_D, L, N, 1), out=opm)
+            ev = self.call_begin()
+            self.ops.outer_prod_mean_slabs_cuda(self.ctx["left"].view(OPM_D // G, L, N, 1), self.ctx["right_all"].view(OPM_D, L, N, 1), out=opm,
+                                                **self.path_kw())
+            self.call_end(ev, "outer_prod_mean", "opm", left=self.ctx["left"].view(OPM_D // G, L, N, 1),
+                          right=self.ctx["right_all"].view(OPM_D, L, N, 1), out=opm)
         self.out["opm"] = opm
         with self.timed("linear_q8"):
             self.linear(self.rows("x_opm"), D_PAIR, True, "oo")
@@ -272,21 +313,23 @@ class Block:
                     for t in ("tlg", "trg", "tg"):
                         self.linear(x, TRI_D, False, t + d)
             with self.timed("tri_mul"):
-                tm = self.ops.tri_mul_cuda(a.view(TRI_D // G, L, L, 1), b.view(TRI_D // G, L, L, 1), float(L), direction)
+                ev = self.call_begin()
+                tm = self.ops.tri_mul_cuda(a.view(TRI_D // G, L, L, 1), b.view(TRI_D // G, L, L, 1), float(L), direction, **self.path_kw())
+                self.call_end(ev, "tri_mul", d, left=a.view(TRI_D // G, L, L, 1), right=b.view(TRI_D // G, L, L, 1), outgoing=direction, out=tm)
             self.out["tri_" + d] = tm
             with self.timed("linear_tf32"):
                 self.linear(tm.view(self.tok_pair, TRI_D), D_PAIR, False, "to" + d)
         self.ctx["pr_b"] = self.pair_bias("pr")
 
     def seg_e(self):
-        self.ctx["row"] = self.attention(self.rows("x_pair"), L_RES // self.G, self.ctx["pr_bias"], 1.0 / 16 ** 0.5, "pr")
+        self.ctx["row"] = self.attention(self.rows("x_pair"), self.L // self.G, self.ctx["pr_bias"], 1.0 / 16 ** 0.5, "pr")
 
     def seg_f(self):
         self.ctx["pc_b"] = self.pair_bias("pc")
 
     def seg_g(self):
         x = self.rows("x_pair")
-        self.attention(x, L_RES // self.G, self.ctx["pc_bias"], 1.0 / 16 ** 0.5, "pc")
+        self.attention(x, self.L // self.G, self.ctx["pc_bias"], 1.0 / 16 ** 0.5, "pc")
         with self.timed("linear_tf32"):
             self.linear(x, 2 * D_PAIR, False, "pf1")
             self.linear(self.rows("x_pff"), D_PAIR, False, "pf2")
@@ -321,7 +364,7 @@ class Block:
                      else self.ex_qsum,                                                  # partial sums of the global query
                      self.ex_right,
                      self.ex_bias("pr_b", "pr_bias"),
-                     self.ex_transpose("row", L_RES, "row_t"),       # transpose closing pair row attention
+                     self.ex_transpose("row", self.L, "row_t"),       # transpose closing pair row attention
                      self.ex_bias("pc_b", "pc_bias")]
         return segments, exchanges
 
@@ -352,12 +395,15 @@ def exchange_bytes(G, kind="main"):
     return out
 
 
-def make_inputs_and_weights(torch, ops, dev, kind="main", G=1):
-    """Inputs and weights from one seed, identical on every rank."""
-    g = torch.Generator(device=dev).manual_seed(5)
+def make_inputs_and_weights(torch, ops, dev, kind="main", G=1, size="full"):
+    """Inputs and weights from one seed, identical on every rank.  size = "dev": 51 residues, MSA depth 8, fp32 weights only."""
+    g = torch.Generator(device=dev).manual_seed(5 if size == "full" else 1)
     rnd = lambda *shape: torch.randn(shape, device=dev, generator=g)
     N, D_M, hd_m = KINDS[kind]
     L = L_RES
+    if size == "dev":
+        L, N = DEV_L, DEV_N
+    use_q8 = size == "full"
     inputs = {"x_msa": rnd(N * L, D_M), "x_pair": rnd(L * L, D_PAIR), "x_ff": rnd(N * L, 4 * D_M),
               "x_pff": rnd(L * L, 2 * D_PAIR), "x_opm": rnd(L * L, OPM_D * OPM_D)}
     attn = [("mr", D_M, hd_m), ("pr", D_PAIR, HEAD_DIM), ("pc", D_PAIR, HEAD_DIM)] + ([("mc", D_M, hd_m)] if kind == "main" else [])
@@ -379,17 +425,35 @@ def make_inputs_and_weights(torch, ops, dev, kind="main", G=1):
         w = rnd(n_out, k) * 0.02
         b = rnd(n_out) * 0.1
         raw[tag] = (w, b)
+        q8 = q8 and use_q8
         weights[(tag, k, n_out, q8)] = (ops.quantize_q8_0r(w) if q8 else w, b)
     # concatenated weights of the fused form
     cat = lambda tags: (torch.cat([raw[t][0] for t in tags], 0).contiguous(), torch.cat([raw[t][1] for t in tags], 0).contiguous())
     for tag, d_in, hd in attn:
         w, b = cat([tag + t for t in "qkvg"])
-        weights[(tag + "qkvg", d_in, 4 * HEADS * hd, True)] = (ops.quantize_q8_0r(w), b)
+        weights[(tag + "qkvg", d_in, 4 * HEADS * hd, use_q8)] = (ops.quantize_q8_0r(w) if use_q8 else w, b)
     if kind == "extra":
         weights[("gcqkvg", D_M, 4 * HEADS * hd_m, False)] = cat(["gc" + t for t in "qkvg"])
     for d in ("out", "in"):
         weights[("tgates" + d, D_PAIR, 3 * TRI_D, False)] = cat([t + d for t in ("tlg", "trg", "tg")])
     return inputs, weights
+
+
+def dev_blocks(torch, ops, dev, path=None, fused=True):
+    """The blocks of the dev-size forward (BASELINE config 0: 51 residues, MSA depth 8, fp32 weights; 1 extra + 2 main blocks,
+    of which one of each kind is run: the second main block makes the same calls) with every call traced: returns
+    {kind: Block}; each Block's `trace` lists its mul_mat / attention / tri_mul / outer-product-mean calls with their
+    operands, results and CUDA events.  Checking them against the CPU checker is the caller's business (tests, bench)."""
+    blocks = {}
+    for kind in ("extra", "main"):
+        inputs, weights = make_inputs_and_weights(torch, ops, dev, kind, 1, size="dev")
+        warm = Block(torch, None, ops, inputs, weights, 1, 0, dev, fused=fused, kind=kind, size="dev", path=path)
+        warm.run()                               # first-use costs (module load, attributes) stay out of the per-call times
+        blk = Block(torch, None, ops, inputs, weights, 1, 0, dev, fused=fused, kind=kind, size="dev", path=path, trace=True)
+        blk.run()
+        torch.cuda.synchronize()
+        blocks[kind] = blk
+    return blocks
 
 
 def verify(torch, sharded, full, G, rank):

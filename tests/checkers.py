@@ -334,3 +334,51 @@ class Ref:
         out = np.empty(nb * 32, np.float32)
         (self.lib.ref_dequantize_q8_0 if kind == 0 else self.lib.ref_dequantize_q8_1)(_ptr(blocks), _ptr(out), _i64(nb * 32))
         return out
+
+
+def check_block_calls(trace, oracle, heads=8):
+    """Every call a traced block made (proteinpredictmachinelearning_b200.block_bench.Block with trace=True) against the
+    CPU checker on the very tensors the call saw.  Returns one dict per call: op, tag, shape, us (the call's own CUDA-event
+    time), err (normalised max error)."""
+    host = lambda t: None if t is None else t.detach().float().cpu().numpy()
+
+    def rel(got, ref):
+        return float(np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+    out = []
+    for c in trace:
+        op, got = c["op"], host(c["out"])
+        if op == "mul_mat":
+            x, w = host(c["x"]), host(c["w"])
+            ref = oracle.mul_mat_f32(x, w, host(c["bias"]))
+            shape = f"M={x.shape[0]} K={x.shape[1]} N={w.shape[0]}"
+        elif op == "mul_mat_q8":
+            x = host(c["x"])
+            wq = c["w"].detach().cpu().numpy()
+            n_out = got.shape[1]
+            ref = oracle.mul_mat_q8(wq, x, n_out, wtype=2, c_trans=1, bias=host(c["bias"]))
+            shape = f"M={x.shape[0]} K={x.shape[1]} N={n_out} (Q8)"
+        elif op in ("flash_attn", "flash_attn_tokens"):
+            q, k, v, bias = host(c["q"]), host(c["k"]), host(c["v"]), host(c["bias"])
+            if op == "flash_attn_tokens":                   # [B, L, h*d] token-major -> [B, h, L, d]
+                split = lambda t: np.ascontiguousarray(t.reshape(t.shape[0], t.shape[1], heads, -1).transpose(0, 2, 1, 3))
+                q, k, v = split(q), split(k), split(v)
+            ref, _ = oracle.flash_attn(q, k, v, bias, scale=c["scale"], bias_bcast=bias is not None)
+            if op == "flash_attn_tokens":
+                ref = np.ascontiguousarray(ref.transpose(0, 2, 1, 3)).reshape(got.shape)
+                if c.get("gate") is not None:
+                    ref = act_mul_f32(host(c["gate"]), ref, "sigmoid")
+            shape = f"B'={q.shape[0]} h={q.shape[1]} Lq={q.shape[2]} Lk={k.shape[2]} d={q.shape[3]}" + (", bias" if bias is not None else "")
+        elif op == "tri_mul":
+            left, right = host(c["left"]), host(c["right"])
+            ref = oracle.tri_mul(left, right, float(left.shape[1]), c["outgoing"])
+            shape = f"D={left.shape[0]} L={left.shape[1]} " + ("outgoing" if c["outgoing"] else "incoming")
+        elif op == "outer_prod_mean":
+            left, right = host(c["left"]), host(c["right"])
+            ref = oracle.outer_prod_mean(left, right)
+            shape = f"c={left.shape[0]} L={left.shape[1]} N={left.shape[2]}"
+        else:
+            raise ValueError(op)
+        e0, e1 = c["events"]
+        out.append({"op": op, "tag": c["tag"], "shape": shape, "us": e0.elapsed_time(e1) * 1e3, "err": rel(got, ref)})
+    return out
