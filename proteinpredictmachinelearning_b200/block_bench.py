@@ -443,7 +443,7 @@ def dev_blocks(torch, ops, dev, path=None, fused=True):
     """The blocks of the dev-size forward (BASELINE config 0: 51 residues, MSA depth 8, fp32 weights; 1 extra + 2 main blocks,
     of which one of each kind is run: the second main block makes the same calls) with every call traced: returns
     {kind: Block}; each Block's `trace` lists its mul_mat / attention / tri_mul / outer-product-mean calls with their
-    operands, results and CUDA events.  Checking them against the CPU checker is the caller's business (tests, bench)."""
+    operands, results and CUDA events, and `graph_us` is the block's time replayed from a CUDA graph.  Checking them against the CPU checker is the caller's business (tests, bench)."""
     blocks = {}
     for kind in ("extra", "main"):
         inputs, weights = make_inputs_and_weights(torch, ops, dev, kind, 1, size="dev")
@@ -452,6 +452,20 @@ def dev_blocks(torch, ops, dev, path=None, fused=True):
         blk = Block(torch, None, ops, inputs, weights, 1, 0, dev, fused=fused, kind=kind, size="dev", path=path, trace=True)
         blk.run()
         torch.cuda.synchronize()
+        # the same block replayed from a CUDA graph: its time without the host's launch cost
+        warm.capturing = True
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            warm.run()
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        blk.graph_us = e0.elapsed_time(e1) * 1e3 / 20
         blocks[kind] = blk
     return blocks
 

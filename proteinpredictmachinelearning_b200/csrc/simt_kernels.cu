@@ -8,6 +8,8 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <type_traits>
+
 namespace ppml_b200 {
 
 __device__ int g_device_error[4] = {0, 0, 0, 0};
@@ -409,7 +411,7 @@ int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int 
 }
 
 // =============================================================================================
-// General attention forward (any L, Lk, head dim <= 128): one warp per query row, lanes over keys.
+// General attention forward (any L, Lk, head dim <= 128): a warp per query row at a time, lanes over keys.
 // O = softmax(scale * Q K^T + bias) V with denominator (l + eps); LSE = m + log(l + eps);
 // a row with no unmasked key gives O = 0, LSE = -inf.
 // `ft` > 0 reproduces a property of the reference's CPU kernel (src/ops/FlashAttn.cpp:82-121), which walks the keys in
@@ -421,85 +423,217 @@ __device__ __forceinline__ float attn_ld(const float* p) { return *p; }
 __device__ __forceinline__ float attn_ld(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ float attn_ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
-template <typename T>
+// CTA = 4 warps x kRowsPerWarp query rows of one (batch, head).  The keys are walked in tiles of 32 that the CTA stages
+// in shared memory once for all its rows (K rows padded to d + 1 floats: lane = key reads its row without bank
+// conflicts; V unpadded: lane = channel).  Per row and tile: lane j holds the score of key j0 + j, the maximum and the
+// sum go through shuffles, then the 32 probabilities are broadcast one by one against the V tile.
+// DT: the head dim when it is 32 or 64 (loops unrolled, the query row in registers), 0 = any head dim up to 128.
+constexpr int kRowsPerWarp = 4;
+
+template <typename T, int DT>
 __global__ void __launch_bounds__(128)
 attn_rowwarp_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
                     const float* __restrict__ bias, float* __restrict__ O, float* __restrict__ LSE,
                     int H, int L, int Lk, int d, int causal, float scale, float eps, long long bias_batch_stride, int ft,
                     const AttnLayout lay) {
-    extern __shared__ float qs[];                    // [4][d]
+    extern __shared__ float sm[];
+    float* ks = sm;                                  // [32][d + 1]
+    float* vs = ks + 32 * (d + 1);                   // [32][d]
+    float* qs = vs + 32 * d;                         // [4 * kRowsPerWarp][d]
+    float* ps = qs + 4 * kRowsPerWarp * d;           // [4 * kRowsPerWarp][32] probabilities of the current tile (DT > 0)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int i = blockIdx.x * 4 + warp;
+    const int row0 = blockIdx.x * (4 * kRowsPerWarp);
     const int hh = blockIdx.y, b = blockIdx.z;
     const size_t bh = static_cast<size_t>(b) * H + hh;
     const T* Qb = Q + b * lay.q_b + hh * lay.q_h;
     const T* Kb = K + b * lay.k_b + hh * lay.k_h;
     const T* Vb = V + b * lay.v_b + hh * lay.v_h;
-    float* myq = qs + warp * d;
-    if (i < L) for (int dd = lane; dd < d; dd += 32) myq[dd] = attn_ld(Qb + static_cast<size_t>(i) * lay.q_l + dd);
-    __syncwarp();
-    if (i >= L) return;
-    const float* Bb = bias ? bias + static_cast<size_t>(b) * bias_batch_stride +
-                                 (static_cast<size_t>(hh) * L + i) * static_cast<size_t>(Lk) : nullptr;
-    const int jmax = causal ? ((i + 1 < Lk) ? i + 1 : Lk) : Lk;
-    float m = -CUDART_INF_F, l = 0.0f;
-    float mfirst = -CUDART_INF_F;                    // maximum over the first `ft` keys (see launch_attn_rowwarp)
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int j0 = 0; j0 < jmax; j0 += 32) {
-        const int j = j0 + lane;
-        float s = -CUDART_INF_F;
-        if (j < jmax) {
-            const T* k = Kb + static_cast<size_t>(j) * lay.k_l;
-            float dot = 0.0f;
-            for (int dd = 0; dd < d; ++dd) dot = fmaf(myq[dd], attn_ld(k + dd), dot);
-            s = dot * scale;
-            if (Bb) s += Bb[j];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int i = row0 + warp * kRowsPerWarp + r;
+        for (int dd = lane; dd < d; dd += 32)
+            qs[(warp * kRowsPerWarp + r) * d + dd] = i < L ? attn_ld(Qb + static_cast<size_t>(i) * lay.q_l + dd) : 0.0f;
+    }
+    const int last_row = min(row0 + 4 * kRowsPerWarp - 1, L - 1);
+    const int jend = causal ? min(last_row + 1, Lk) : Lk;     // keys needed by any row of this CTA
+    float m[kRowsPerWarp], l[kRowsPerWarp], mfirst[kRowsPerWarp], acc[kRowsPerWarp][4];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        m[r] = -CUDART_INF_F; l[r] = 0.0f; mfirst[r] = -CUDART_INF_F;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) acc[r][t] = 0.0f;
+    }
+    for (int j0 = 0; j0 < jend; j0 += 32) {
+        __syncthreads();                             // every warp is done with the previous tile (and, first, qs is written)
+        for (int key = warp; key < 32; key += 4) {
+            const bool ok = j0 + key < Lk;
+            const T* kp = Kb + static_cast<size_t>(ok ? j0 + key : 0) * lay.k_l;
+            const T* vp = Vb + static_cast<size_t>(ok ? j0 + key : 0) * lay.v_l;
+            for (int dd = lane; dd < d; dd += 32) {
+                ks[key * (d + 1) + dd] = ok ? attn_ld(kp + dd) : 0.0f;
+                vs[key * d + dd] = ok ? attn_ld(vp + dd) : 0.0f;
+            }
         }
-        if (j < ft) mfirst = fmaxf(mfirst, s);
-        float mt = s;
+        __syncthreads();
+        if constexpr (DT > 0) {
+            // the warp's rows together: one read of a K or V element serves all of them, and the probabilities go to the
+            // P V loop through shared memory (16-byte broadcast reads) instead of one shuffle per key and row
+            const int j = j0 + lane;
+            float dot[kRowsPerWarp];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off));
-        const float m_new = fmaxf(m, mt);
-        const float alpha = (m == -CUDART_INF_F) ? 0.0f : expf(m - m_new);
-        const float pj = (j < jmax && m_new != -CUDART_INF_F) ? expf(s - m_new) : 0.0f;
-        float lt = pj;
+            for (int r = 0; r < kRowsPerWarp; ++r) dot[r] = 0.0f;
+            const float* k = ks + lane * (DT + 1);
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, off);
-        l = alpha * l + lt;
-        m = m_new;
+            for (int d4 = 0; d4 < DT / 4; ++d4) {
+                const float k0 = k[4 * d4], k1 = k[4 * d4 + 1], k2 = k[4 * d4 + 2], k3 = k[4 * d4 + 3];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) acc[t] *= alpha;
-        const int nj = (jmax - j0 < 32) ? (jmax - j0) : 32;
-        for (int jj = 0; jj < nj; ++jj) {
-            const float p = __shfl_sync(0xffffffffu, pj, jj);
-            const T* v = Vb + static_cast<size_t>(j0 + jj) * lay.v_l;
+                for (int r = 0; r < kRowsPerWarp; ++r) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + (warp * kRowsPerWarp + r) * DT + 4 * d4);
+                    dot[r] = fmaf(q4.x, k0, dot[r]); dot[r] = fmaf(q4.y, k1, dot[r]);
+                    dot[r] = fmaf(q4.z, k2, dot[r]); dot[r] = fmaf(q4.w, k3, dot[r]);
+                }
+            }
+            float* pw = ps + warp * kRowsPerWarp * 32;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const int dd = lane + 32 * t;
-                if (dd < d) acc[t] = fmaf(p, attn_ld(v + dd), acc[t]);
+            for (int r = 0; r < kRowsPerWarp; ++r) {
+                const int i = row0 + warp * kRowsPerWarp + r;
+                const int jmax = i < L ? (causal ? min(i + 1, Lk) : Lk) : 0;
+                float s = -CUDART_INF_F;
+                if (j < jmax) {
+                    s = dot[r] * scale;
+                    if (bias) s += bias[static_cast<size_t>(b) * bias_batch_stride + (static_cast<size_t>(hh) * L + i) * static_cast<size_t>(Lk) + j];
+                }
+                if (j < ft) mfirst[r] = fmaxf(mfirst[r], s);
+                float mt = s;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off));
+                const float m_new = fmaxf(m[r], mt);
+                const float alpha = (m[r] == -CUDART_INF_F) ? 0.0f : expf(m[r] - m_new);
+                const float pj = (j < jmax && m_new != -CUDART_INF_F) ? expf(s - m_new) : 0.0f;
+                float lt = pj;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, off);
+                l[r] = alpha * l[r] + lt;
+                m[r] = m_new;
+#pragma unroll
+                for (int t = 0; t < DT / 32; ++t) acc[r][t] *= alpha;
+                pw[r * 32 + lane] = pj;
+            }
+            __syncwarp();
+#pragma unroll 2
+            for (int j4 = 0; j4 < 8; ++j4) {
+                float v[4][DT / 32];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int t = 0; t < DT / 32; ++t) v[u][t] = vs[(j4 * 4 + u) * DT + lane + 32 * t];
+#pragma unroll
+                for (int r = 0; r < kRowsPerWarp; ++r) {
+                    const float4 p4 = *reinterpret_cast<const float4*>(pw + r * 32 + j4 * 4);
+#pragma unroll
+                    for (int t = 0; t < DT / 32; ++t) {
+                        acc[r][t] = fmaf(p4.x, v[0][t], acc[r][t]); acc[r][t] = fmaf(p4.y, v[1][t], acc[r][t]);
+                        acc[r][t] = fmaf(p4.z, v[2][t], acc[r][t]); acc[r][t] = fmaf(p4.w, v[3][t], acc[r][t]);
+                    }
+                }
+            }
+            __syncwarp();                            // the probabilities are read before the next tile overwrites them
+            continue;
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int i = row0 + warp * kRowsPerWarp + r;
+            const int jmax = i < L ? (causal ? min(i + 1, Lk) : Lk) : 0;
+            if (j0 >= jmax) continue;                // the same for every lane of the warp
+            const float* myq = qs + (warp * kRowsPerWarp + r) * d;
+            const int j = j0 + lane;
+            float s = -CUDART_INF_F;
+            if (j < jmax) {
+                const float* k = ks + lane * (d + 1);
+                float dot = 0.0f;
+                if constexpr (DT > 0) {
+#pragma unroll
+                    for (int d4 = 0; d4 < DT / 4; ++d4) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(myq + 4 * d4);      // the same address in every lane
+                        dot = fmaf(q4.x, k[4 * d4], dot); dot = fmaf(q4.y, k[4 * d4 + 1], dot);
+                        dot = fmaf(q4.z, k[4 * d4 + 2], dot); dot = fmaf(q4.w, k[4 * d4 + 3], dot);
+                    }
+                } else {
+                    for (int dd = 0; dd < d; ++dd) dot = fmaf(myq[dd], k[dd], dot);
+                }
+                s = dot * scale;
+                if (bias) s += bias[static_cast<size_t>(b) * bias_batch_stride + (static_cast<size_t>(hh) * L + i) * static_cast<size_t>(Lk) + j];
+            }
+            if (j < ft) mfirst[r] = fmaxf(mfirst[r], s);
+            float mt = s;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, off));
+            const float m_new = fmaxf(m[r], mt);
+            const float alpha = (m[r] == -CUDART_INF_F) ? 0.0f : expf(m[r] - m_new);
+            const float pj = (j < jmax && m_new != -CUDART_INF_F) ? expf(s - m_new) : 0.0f;
+            float lt = pj;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, off);
+            l[r] = alpha * l[r] + lt;
+            m[r] = m_new;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) acc[r][t] *= alpha;
+            const int nj = (jmax - j0 < 32) ? (jmax - j0) : 32;
+            if constexpr (DT > 0) {
+                if (nj == 32) {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const float p = __shfl_sync(0xffffffffu, pj, jj);
+#pragma unroll
+                        for (int t = 0; t < DT / 32; ++t) acc[r][t] = fmaf(p, vs[jj * DT + lane + 32 * t], acc[r][t]);
+                    }
+                } else {
+                    for (int jj = 0; jj < nj; ++jj) {
+                        const float p = __shfl_sync(0xffffffffu, pj, jj);
+#pragma unroll
+                        for (int t = 0; t < DT / 32; ++t) acc[r][t] = fmaf(p, vs[jj * DT + lane + 32 * t], acc[r][t]);
+                    }
+                }
+            } else {
+                for (int jj = 0; jj < nj; ++jj) {
+                    const float p = __shfl_sync(0xffffffffu, pj, jj);
+                    const float* v = vs + jj * d;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int dd = lane + 32 * t;
+                        if (dd < d) acc[r][t] = fmaf(p, v[dd], acc[r][t]);
+                    }
+                }
             }
         }
     }
-    if (ft > 0) {
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) mfirst = fmaxf(mfirst, __shfl_xor_sync(0xffffffffu, mfirst, off));
-        if (mfirst == -CUDART_INF_F) l = 0.0f;       // the reference's first key tile is fully masked: O = 0, LSE = -inf
-    }
-    const long long ooff = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l;
-    const long long goff = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l;
-    float* o = O + ooff;
-    if (l > 0.0f) {
-        const float inv = 1.0f / (l + eps);
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int i = row0 + warp * kRowsPerWarp + r;
+        float mf = mfirst[r];
+        if (ft > 0) {
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const int dd = lane + 32 * t;
-            if (dd < d) o[dd] = lay.gate ? act_scalar(lay.act, lay.gate[goff + dd]) * (acc[t] * inv) : acc[t] * inv;
+            for (int off = 16; off > 0; off >>= 1) mf = fmaxf(mf, __shfl_xor_sync(0xffffffffu, mf, off));
         }
-        if (LSE && lane == 0) LSE[bh * L + i] = m + logf(l + eps);
-    } else {
+        if (i >= L) continue;
+        float lr = l[r];
+        if (ft > 0 && mf == -CUDART_INF_F) lr = 0.0f;    // the reference's first key tile is fully masked: O = 0, LSE = -inf
+        const long long ooff = b * lay.o_b + hh * lay.o_h + static_cast<long long>(i) * lay.o_l;
+        const long long goff = b * lay.g_b + hh * lay.g_h + static_cast<long long>(i) * lay.g_l;
+        float* o = O + ooff;
+        if (lr > 0.0f) {
+            const float inv = 1.0f / (lr + eps);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) { const int dd = lane + 32 * t; if (dd < d) o[dd] = 0.0f; }
-        if (LSE && lane == 0) LSE[bh * L + i] = -CUDART_INF_F;
+            for (int t = 0; t < 4; ++t) {
+                const int dd = lane + 32 * t;
+                if (dd < d) o[dd] = lay.gate ? act_scalar(lay.act, lay.gate[goff + dd]) * (acc[r][t] * inv) : acc[r][t] * inv;
+            }
+            if (LSE && lane == 0) LSE[bh * L + i] = m[r] + logf(lr + eps);
+        } else {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) { const int dd = lane + 32 * t; if (dd < d) o[dd] = 0.0f; }
+            if (LSE && lane == 0) LSE[bh * L + i] = -CUDART_INF_F;
+        }
     }
 }
 
@@ -891,18 +1025,22 @@ int launch_attn_rowwarp(const void* Q, const void* K, const void* V, int elem, c
                                           bias, O, LSE, B, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay, st);
         if (done) return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
     }
-    dim3 grid((L + 3) / 4, H, B);
-    const size_t smem = 4 * d * sizeof(float);
-    if (elem == 0)
-        attn_rowwarp_kernel<float><<<grid, 128, smem, st>>>(static_cast<const float*>(Q), static_cast<const float*>(K),
-            static_cast<const float*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay);
-    else if (elem == 1)
-        attn_rowwarp_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(Q),
-            static_cast<const __nv_bfloat16*>(K), static_cast<const __nv_bfloat16*>(V), bias, O, LSE, H, L, Lk, d, causal,
-            scale, eps, bias_batch_stride, ft, lay);
-    else
-        attn_rowwarp_kernel<__half><<<grid, 128, smem, st>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
-            static_cast<const __half*>(V), bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay);
+    dim3 grid((L + 4 * kRowsPerWarp - 1) / (4 * kRowsPerWarp), H, B);
+    const size_t smem = (32 * (d + 1) + 32 * d + 4 * kRowsPerWarp * (d + 32)) * sizeof(float);     // at most 43 KB (d = 128)
+    auto go = [&](auto tag, auto dt) {
+        using T = decltype(tag);
+        constexpr int DT = decltype(dt)::value;
+        attn_rowwarp_kernel<T, DT><<<grid, 128, smem, st>>>(static_cast<const T*>(Q), static_cast<const T*>(K), static_cast<const T*>(V),
+                                                            bias, O, LSE, H, L, Lk, d, causal, scale, eps, bias_batch_stride, ft, lay);
+    };
+    auto by_dim = [&](auto tag) {
+        if (d == 32) go(tag, std::integral_constant<int, 32>{});
+        else if (d == 64) go(tag, std::integral_constant<int, 64>{});
+        else go(tag, std::integral_constant<int, 0>{});
+    };
+    if (elem == 0) by_dim(float{});
+    else if (elem == 1) by_dim(__nv_bfloat16{});
+    else by_dim(__half{});
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
 }
 
