@@ -450,6 +450,10 @@ def dev_blocks(torch, ops, dev, path=None, fused=True):
         warm = Block(torch, None, ops, inputs, weights, 1, 0, dev, fused=fused, kind=kind, size="dev", path=path)
         warm.run()                               # first-use costs (module load, attributes) stay out of the per-call times
         blk = Block(torch, None, ops, inputs, weights, 1, 0, dev, fused=fused, kind=kind, size="dev", path=path, trace=True)
+        blk.run()                                # its results come from fresh device allocations: not the run to time
+        torch.cuda.synchronize()
+        blk.out.clear()
+        blk.trace.clear()
         blk.run()
         torch.cuda.synchronize()
         # the same block replayed from a CUDA graph: its time without the host's launch cost
