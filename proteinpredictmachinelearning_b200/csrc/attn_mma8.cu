@@ -27,6 +27,9 @@ namespace {
 __device__ __forceinline__ float ex2_approx(float x) {
     float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
+}
 // the tensor core reads the upper 19 bits of an operand: adding half an ulp of tf32 first makes that a rounding
 __device__ __forceinline__ uint32_t tf32_bits(float x) { return __float_as_uint(x) + 0x1000u; }
 
@@ -203,8 +206,8 @@ attn_d8_mma_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
             float v0 = o[mi][hr * 2] * inv, v1 = o[mi][hr * 2 + 1] * inv;
             if (lay.gate) {
                 if (lay.act == 1) {                                 // sigmoid: 1 / (1 + 2^(-x log2 e)) on the fast units
-                    v0 *= __frcp_rn(1.0f + ex2_approx(-gv[r][0] * kLog2e));
-                    v1 *= __frcp_rn(1.0f + ex2_approx(-gv[r][1] * kLog2e));
+                    v0 *= rcp_approx(1.0f + ex2_approx(-gv[r][0] * kLog2e));
+                    v1 *= rcp_approx(1.0f + ex2_approx(-gv[r][1] * kLog2e));
                 } else {
                     v0 *= act_scalar(lay.act, gv[r][0]); v1 *= act_scalar(lay.act, gv[r][1]);
                 }

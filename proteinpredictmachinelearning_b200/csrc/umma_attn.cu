@@ -72,15 +72,18 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // tested once per row, not per element (32 copies of the switch with their expf / tanhf bodies made the gate cost as much
 // as the rest of the kernel: 20.8 M against 15.3 M executed instructions, stalls on instruction fetch).  Sigmoid and SiLU,
 // what the model uses, take the hardware exp2 and reciprocal approximations (2 ulp, far inside the 1e-3 of the tf32 products).
+// one instruction each on the transcendental unit (the IEEE-rounded reciprocal is a sequence of a dozen)
+__device__ __forceinline__ float ex2_fast(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcp_fast(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ void gate_row(int kind, const float (&g)[32], float (&o)[32]) {
     switch (kind) {
         case 1:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] *= __frcp_rn(1.0f + __expf(-g[j]));
+            for (int j = 0; j < 32; ++j) o[j] *= rcp_fast(1.0f + ex2_fast(-1.4426950408889634f * g[j]));
             break;
         case 2:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] *= g[j] * __frcp_rn(1.0f + __expf(-g[j]));
+            for (int j = 0; j < 32; ++j) o[j] *= g[j] * rcp_fast(1.0f + ex2_fast(-1.4426950408889634f * g[j]));
             break;
         case 3:
 #pragma unroll
