@@ -65,11 +65,19 @@ constexpr int kEpiStagePitch = 144;                       // bytes per staged ro
 constexpr int kEpiStageBytes = 32 * kEpiStagePitch;       // one warp's 32 x 32 transposition buffer
 constexpr int kEpiBiasBytes = 2 * 256 * 4;                // one warp's copy of the tile's bias slice and of its u slice
 
-// the activations of the reference's act_fwd_scalar (src/backend/CPUKernels.cpp:1903-1916), same formulas
+// the activations of the reference's act_fwd_scalar (src/backend/CPUKernels.cpp:1903-1916), same formulas; sigmoid and
+// SiLU (what the model's gates use) take the hardware exp2 / reciprocal approximations (about 2 ulp, far inside the 1e-3
+// of the tf32 product they follow): expf and an IEEE division cost a dozen instructions per element
+__device__ __forceinline__ float act_sigmoid_fast(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
 __device__ __forceinline__ float act_apply(int kind, float x) {
     switch (kind) {
-        case 1: return 1.0f / (1.0f + expf(-x));
-        case 2: return x / (1.0f + expf(-x));
+        case 1: return act_sigmoid_fast(x);
+        case 2: return x * act_sigmoid_fast(x);
         case 3: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
         case 4: return tanhf(x);
         case 5: return x > 0.0f ? x : 0.0f;
