@@ -124,18 +124,46 @@ peer_transpose_kernel(const uint4* __restrict__ x, Peers out, int n_loc, int L, 
     __shared__ int ok_s;
     const uint32_t epoch = g_site_epoch[site] + 1u;
     if (!exchange_begin(flags, site, rank, world, epoch, err, &ok_s)) return;
+    // a warp moves whole rows of c4 16-byte words: the destination of a row is found once per row with 32-bit arithmetic
+    // (a division per 16-byte word, as first written, cost more than the copy), and four rows are in flight per warp
     const int l_loc = L / world;
-    const long long total = static_cast<long long>(n_loc) * L * c4;
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const int rows = n_loc * L;
     const long long n_all = static_cast<long long>(world) * n_loc;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int c = static_cast<int>(i % c4);
-        const long long row = i / c4;
-        const int l = static_cast<int>(row % L);
-        const int n = static_cast<int>(row / L);
+    const int lane = threadIdx.x & 31;
+    const int warps_total = static_cast<int>(gridDim.x) * (blockDim.x >> 5);
+    const int warp_id = static_cast<int>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr int kRows = 4;
+    auto dst_of = [&](int row) -> uint4* {
+        const int n = row / L, l = row - n * L;
         const int peer = l / l_loc;
-        uint4* dst = static_cast<uint4*>(out.p[peer]) + ((static_cast<long long>(l - peer * l_loc) * n_all + rank * n_loc + n) * c4 + c);
-        *dst = x[i];
+        return static_cast<uint4*>(out.p[peer]) + (static_cast<long long>(l - peer * l_loc) * n_all + rank * n_loc + n) * c4;
+    };
+    if (c4 <= 64) {
+        for (int row = warp_id * kRows; row < rows; row += warps_total * kRows) {
+            uint4 v[kRows][2];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int c = lane + 32 * k;
+                    if (row + r < rows && c < c4) v[r][k] = x[static_cast<long long>(row + r) * c4 + c];
+                }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                if (row + r >= rows) break;
+                uint4* dst = dst_of(row + r);
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int c = lane + 32 * k;
+                    if (c < c4) dst[c] = v[r][k];
+                }
+            }
+        }
+    } else {
+        for (int row = warp_id; row < rows; row += warps_total) {
+            uint4* dst = dst_of(row);
+            for (int c = lane; c < c4; c += 32) dst[c] = x[static_cast<long long>(row) * c4 + c];
+        }
     }
     exchange_end(flags, site, rank, world, epoch, err);
 }
@@ -209,9 +237,10 @@ int ppml_b200_peer_transpose(const float* x, void* const* out_ptrs, int n_loc, i
     if ((reinterpret_cast<uintptr_t>(x) & 15u) || !peers_ok(out_ptrs, world) || !peers_ok(flag_ptrs, world)) return ST_BAD_ARGS;
     int* err = device_error_ptr();
     if (!err) return ST_LAUNCH;
+    if (static_cast<long long>(n_loc) * L > 0x7fffffffLL) return ST_BAD_ARGS;
     const long long total = static_cast<long long>(n_loc) * L * (C / 4);
     long long grid = (total + 255) / 256;
-    const int cap = num_sms() / 2 > 0 ? num_sms() / 2 : 1;
+    const int cap = num_sms() > 0 ? num_sms() : 1;
     if (grid > cap) grid = cap;
     peer_transpose_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint4*>(x), as_peers(out_ptrs, world), n_loc, L, C / 4, rank, world, as_peers(flag_ptrs, world), site, err);
