@@ -4,15 +4,17 @@
 // operands in swizzled shared-memory tiles of at least 32 bytes per row) do not fit a contraction this short, and on
 // CUDA cores the sixteen FMAs per (query, key) pair alone cost 0.24 ms at the extra-MSA size.
 //
-// CTA = 4 warps.  A warp owns 32 query rows (two m tiles) of one (batch, head) and walks the keys in tiles of 64:
+// A warp owns 32 query rows (two m tiles) of one (batch, head) and walks the keys in tiles of 64:
 //   S = bias tile (the accumulator's start value) + Q K^T    8 n tiles x 2 m tiles, K fragments shared by the m tiles
 //   online softmax in the accumulator layout (a row lives in the four lanes of a quad: two shuffles per row and tile)
 //   O += P V                                                 P is the score fragment itself: with the keys of an n tile
 //                                                            taken in the order (0, 2, 4, 6, 1, 3, 5, 7) the
 //                                                            accumulator layout of S is the A layout of the product
-// With a bias shared by the batch (or none) the four warps of a CTA work on four batch elements and the same rows, so
-// one staged bias tile serves four; with a bias per batch element they work on 128 rows of one batch element.
-// K, V (fp32, 16-byte aligned rows) and the bias tile arrive by cp.async into two stages, laid out so that every
+//   l += P 1                                                 the row sums come from a product of the same fragment with ones
+// With a bias shared by the batch (or none) a CTA of 8 warps works on four batch elements and 64 rows, so one staged bias
+// tile serves four batch elements and one staged K / V tile two row groups; with a bias per batch element a CTA of 4 warps
+// works on 128 rows of one batch element.  A CTA walks several consecutive row blocks; its copies run ahead across them.
+// Q, K, V (fp32, 16-byte aligned rows) and the bias tile arrive by cp.async into two stages, laid out so that every
 // fragment read is one conflict-free 4-byte (K, V) or 8-byte (bias) read per lane.  Arithmetic contract as the other
 // attention kernels (masking, eps in the denominator, rows without a visible key, first-tile rule); Q, K and V are
 // rounded to tf32 (half away from zero), P is cut to tf32 and its row sum taken from the cut values; softmax and
