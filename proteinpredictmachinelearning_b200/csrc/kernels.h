@@ -39,6 +39,9 @@ int launch_quantize_q8_1(const float* x, void* y, long long ne, cudaStream_t st)
 int launch_quantize_q8_0r(const float* w, void* out, long long ne, cudaStream_t st);
 int launch_repack_q8_0(const void* blocks34, long long nblocks, void* q8_0r, cudaStream_t st);
 int launch_dequantize_q8(const void* x, float* y, long long ne, int kind, cudaStream_t st);
+// Q8 product with at most 16 output columns in one pass on CUDA cores (planar weights, C[token][M]); ST_UNSUPPORTED_PATH otherwise
+int launch_q8_skinny(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
+                     int* sumi_out, cudaStream_t st);
 int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int nblk, int wtype, int c_trans,
                    const float* bias, int* sumi_out, cudaStream_t st);
 // elem: 0 = fp32 Q/K/V, 1 = bf16, 2 = fp16; bias, O and LSE are fp32

@@ -411,6 +411,135 @@ int launch_q8_dp4a(const void* W, const void* acts, float* C, int M, int N, int 
 }
 
 // =============================================================================================
+// Q8 product with very few output columns (the model's pair-bias and outer-product-mean projections: 128 -> 8,
+// 256 -> 16, 64 -> 16), planar Q8_0R weights, C[token][M].  The tensor-core kernel is bound by its activation quantizer on
+// such shapes; here the whole product is one pass over the activations on CUDA cores.  A lane takes one quant block
+// (32 values, 128 contiguous bytes) of one token row, consecutive lanes consecutive blocks: the warp reads its 4 KB with
+// eight fully coalesced 16-byte loads per lane into a padded shared-memory buffer and each lane reads its block back
+// (a lane loading its own 128 bytes directly makes every load instruction touch 32 lines, which bounds the kernel by
+// the L1 tag rate) -- quantizes it in registers by the Q8_1 rule (bit-exact with the host quantizer, see quantize_q8_1_kernel),
+// takes its int32 dot products with the MP (padded M) weight rows from shared memory by dp4a, scales them, and the
+// K / 32 lanes of a token row add their parts with shuffles.
+// =============================================================================================
+__device__ __forceinline__ uint32_t sk_pack_s8(int a, int b, uint32_t c) {       // (c << 16) | (sat_s8(a) << 8) | sat_s8(b)
+    uint32_t r; asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c)); return r;
+}
+__device__ __forceinline__ int sk_round_half_away(float y) {                     // trunc(y + copysign(0.5, y)), the sum rounded toward zero
+    float t; asm("add.rz.f32 %0, %1, %2;" : "=f"(t) : "f"(y), "f"(copysignf(0.5f, y)));
+    int r; asm("cvt.rzi.s32.f32 %0, %1;" : "=r"(r) : "f"(t)); return r;
+}
+
+constexpr int kSkinnyWarps = 4, kSkinnyPitch = 36;     // floats per staged block: 16-byte reads of 8 lanes hit 8 bank groups
+
+template <int MP>
+__global__ void __launch_bounds__(32 * kSkinnyWarps)
+q8_skinny_kernel(const uint8_t* __restrict__ W, const float* __restrict__ X, float* __restrict__ C, int M, long long units,
+                 int nblk, int lg_nblk, const float* __restrict__ bias, int* __restrict__ sumi_out) {
+    extern __shared__ __align__(16) int sk_smem[];
+    int* ws = sk_smem;                                              // [MP][nblk][8] weight words
+    float* dws = reinterpret_cast<float*>(ws + MP * nblk * 8);      // [MP][nblk] weight scales
+    float* xs = dws + MP * nblk + (threadIdx.x >> 5) * (32 * kSkinnyPitch);     // this warp's 32 staged blocks
+    const size_t nb_all = static_cast<size_t>(M) * nblk;
+    for (int e = threadIdx.x; e < MP * nblk * 8; e += blockDim.x) {
+        const int m = e / (nblk * 8);
+        ws[e] = m < M ? reinterpret_cast<const int*>(W)[e] : 0;     // planar: [M][nblk][32] int8, row m block ib at (m nblk + ib) 32
+    }
+    for (int e = threadIdx.x; e < MP * nblk; e += blockDim.x)
+        dws[e] = e < M * nblk ? __half2float(*reinterpret_cast<const __half*>(W + nb_all * 32 + static_cast<size_t>(e) * 2)) : 0.0f;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const long long step = static_cast<long long>(gridDim.x) * (blockDim.x >> 5) * 32;
+    for (long long u0 = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; u0 < units; u0 += step) {
+        const long long u = u0 + lane;
+        const bool live = u < units;
+        const long long row = u >> lg_nblk;
+        const int ib = static_cast<int>(u & (nblk - 1));
+        float x[32];
+        {
+            const float4* src = reinterpret_cast<const float4*>(X + u0 * 32);       // the warp's 32 blocks: 256 16-byte words
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int g = j * 32 + lane;                                        // word g: block g / 8, word g % 8 of it
+                v[j] = (u0 + (g >> 3) < units) ? __ldg(src + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            __syncwarp();                                                           // the previous step's reads are done
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int g = j * 32 + lane;
+                *reinterpret_cast<float4*>(xs + (g >> 3) * kSkinnyPitch + (g & 7) * 4) = v[j];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 w = *reinterpret_cast<const float4*>(xs + lane * kSkinnyPitch + j * 4);
+                x[4 * j] = w.x; x[4 * j + 1] = w.y; x[4 * j + 2] = w.z; x[4 * j + 3] = w.w;
+            }
+        }
+        float amax = fabsf(x[0]), vmax = x[0];                      // the first element of maximum magnitude
+#pragma unroll
+        for (int j = 1; j < 32; ++j)
+            if (fabsf(x[j]) > amax) { amax = fabsf(x[j]); vmax = x[j]; }
+        const float d = (amax == 0.0f) ? 0.0f : vmax * -0.0078125f;
+        const float inv = (d == 0.0f) ? 0.0f : 1.0f / d;
+        uint32_t aq[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int q0 = sk_round_half_away(x[4 * j] * inv), q1 = sk_round_half_away(x[4 * j + 1] * inv);
+            const int q2 = sk_round_half_away(x[4 * j + 2] * inv), q3 = sk_round_half_away(x[4 * j + 3] * inv);
+            aq[j] = sk_pack_s8(q1, q0, sk_pack_s8(q3, q2, 0u));
+        }
+        const float da = __half2float(__float2half_rn(d));
+        float part[MP];
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            const int4 w0 = *reinterpret_cast<const int4*>(ws + (m * nblk + ib) * 8);
+            const int4 w1 = *reinterpret_cast<const int4*>(ws + (m * nblk + ib) * 8 + 4);
+            int sumi = __dp4a(w0.x, static_cast<int>(aq[0]), 0);
+            sumi = __dp4a(w0.y, static_cast<int>(aq[1]), sumi); sumi = __dp4a(w0.z, static_cast<int>(aq[2]), sumi);
+            sumi = __dp4a(w0.w, static_cast<int>(aq[3]), sumi); sumi = __dp4a(w1.x, static_cast<int>(aq[4]), sumi);
+            sumi = __dp4a(w1.y, static_cast<int>(aq[5]), sumi); sumi = __dp4a(w1.z, static_cast<int>(aq[6]), sumi);
+            sumi = __dp4a(w1.w, static_cast<int>(aq[7]), sumi);
+            if (sumi_out != nullptr && live && m < M) sumi_out[(static_cast<size_t>(row) * M + m) * nblk + ib] = sumi;
+            part[m] = static_cast<float>(sumi) * (dws[m * nblk + ib] * da);
+        }
+        for (int off = nblk >> 1; off > 0; off >>= 1) {             // the lanes of a token row are neighbours (nblk is a power of two)
+#pragma unroll
+            for (int m = 0; m < MP; ++m) part[m] += __shfl_xor_sync(0xffffffffu, part[m], off);
+        }
+        if (live && ib == 0) {
+            float* c = C + static_cast<size_t>(row) * M;
+#pragma unroll
+            for (int m = 0; m < MP; ++m)
+                if (m < M) c[m] = part[m] + (bias != nullptr ? bias[m] : 0.0f);
+        }
+    }
+}
+
+// ST_UNSUPPORTED_PATH unless: planar weights (the caller checks), c_trans, M <= 16, K / 32 a power of two up to 32,
+// activations 16-byte aligned
+int launch_q8_skinny(const void* W, const float* X, float* C, int M, int N, int K, int c_trans, const float* bias,
+                     int* sumi_out, cudaStream_t st) {
+    const int nblk = K / 32;
+    if (!c_trans || M > 16 || nblk < 1 || nblk > 32 || (nblk & (nblk - 1)) != 0 || (reinterpret_cast<uintptr_t>(X) & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(W) & 3) != 0)
+        return ST_UNSUPPORTED_PATH;
+    int lg = 0;
+    while ((1 << lg) < nblk) ++lg;
+    const long long units = static_cast<long long>(N) * nblk;
+    long long grid = (units + 32 * kSkinnyWarps - 1) / (32 * kSkinnyWarps);
+    const long long cap = 8LL * num_sms();
+    if (grid > cap) grid = cap;
+    const int mp = M <= 8 ? 8 : 16;
+    const size_t smem = static_cast<size_t>(mp) * nblk * (32 + 4) + kSkinnyWarps * 32 * kSkinnyPitch * sizeof(float);   // <= 36.9 KB
+    if (mp == 8)
+        q8_skinny_kernel<8><<<static_cast<unsigned>(grid), 32 * kSkinnyWarps, smem, st>>>(static_cast<const uint8_t*>(W), X, C, M, units, nblk, lg, bias, sumi_out);
+    else
+        q8_skinny_kernel<16><<<static_cast<unsigned>(grid), 32 * kSkinnyWarps, smem, st>>>(static_cast<const uint8_t*>(W), X, C, M, units, nblk, lg, bias, sumi_out);
+    return cudaGetLastError() == cudaSuccess ? ST_OK : ST_LAUNCH;
+}
+
+// =============================================================================================
 // General attention forward (any L, Lk, head dim <= 128): a warp per query row at a time, lanes over keys.
 // O = softmax(scale * Q K^T + bias) V with denominator (l + eps); LSE = m + log(l + eps);
 // a row with no unmasked key gives O = 0, LSE = -inf.

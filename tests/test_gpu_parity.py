@@ -288,6 +288,27 @@ def test_mul_mat_q8_one_and_two_pass_forms(oracle, Mout, Ntok, K):
     assert cases.rel_err(out[1][0], ref) <= TOL_FP32
 
 
+@pytest.mark.parametrize("Mout,Ntok,K", [(8, 2601, 128), (16, 408, 256), (16, 1000, 64), (5, 300, 1024), (1, 4099, 32), (13, 70, 512)])
+def test_mul_mat_q8_few_output_columns(oracle, Mout, Ntok, K):
+    """At most 16 output columns (the model's pair-bias and outer-product-mean projections): PATH_AUTO takes the one-pass
+    CUDA-core kernel -- quantization in registers, dp4a against the weights in shared memory.  int32 block sums bit-exact,
+    fp32 output 1e-5, and the same results as the tensor-core kernel asked for by name."""
+    w, x = cases.q8_case(Mout, Ntok, K, seed=7)
+    x = _q8_special(x)
+    W = oracle.repack_q8_0(oracle.quantize_q8_0(w))
+    bias = (np.random.default_rng(3).standard_normal(Mout) * 0.1).astype(np.float32)
+    ref, ref_sumi = oracle.mul_mat_q8(W, x, Mout, wtype=2, c_trans=1, bias=bias, want_sumi=True)
+    got, taken, sumi = ops.mul_mat_q8_cuda(dev(W), dev(x), Mout, wtype=2, c_trans=1, bias=dev(bias), path=PATH_AUTO, want_sumi=True)
+    assert taken == 0                                                  # CUDA cores (every case here is inside the rule)
+    assert np.array_equal(host(sumi), ref_sumi)
+    assert cases.rel_err(host(got), ref) <= TOL_FP32
+    fast, _ = ops.mul_mat_q8_cuda(dev(W), dev(x), Mout, wtype=2, c_trans=1, path=PATH_AUTO)          # without bias, without sums
+    ref_nb = oracle.mul_mat_q8(W, x, Mout, wtype=2, c_trans=1)
+    assert cases.rel_err(host(fast), ref_nb) <= TOL_FP32
+    tc, taken_tc = ops.mul_mat_q8_cuda(dev(W), dev(x), Mout, wtype=2, c_trans=1, bias=dev(bias), path=PATH_UMMA)
+    assert taken_tc == 1 and cases.rel_err(host(tc), host(got)) <= TOL_FP32
+
+
 @pytest.mark.parametrize("wtype", [0, 1, 2])
 @pytest.mark.parametrize("c_trans", [0, 1])
 def test_mul_mat_q8_weight_layouts(oracle, wtype, c_trans):
