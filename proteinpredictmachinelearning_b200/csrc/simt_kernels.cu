@@ -436,13 +436,14 @@ __global__ void __launch_bounds__(32 * kSkinnyWarps)
 q8_skinny_kernel(const uint8_t* __restrict__ W, const float* __restrict__ X, float* __restrict__ C, int M, long long units,
                  int nblk, int lg_nblk, const float* __restrict__ bias, int* __restrict__ sumi_out) {
     extern __shared__ __align__(16) int sk_smem[];
-    int* ws = sk_smem;                                              // [MP][nblk][8] weight words
-    float* dws = reinterpret_cast<float*>(ws + MP * nblk * 8);      // [MP][nblk] weight scales
+    int* ws = sk_smem;                                              // [MP][nblk][12] weight words: 8 used, a pitch of 48 bytes keeps the
+                                                                    // 16-byte reads of lanes on different blocks off each other's banks
+    float* dws = reinterpret_cast<float*>(ws + MP * nblk * 12);     // [MP][nblk] weight scales
     float* xs = dws + MP * nblk + (threadIdx.x >> 5) * (32 * kSkinnyPitch);     // this warp's 32 staged blocks
     const size_t nb_all = static_cast<size_t>(M) * nblk;
-    for (int e = threadIdx.x; e < MP * nblk * 8; e += blockDim.x) {
-        const int m = e / (nblk * 8);
-        ws[e] = m < M ? reinterpret_cast<const int*>(W)[e] : 0;     // planar: [M][nblk][32] int8, row m block ib at (m nblk + ib) 32
+    for (int e = threadIdx.x; e < MP * nblk * 8; e += blockDim.x) {          // planar: [M][nblk][32] int8, row m block ib at (m nblk + ib) 32
+        const int blk = e >> 3;
+        ws[blk * 12 + (e & 7)] = blk < M * nblk ? reinterpret_cast<const int*>(W)[e] : 0;
     }
     for (int e = threadIdx.x; e < MP * nblk; e += blockDim.x)
         dws[e] = e < M * nblk ? __half2float(*reinterpret_cast<const __half*>(W + nb_all * 32 + static_cast<size_t>(e) * 2)) : 0.0f;
@@ -493,8 +494,8 @@ q8_skinny_kernel(const uint8_t* __restrict__ W, const float* __restrict__ X, flo
         float part[MP];
 #pragma unroll
         for (int m = 0; m < MP; ++m) {
-            const int4 w0 = *reinterpret_cast<const int4*>(ws + (m * nblk + ib) * 8);
-            const int4 w1 = *reinterpret_cast<const int4*>(ws + (m * nblk + ib) * 8 + 4);
+            const int4 w0 = *reinterpret_cast<const int4*>(ws + (m * nblk + ib) * 12);
+            const int4 w1 = *reinterpret_cast<const int4*>(ws + (m * nblk + ib) * 12 + 4);
             int sumi = __dp4a(w0.x, static_cast<int>(aq[0]), 0);
             sumi = __dp4a(w0.y, static_cast<int>(aq[1]), sumi); sumi = __dp4a(w0.z, static_cast<int>(aq[2]), sumi);
             sumi = __dp4a(w0.w, static_cast<int>(aq[3]), sumi); sumi = __dp4a(w1.x, static_cast<int>(aq[4]), sumi);
@@ -531,7 +532,7 @@ int launch_q8_skinny(const void* W, const float* X, float* C, int M, int N, int 
     const long long cap = 8LL * num_sms();
     if (grid > cap) grid = cap;
     const int mp = M <= 8 ? 8 : 16;
-    const size_t smem = static_cast<size_t>(mp) * nblk * (32 + 4) + kSkinnyWarps * 32 * kSkinnyPitch * sizeof(float);   // <= 36.9 KB
+    const size_t smem = static_cast<size_t>(mp) * nblk * (48 + 4) + kSkinnyWarps * 32 * kSkinnyPitch * sizeof(float);   // <= 44.4 KB
     if (mp == 8)
         q8_skinny_kernel<8><<<static_cast<unsigned>(grid), 32 * kSkinnyWarps, smem, st>>>(static_cast<const uint8_t*>(W), X, C, M, units, nblk, lg, bias, sumi_out);
     else
