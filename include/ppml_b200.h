@@ -171,7 +171,12 @@ int ppml_b200_q8_file_load(void* handle, int index, void* dst_dev, void* scratch
  * Replaces flash_attn_forward_cuda (src/backend/CUDAKernels.cpp:174; include/ppml/FlashAttn.h:60;
  * src/cuda/FlashAttnKernel.cu:206-251).  Q/K/V/O [B][h][L][d] (d innermost), bias [B][h][L][L] or
  * NULL, LSE [B][h][L] or NULL.  O = softmax(scale*Q K^T + bias) V with denominator (l + eps).
- * scale <= 0 means 1/sqrt(d). */
+ * scale <= 0 means 1/sqrt(d).
+ * path: PPML_B200_PATH_SIMT runs the exact fp32 kernels for every head dim.  PPML_B200_PATH_AUTO takes a tensor-core
+ * kernel where there is one -- head dim 32 (tcgen05) and head dim 8 with at least 16 query rows (warp-level mma), both
+ * with tf32 products and fp32 softmax, 1e-3 on O and 2e-3 on LSE -- when the operands are 16-byte aligned (head dim 32
+ * with a bias: bias rows a multiple of 16 bytes), and the exact kernels otherwise.  PPML_B200_PATH_UMMA returns
+ * status 1 instead of falling back. */
 typedef struct ppml_b200_flash_cfg {
     int B, h, L, d;
     int causal;
