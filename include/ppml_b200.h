@@ -103,7 +103,10 @@ int ppml_b200_cast_f32_to_bf16(const float* x, void* y, int64_t n, void* stream)
  * W: quantized weights, M rows (out features) of K; wtype 0 = Q8_0 (34-byte blocks), 1 = Q8_1
  * (36-byte blocks), 2 = Q8_0R ([M*K/32*32] int8 plane then [M*K/32] half scales).  X: fp32
  * activations [N][K], quantized on the fly per 32-block.  c_trans 0: C[m*N+n]; 1: C[n*M+m].
- * path_out (may be NULL): 1 = tensor cores, 0 = dp4a.
+ * path_out (may be NULL): 1 = tensor cores, 0 = dp4a on CUDA cores.  PPML_B200_PATH_AUTO runs the tensor-core kernel,
+ * except for planar weights with M <= 16 (the model's pair-bias and outer-product-mean projections), where that kernel
+ * is bound by its activation quantizer and a one-pass CUDA-core kernel is faster (same quantization, int32 block sums
+ * bit for bit the same); PPML_B200_PATH_SIMT is the two-kernel dp4a form of the reference's fallback.
  * Extensions over the reference: bias[M] (may be NULL) is added after the last block;
  * sumi_out (may be NULL) receives the exact int32 block sums as [N][M][K/32]. */
 int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, int K, int wtype, int c_trans,
