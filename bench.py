@@ -7,7 +7,7 @@ Headline workload (the reference's Q8 benchmark configuration): the Q8 block-qua
 W[N,K] ~ N(0, 0.02) quantized to int8 blocks of 32 with an fp16 scale (planar Q8_0R), activations X[M,K] ~ N(0,1)
 quantized on the fly; K in {128, 256, 1024}, N in {128, 256, 512, 1024}, M in {408, 2601, 65536}; seed 2.
 One pass = the 36 shapes, captured once as a CUDA graph; one step = `passes_per_step` replays of it (so that a
-step lasts about 0.1 s and the clock sampler sees the timed region).  `value`, `ms_per_step` and `roofline` all come
+step lasts 0.125 s or more, the timed region 2.6 s or more, and the clock sampler sees it).  `value`, `ms_per_step` and `roofline` all come
 from that one timed region (inputs resident in HBM); `e2e` is the same pass through the C ABI with pinned host
 buffers, copies inside the timed region.  After the timed region sampled token rows of every shape are compared
 with the CPU checker (`checked`).  At N > 1 GPUs every rank runs the sweep on its own token rows (weak scaling, no
@@ -576,7 +576,9 @@ def run_ours(args):
     e1.record()
     barrier()
     pass_ms_est = max_over_ranks(e0.elapsed_time(e1) / 5)
-    passes = args.passes if args.passes > 0 else max(1, int(math.ceil(125.0 / max(pass_ms_est, 1e-3))))
+    # a step lasts at least 0.125 s and the timed region at least 2.6 s, so that the 100 ms clock sampler sees 20+ samples
+    step_ms = max(125.0, 2600.0 / max(args.steps, 1))
+    passes = args.passes if args.passes > 0 else max(1, int(math.ceil(step_ms / max(pass_ms_est, 1e-3))))
     for _ in range(max(args.warmup, 3)):   # W warm-up steps of the timed form
         for _ in range(passes if args.warmup_full else 1):
             run()
@@ -824,7 +826,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--passes", type=int, default=0, help="replays of the sweep per step (0: as many as make a step last about 0.125 s)")
+    ap.add_argument("--passes", type=int, default=0, help="replays of the sweep per step (0: as many as make a step last 0.125 s or more and the timed region 2.6 s)")
     ap.add_argument("--warmup-full", action="store_true", help="warm-up steps replay `passes` passes too (default: one pass each)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="stop after the device-resident region (profiling runs)")
