@@ -441,6 +441,21 @@ q8_skinny_kernel(const uint8_t* __restrict__ W, const float* __restrict__ X, flo
     float* dws = reinterpret_cast<float*>(ws + MP * nblk * 12);     // [MP][nblk] weight scales
     float* xs = dws + MP * nblk + (threadIdx.x >> 5) * (32 * kSkinnyPitch);     // this warp's 32 staged blocks
     const size_t nb_all = static_cast<size_t>(M) * nblk;
+    const int lane = threadIdx.x & 31;
+    const long long step = static_cast<long long>(gridDim.x) * (blockDim.x >> 5) * 32;
+    long long u0 = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32;
+    // the warp's 32 blocks of a step are 256 16-byte words: word g (block g / 8, word g % 8 of it) by lane g % 32.  The first
+    // step's words are requested before the weights are staged, every later step's while the one before is worked on
+    float4 v[8];
+    auto request = [&](long long base) {
+        const float4* src = reinterpret_cast<const float4*>(X + base * 32);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int g = j * 32 + lane;
+            v[j] = (base + (g >> 3) < units) ? __ldg(src + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    if (u0 < units) request(u0);
     for (int e = threadIdx.x; e < MP * nblk * 8; e += blockDim.x) {          // planar: [M][nblk][32] int8, row m block ib at (m nblk + ib) 32
         const int blk = e >> 3;
         ws[blk * 12 + (e & 7)] = blk < M * nblk ? reinterpret_cast<const int*>(W)[e] : 0;
@@ -448,22 +463,13 @@ q8_skinny_kernel(const uint8_t* __restrict__ W, const float* __restrict__ X, flo
     for (int e = threadIdx.x; e < MP * nblk; e += blockDim.x)
         dws[e] = e < M * nblk ? __half2float(*reinterpret_cast<const __half*>(W + nb_all * 32 + static_cast<size_t>(e) * 2)) : 0.0f;
     __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const long long step = static_cast<long long>(gridDim.x) * (blockDim.x >> 5) * 32;
-    for (long long u0 = (static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; u0 < units; u0 += step) {
+    for (; u0 < units; u0 += step) {
         const long long u = u0 + lane;
         const bool live = u < units;
         const long long row = u >> lg_nblk;
         const int ib = static_cast<int>(u & (nblk - 1));
         float x[32];
         {
-            const float4* src = reinterpret_cast<const float4*>(X + u0 * 32);       // the warp's 32 blocks: 256 16-byte words
-            float4 v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int g = j * 32 + lane;                                        // word g: block g / 8, word g % 8 of it
-                v[j] = (u0 + (g >> 3) < units) ? __ldg(src + g) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
             __syncwarp();                                                           // the previous step's reads are done
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -471,6 +477,7 @@ q8_skinny_kernel(const uint8_t* __restrict__ W, const float* __restrict__ X, flo
                 *reinterpret_cast<float4*>(xs + (g >> 3) * kSkinnyPitch + (g & 7) * 4) = v[j];
             }
             __syncwarp();
+            if (u0 + step < units) request(u0 + step);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float4 w = *reinterpret_cast<const float4*>(xs + lane * kSkinnyPitch + j * 4);
