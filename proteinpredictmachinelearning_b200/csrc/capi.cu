@@ -234,10 +234,11 @@ int ppml_b200_mul_mat_q8(const void* W, const float* X, float* C, int M, int N, 
     cudaStream_t st = as_stream(stream);
     if (path != PPML_B200_PATH_SIMT) {
         int rc = ST_UNSUPPORTED_PATH;
-        if (wtype == 2 && path == PPML_B200_PATH_AUTO && (M <= 8 || (M <= 16 && (K <= 128 || N <= 16384)))) {
+        if (wtype == 2 && path == PPML_B200_PATH_AUTO && M <= 16) {
             // very few output columns: the tensor-core kernel would be bound by its activation quantizer (measured at
-            // 65536 tokens: 128 -> 8 11 against 21 us, 64 -> 16 at 262144 tokens 32 against 56; 256 -> 16 is the one case
-            // where the tensor-core kernel still wins with many tokens, 32 against 36 us, and loses with few, 12 against 7)
+            // 65536 tokens: 128 -> 8 11 against 21 us, 256 -> 16 32 against 32, 64 -> 16 at 262144 tokens 29 against 56; at the
+            // 8192 tokens of an eight-way shard 4 against 8 and 6 against 12).  The choice must not depend on the token
+            // count: a shard of the tokens and the whole have to take the same kernel to give the same bits.
             const int rs = launch_q8_skinny(W, X, C, M, N, K, c_trans, bias, sumi_out, st);
             if (rs != ST_UNSUPPORTED_PATH) return rs;
         }
